@@ -1,0 +1,140 @@
+"""Python-side mirror of the kernel entry points, for tests and the benchmark.
+
+The reference registers one callable per kernel, all of the shape
+``void name(half *A, half *B, half *C, size_t M, size_t N, size_t K)`` (reference
+src/main.cu:11-33). The functions here keep that argument order and meaning for torch CUDA
+tensors: ``A`` is ``[M, K]`` row-major, ``B`` is ``[N, K]`` row-major (the reference's
+"col-major K x N", src/common/tester.h:117-119), ``C`` is ``[M, N]`` row-major; all float16
+and contiguous. Everything runs on torch's current stream and returns without synchronising.
+torch is used for device memory and streams only; the arithmetic is the native library's.
+"""
+from __future__ import annotations
+
+import ctypes
+
+from . import _native
+from ._native import HgemmError, Plan, check
+
+__all__ = [
+    "b200Hgemm", "b200HgemmCta1", "b200HgemmCta2", "b200HgemmSplitK", "b200HgemmStreamK", "b200HgemmSimt",
+    "hgemm_ex", "hgemm_host", "select_plan", "workspace_bytes", "last_device_error", "launch_count",
+    "KERNEL_LOG_NAMES", "Plan", "HgemmError",
+]
+
+# log names, in the reference's style (no spaces: its plot tool splits lines on spaces,
+# reference tools/performance/performance.py:57-62)
+KERNEL_LOG_NAMES = {
+    "b200Hgemm": "B200-Tcgen05-Auto",
+    "b200HgemmCta1": "B200-Tcgen05-1Cta",
+    "b200HgemmCta2": "B200-Tcgen05-2Cta",
+    "b200HgemmSplitK": "B200-Tcgen05-SplitK",
+    "b200HgemmStreamK": "B200-Tcgen05-StreamK",
+    "b200HgemmSimt": "B200-Simt-Fp32Acc",
+}
+
+
+def _shape_of(A, B, C):
+    import torch
+
+    for name, t in (("A", A), ("B", B), ("C", C)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.float16 or not t.is_cuda or not t.is_contiguous():
+            raise TypeError(f"{name} must be a contiguous float16 CUDA tensor")
+        if t.dim() != 2:
+            raise ValueError(f"{name} must be 2-D")
+    M, K = A.shape
+    N, Kb = B.shape
+    if Kb != K or tuple(C.shape) != (M, N):
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)}, B {tuple(B.shape)} (N x K), C {tuple(C.shape)}")
+    if A.device != B.device or A.device != C.device:
+        raise ValueError("A, B and C must live on one device")
+    return int(M), int(N), int(K)
+
+
+def _stream_of(t) -> int:
+    import torch
+
+    return int(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _call(symbol: str, A, B, C):
+    import torch
+
+    M, N, K = _shape_of(A, B, C)
+    fn = getattr(_native.load(), symbol)
+    with torch.cuda.device(A.device):
+        check(fn(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, _stream_of(A)))
+    return C
+
+
+def b200Hgemm(A, B, C):
+    """Auto-dispatching GEMM (C ABI ``b200_hgemm``)."""
+    return _call("b200_hgemm", A, B, C)
+
+
+def b200HgemmCta1(A, B, C):
+    """Single-CTA tcgen05 tiles (C ABI ``b200_hgemm_cta1``)."""
+    return _call("b200_hgemm_cta1", A, B, C)
+
+
+def b200HgemmCta2(A, B, C):
+    """CTA-pair tcgen05 tiles (C ABI ``b200_hgemm_cta2``)."""
+    return _call("b200_hgemm_cta2", A, B, C)
+
+
+def b200HgemmSplitK(A, B, C):
+    """Fixed k-slices per tile with an FP32 workspace reduce (C ABI ``b200_hgemm_splitk``)."""
+    return _call("b200_hgemm_splitk", A, B, C)
+
+
+def b200HgemmStreamK(A, B, C):
+    """Equal k-ranges over all SMs (C ABI ``b200_hgemm_streamk``)."""
+    return _call("b200_hgemm_streamk", A, B, C)
+
+
+def b200HgemmSimt(A, B, C):
+    """CUDA-core kernel for any shape (C ABI ``b200_hgemm_simt``)."""
+    return _call("b200_hgemm_simt", A, B, C)
+
+
+def hgemm_ex(A, B, C, plan: Plan):
+    """Run an explicit plan (C ABI ``b200_hgemm_ex``)."""
+    import torch
+
+    M, N, K = _shape_of(A, B, C)
+    with torch.cuda.device(A.device):
+        check(_native.load().b200_hgemm_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, ctypes.byref(plan),
+                                           _stream_of(A)))
+    return C
+
+
+def hgemm_host(A_host, B_host, C_host):
+    """HOST tensors in, HOST tensor out (C ABI ``b200_hgemm_host``): uploads, multiplies, downloads, synchronises."""
+    import torch
+
+    for name, t in (("A", A_host), ("B", B_host), ("C", C_host)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.float16 or t.is_cuda or not t.is_contiguous():
+            raise TypeError(f"{name} must be a contiguous float16 CPU tensor")
+    M, K = A_host.shape
+    N, Kb = B_host.shape
+    if Kb != K or tuple(C_host.shape) != (M, N):
+        raise ValueError("shape mismatch")
+    check(_native.load().b200_hgemm_host(A_host.data_ptr(), B_host.data_ptr(), C_host.data_ptr(), int(M), int(N), int(K)))
+    return C_host
+
+
+def select_plan(M: int, N: int, K: int) -> Plan:
+    plan = Plan()
+    check(_native.load().b200_hgemm_select(M, N, K, ctypes.byref(plan)))
+    return plan
+
+
+def workspace_bytes(M: int, N: int, K: int, plan: Plan) -> int:
+    return int(_native.load().b200_hgemm_workspace_bytes(M, N, K, ctypes.byref(plan)))
+
+
+def last_device_error() -> int:
+    return int(_native.load().b200_hgemm_last_device_error())
+
+
+def launch_count() -> int:
+    return int(_native.load().b200_hgemm_launch_count())

@@ -1,0 +1,462 @@
+// The sm_100a HGEMM kernel family: C[M x N] = A[M x K] * B^T, with A row-major (K
+// contiguous), B stored as N rows of K contiguous halves, C row-major FP16 -- the operand
+// layouts of the reference's entry points (src/main.cu:11, src/common/tester.h:117-119,
+// element indexing as in src/simt_naive.cu:18-24). FP16 products are accumulated in FP32 in
+// tensor memory and rounded to FP16 once.
+//
+// It replaces the reference's mma.sync / WMMA kernels (src/mma/*.cu, src/wmma/*.cu, e.g.
+// src/mma/mma_async_stage4.cu:54-644) with one warp-specialised design:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of a 128 x 64 slab of A and a
+//               (BN / CG) x 64 slab of B into a ring of 128B-swizzled stages
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (UMMA 128*CG x BN x 16)
+//               and commits stage releases / accumulator hand-offs to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld -> FP32 -> FP16 -> swizzled staging -> TMA store
+//               (or FP32 partials to the workspace when a tile's k-range is split)
+//
+// Two accumulators live in TMEM, so the epilogue of one tile overlaps the main loop of the
+// next. CG = 2 runs a pair of CTAs (a 2-CTA cluster) on one 256 x BN tile: each CTA stages
+// its own 128 rows of A and half of the B slab, the leader CTA issues the MMAs for both.
+//
+// Every wait in the kernel is time-bounded; on expiry the CTA drains, frees its tensor
+// memory and raises an error word the host reads.
+#pragma once
+
+#include "ptx_sm100.cuh"
+#include "sched.h"
+
+namespace b200 {
+
+constexpr int kBM = 128;          // rows of C per CTA
+constexpr int kBK = 64;           // halves per k-block = one 128-byte swizzle row
+constexpr int kThreads = 192;     // 6 warps
+constexpr int kEpiThreads = 128;  // warps 2..5
+constexpr uint32_t kStagingBytes = 4u * 2u * 4096u;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+
+enum GemmMode : int {
+    kModeTiles = 0,    // every CTA walks whole tiles, strided by the grid
+    kModeStreamK = 1,  // every CTA owns a contiguous range of (tile, k-block) units
+};
+
+// Error codes a kernel can raise in GemmParams::error_word.
+enum DeviceError : uint32_t {
+    kDevOk = 0,
+    kDevWaitTimeout = 1,
+};
+
+struct alignas(64) GemmParams {
+    CUtensorMap tm_a;  // A as {K, M}, box {64, 128}
+    CUtensorMap tm_b;  // B as {K, N}, box {64, BN / CG}
+    CUtensorMap tm_c;  // C as {N, M}, box {64, 32} (only valid when tma_store != 0)
+    __half *c;
+    float4 *partials;        // stream-K: 2 slots per part, each 128 x BN FP32
+    uint32_t *tile_counters; // stream-K: one per tile, zero between launches
+    uint32_t *error_word;
+    uint32_t m, n, k;
+    uint32_t m_blocks;  // number of (128 * CG)-row blocks
+    uint32_t n_blocks;
+    uint32_t k_blocks;
+    uint32_t tiles;
+    uint32_t group_m;
+    uint32_t tma_store;  // 1: epilogue uses TMA stores (needs N % 8 == 0)
+    uint32_t c_vec_ok;   // 1: 16-byte vector stores to C are aligned (N % 8 == 0)
+};
+
+template <int BN, int STAGES, int CG>
+struct KernelTraits {
+    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+    static_assert(CG == 1 || CG == 2, "CG is the CTA-pair size");
+    static constexpr uint32_t kARows = kBM;
+    static constexpr uint32_t kBRows = BN / CG;
+    static constexpr uint32_t kABytes = kARows * kBK * 2;
+    static constexpr uint32_t kBBytes = kBRows * kBK * 2;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two
+    static constexpr uint32_t kBarrierBytes = 256;
+    static constexpr uint32_t kSmemBytes = 1024 + STAGES * kStageBytes + kStagingBytes + kBarrierBytes;
+    static_assert((kStageBytes % 1024) == 0, "stages must keep 1024-byte alignment");
+    static_assert(kSmemBytes <= 232448, "exceeds 227 KB of shared memory");
+    static_assert((2 * STAGES + 4) * 8 + 16 <= kBarrierBytes, "barrier area too small");
+};
+
+// Iterates this worker's segments; all three roles walk the same sequence.
+template <int MODE>
+struct WorkWalker;
+
+template <>
+struct WorkWalker<kModeTiles> {
+    uint32_t t, step, tiles, k_blocks;
+    __device__ WorkWalker(const GemmParams &p, uint32_t worker, uint32_t workers)
+        : t(worker), step(workers), tiles(p.tiles), k_blocks(p.k_blocks) {}
+    __device__ bool next(Segment &s) {
+        if (t >= tiles) return false;
+        s.tile = t;
+        s.kb0 = 0;
+        s.kb1 = k_blocks;
+        t += step;
+        return true;
+    }
+};
+
+template <>
+struct WorkWalker<kModeStreamK> {
+    SegmentWalker w;
+    __device__ WorkWalker(const GemmParams &p, uint32_t worker, uint32_t workers)
+        : w(worker, workers, p.tiles, p.k_blocks) {}
+    __device__ bool next(Segment &s) { return w.next(s); }
+};
+
+// 32 FP32 accumulator columns of one row -> FP16 -> global memory.
+__device__ __forceinline__ void store_row_chunk32(__half *c, uint32_t row, uint32_t col0, uint32_t m, uint32_t n,
+                                                  bool vec_ok, const uint32_t (&r)[32]) {
+    if (row >= m || col0 >= n) return;
+    __half *dst = c + static_cast<size_t>(row) * n + col0;
+    if (vec_ok && col0 + 32 <= n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_half2_rn(r[8 * j + 0], r[8 * j + 1]);
+            v.y = pack_half2_rn(r[8 * j + 2], r[8 * j + 3]);
+            v.z = pack_half2_rn(r[8 * j + 4], r[8 * j + 5]);
+            v.w = pack_half2_rn(r[8 * j + 6], r[8 * j + 7]);
+            reinterpret_cast<uint4 *>(dst)[j] = v;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col0 + j < n) dst[j] = __float2half_rn(__uint_as_float(r[j]));
+        }
+    }
+}
+
+template <int BN, int STAGES, int CG, int MODE>
+__global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+    using T = KernelTraits<BN, STAGES, CG>;
+    static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - raw_addr);
+
+    const uint32_t staging = base + STAGES * T::kStageBytes;
+    uint8_t *staging_ptr = base_ptr + STAGES * T::kStageBytes;
+    const uint32_t bars = staging + kStagingBytes;
+    uint8_t *bars_ptr = staging_ptr + kStagingBytes;
+    // barrier area: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | tmem base | abort | last flag
+    const uint32_t full_bar = bars;
+    const uint32_t empty_bar = bars + 8u * STAGES;
+    const uint32_t tfull_bar = bars + 16u * STAGES;
+    const uint32_t tempty_bar = tfull_bar + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_ptr + 16u * STAGES + 32u);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    volatile uint32_t *last_flag = tmem_slot + 2;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t cta_rank = (CG == 2) ? cluster_cta_rank() : 0u;
+    const uint32_t worker = blockIdx.x / CG;
+    const uint32_t workers = gridDim.x / CG;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar + 8u * a, 1);
+            mbar_init(tempty_bar + 8u * a, 4 * CG);  // one arrival per epilogue warp of every CTA of the pair
+        }
+        *abort_flag = 0;
+        *last_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&p.tm_a);
+        tma_prefetch_desc(&p.tm_b);
+        if (p.tma_store) tma_prefetch_desc(&p.tm_c);
+    }
+    if (warp == 1) {
+        tmem_alloc<CG>(smem_u32(const_cast<uint32_t *>(tmem_slot)), T::kTmemCols);
+        tmem_relinquish<CG>();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (CG == 2) cluster_sync_all();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            WorkWalker<MODE> work(p, worker, workers);
+            Segment seg;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            while (ok && work.next(seg)) {
+                const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
+                const int32_t row_a = static_cast<int32_t>((tc.m_blk * CG + cta_rank) * kBM);
+                const int32_t row_b = static_cast<int32_t>(tc.n_blk * BN + cta_rank * T::kBRows);
+                for (uint32_t kb = seg.kb0; kb < seg.kb1; ++kb) {
+                    if (!mbar_wait(empty_bar + 8u * stage, phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = base + stage * T::kStageBytes;
+                    const uint32_t sb = sa + T::kABytes;
+                    const int32_t kx = static_cast<int32_t>(kb * kBK);
+                    if (CG == 1) {
+                        mbar_arrive_expect_tx(full_bar + 8u * stage, T::kStageBytes);
+                        tma_load_2d(sa, &p.tm_a, kx, row_a, full_bar + 8u * stage);
+                        tma_load_2d(sb, &p.tm_b, kx, row_b, full_bar + 8u * stage);
+                    } else {
+                        // Both CTAs' copies complete on the leader's barrier; the leader alone
+                        // posts the expected byte count for the pair.
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * T::kStageBytes);
+                        const uint32_t leader_bar = map_to_cta(full_bar + 8u * stage, 0);
+                        tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
+                        tma_load_2d_pair(sb, &p.tm_b, kx, row_b, leader_bar);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16_f32(kBM * CG, BN);
+            WorkWalker<MODE> work(p, worker, workers);
+            Segment seg;
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            while (ok && work.next(seg)) {
+                const uint32_t acc = it & 1u;
+                const uint32_t acc_phase = (it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar + 8u * acc, acc_phase ^ 1u, abort_flag)) break;
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = seg.kb0; kb < seg.kb1; ++kb) {
+                    if (!mbar_wait(full_bar + 8u * stage, phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after_sync();
+                    const uint32_t sa = base + stage * T::kStageBytes;
+                    const uint64_t da = umma_smem_desc_sw128(sa);
+                    const uint64_t db = umma_smem_desc_sw128(sa + T::kABytes);
+#pragma unroll
+                    for (uint32_t k = 0; k < kBK / 16; ++k) {
+                        // 16 halves = 32 bytes along K inside the swizzle atom -> +2 in the address field
+                        umma_f16<CG>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > seg.kb0 || k > 0) ? 1u : 0u);
+                    }
+                    if (CG == 1) {
+                        umma_commit(empty_bar + 8u * stage);
+                    } else {
+                        umma_commit_pair(empty_bar + 8u * stage, 0x3);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                if (CG == 1) {
+                    umma_commit(tfull_bar + 8u * acc);
+                } else {
+                    umma_commit_pair(tfull_bar + 8u * acc, 0x3);
+                }
+                ++it;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
+        const uint32_t epi_tid = threadIdx.x - 64u;
+        uint8_t *my_staging_ptr = staging_ptr + q * 8192u;
+        const uint32_t my_staging = staging + q * 8192u;
+        WorkWalker<MODE> work(p, worker, workers);
+        Segment seg;
+        uint32_t it = 0, store_buf = 0;
+        while (work.next(seg)) {
+            const uint32_t acc = it & 1u;
+            const uint32_t acc_phase = (it >> 1) & 1u;
+            const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
+            const uint32_t m0 = (tc.m_blk * CG + cta_rank) * kBM;
+            const uint32_t n0 = tc.n_blk * BN;
+            if (!mbar_wait(tfull_bar + 8u * acc, acc_phase, abort_flag)) break;
+            tcgen05_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+            const uint32_t row_in_tile = q * 32u + lane;
+            const bool whole_tile = (MODE == kModeTiles) || (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
+
+            if (whole_tile) {
+                if (p.tma_store) {
+                    const bool warp_rows_live = (m0 + q * 32u) < p.m;
+#pragma unroll 1
+                    for (uint32_t c = 0; c < BN / 64; ++c) {
+                        uint32_t r0[32], r1[32];
+                        tmem_ld_32x32b_x32(taddr + c * 64u, r0);
+                        tmem_ld_32x32b_x32(taddr + c * 64u + 32u, r1);
+                        tmem_ld_wait();
+                        const bool live = warp_rows_live && (n0 + c * 64u) < p.n;
+                        if (live) {
+                            uint8_t *buf = my_staging_ptr + (store_buf & 1u) * 4096u;
+                            // the store issued two chunks ago read this buffer: wait until it has
+                            if (lane == 0) tma_store_wait_read<1>();
+                            __syncwarp();
+                            uint8_t *row_ptr = buf + lane * 128u;
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                uint4 v;
+                                v.x = pack_half2_rn(r0[8 * j + 0], r0[8 * j + 1]);
+                                v.y = pack_half2_rn(r0[8 * j + 2], r0[8 * j + 3]);
+                                v.z = pack_half2_rn(r0[8 * j + 4], r0[8 * j + 5]);
+                                v.w = pack_half2_rn(r0[8 * j + 6], r0[8 * j + 7]);
+                                *reinterpret_cast<uint4 *>(row_ptr + ((j ^ (lane & 7u)) << 4)) = v;
+                            }
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                uint4 v;
+                                v.x = pack_half2_rn(r1[8 * j + 0], r1[8 * j + 1]);
+                                v.y = pack_half2_rn(r1[8 * j + 2], r1[8 * j + 3]);
+                                v.z = pack_half2_rn(r1[8 * j + 4], r1[8 * j + 5]);
+                                v.w = pack_half2_rn(r1[8 * j + 6], r1[8 * j + 7]);
+                                *reinterpret_cast<uint4 *>(row_ptr + (((j + 4u) ^ (lane & 7u)) << 4)) = v;
+                            }
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_2d(&p.tm_c, my_staging + (store_buf & 1u) * 4096u,
+                                             static_cast<int32_t>(n0 + c * 64u), static_cast<int32_t>(m0 + q * 32u));
+                                tma_store_commit();
+                            }
+                            ++store_buf;
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (uint32_t c = 0; c < BN / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(taddr + c * 32u, r);
+                        tmem_ld_wait();
+                        store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
+                    }
+                }
+                // accumulator drained: hand it back to the MMA warp
+                tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (CG == 1) {
+                        mbar_arrive(tempty_bar + 8u * acc);
+                    } else {
+                        mbar_arrive_cluster(map_to_cta(tempty_bar + 8u * acc, 0));
+                    }
+                }
+            } else {
+                // ---- this tile's k-range is shared with other workers: publish an FP32 partial
+                const uint32_t slot = partial_slot(worker, workers, p.tiles, p.k_blocks, seg.tile);
+                float4 *ws = p.partials + static_cast<size_t>(slot) * (kBM * BN / 4);
+                const bool row_live = (m0 + row_in_tile) < p.m;
+#pragma unroll 1
+                for (uint32_t c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32u, r);
+                    tmem_ld_wait();
+                    if (row_live && (n0 + c * 32u) < p.n) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            // row-fastest layout: consecutive lanes write consecutive 16-byte words
+                            ws[(c * 8u + j) * kBM + row_in_tile] = v;
+                        }
+                    }
+                }
+                tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar + 8u * acc);
+
+                // ---- count this contribution; whoever completes the tile reduces it
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (epi_tid == 0) {
+                    const uint32_t mine = seg.kb1 - seg.kb0;
+                    const uint32_t before = atomicAdd(p.tile_counters + seg.tile, mine);
+                    *last_flag = (before + mine == p.k_blocks) ? 1u : 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool is_last = (*last_flag != 0);
+                if (is_last) {
+                    __threadfence();
+                    const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
+                    const uint64_t u0 = static_cast<uint64_t>(seg.tile) * p.k_blocks;
+                    const uint32_t part_first = part_of_unit(u0, workers, total_units);
+                    const uint32_t part_last = part_of_unit(u0 + p.k_blocks - 1, workers, total_units);
+                    if (row_live) {
+#pragma unroll 1
+                        for (uint32_t c = 0; c < BN / 32; ++c) {
+                            if ((n0 + c * 32u) >= p.n) break;
+                            float4 sum[8];
+#pragma unroll
+                            for (uint32_t j = 0; j < 8; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            // fixed order over the contributing parts: the result does not depend
+                            // on which of them happened to finish last
+                            for (uint32_t part = part_first; part <= part_last; ++part) {
+                                const uint32_t s = partial_slot(part, workers, p.tiles, p.k_blocks, seg.tile);
+                                const float4 *src = p.partials + static_cast<size_t>(s) * (kBM * BN / 4);
+#pragma unroll
+                                for (uint32_t j = 0; j < 8; ++j) {
+                                    const float4 v = ld_cg_f4(src + (c * 8u + j) * kBM + row_in_tile);
+                                    sum[j].x += v.x;
+                                    sum[j].y += v.y;
+                                    sum[j].z += v.z;
+                                    sum[j].w += v.w;
+                                }
+                            }
+                            uint32_t r[32];
+#pragma unroll
+                            for (uint32_t j = 0; j < 8; ++j) {
+                                r[4 * j + 0] = __float_as_uint(sum[j].x);
+                                r[4 * j + 1] = __float_as_uint(sum[j].y);
+                                r[4 * j + 2] = __float_as_uint(sum[j].z);
+                                r[4 * j + 3] = __float_as_uint(sum[j].w);
+                            }
+                            store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
+                        }
+                    }
+                    // leave the counter at zero for the next launch
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_tid == 0) p.tile_counters[seg.tile] = 0;
+                }
+            }
+            ++it;
+        }
+        // shared memory must stay valid until the last TMA store has read it
+        if (lane == 0) tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        // give copies still in flight time to land before shared memory is released
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+        if (threadIdx.x == 0) atomicExch(p.error_word, static_cast<uint32_t>(kDevWaitTimeout));
+        __syncthreads();
+    }
+    if (CG == 2) cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc<CG>(tmem_base, T::kTmemCols);
+    }
+}
+
+}  // namespace b200

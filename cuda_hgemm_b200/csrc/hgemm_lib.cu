@@ -1,0 +1,689 @@
+// Host side of the library: per-device state, tensor-map cache, shape -> plan selection,
+// kernel launches and the extern "C" entry points declared in include/b200_hgemm.h.
+//
+// What it stands in for in the reference: the per-kernel launchers with their one-time
+// shared-memory opt-in (e.g. src/mma/mma_async_stage4.cu:619-644) and the kernel table of
+// src/main.cu:11-33. Unlike those, nothing here exits the process: errors are return codes.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "../../include/b200_hgemm.h"
+#include "gemm_kernel.cuh"
+
+namespace b200 {
+
+// ------------------------------------------------------------------------------------------
+// per-device state
+// ------------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+constexpr size_t kMaxOwnedWorkspace = size_t(1) << 30;  // the library never grows its own workspace past 1 GiB
+constexpr size_t kCounterBytes = 64 * 1024;             // tile counters at the front of the workspace
+constexpr uint32_t kMaxCountedTiles = kCounterBytes / 4;
+
+struct TensorMapKey {
+    const void *ptr;
+    uint64_t rows, cols;
+    uint32_t box_rows, box_cols;
+    bool operator==(const TensorMapKey &o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols;
+    }
+};
+
+struct TensorMapSlot {
+    bool used = false;
+    TensorMapKey key{};
+    CUtensorMap map{};
+};
+
+struct DeviceState {
+    std::mutex mu;
+    bool probed = false;
+    bool sm100 = false;
+    int sm_count = 0;
+    uint32_t *error_word = nullptr;
+    // split-k workspace: [tile counters | FP32 partial slots]
+    void *ws = nullptr;
+    size_t ws_bytes = 0;
+    bool ws_owned = false;
+    // staging buffers of the host-pointer entry point
+    void *host_a = nullptr, *host_b = nullptr, *host_c = nullptr;
+    size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
+    cudaStream_t host_stream[2] = {nullptr, nullptr};
+    cudaEvent_t host_event[2] = {nullptr, nullptr};
+    bool attr_set[16] = {};
+    TensorMapSlot tm_cache[64];
+};
+
+static DeviceState g_dev[kMaxDevices];
+static std::atomic<uint64_t> g_launches{0};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess) {
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+static int current_state(DeviceState **out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return B200_HGEMM_ERR_CUDA;
+    DeviceState &st = g_dev[dev];
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (!st.probed) {
+        int major = 0, sms = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            return B200_HGEMM_ERR_CUDA;
+        }
+        st.sm100 = (major == 10);
+        st.sm_count = sms;
+        if (st.sm100) {
+            if (cudaMalloc(&st.error_word, 256) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+            if (cudaMemset(st.error_word, 0, 256) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+        }
+        st.probed = true;
+    }
+    *out = &st;
+    return B200_HGEMM_OK;
+}
+
+// A 2-D FP16 tensor of `rows` x `cols` (cols contiguous) viewed through boxes of
+// box_rows x box_cols with the 128-byte swizzle. Out-of-range elements read as zero and
+// are dropped on store.
+static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                          uint32_t box_cols, CUtensorMap *out) {
+    TensorMapKey key{ptr, rows, cols, box_rows, box_cols};
+    size_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
+    h ^= rows * 0xC2B2AE3D27D4EB4Full + cols * 0x165667B19E3779F9ull + box_rows * 131u + box_cols;
+    const size_t idx = (h >> 20) & 63u;
+    std::lock_guard<std::mutex> lock(st.mu);
+    TensorMapSlot &slot = st.tm_cache[idx];
+    if (slot.used && slot.key == key) {
+        *out = slot.map;
+        return B200_HGEMM_OK;
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return B200_HGEMM_ERR_CUDA;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * sizeof(__half)};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult r = enc(&slot.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box,
+                     elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        slot.used = false;
+        return B200_HGEMM_ERR_CUDA;
+    }
+    slot.used = true;
+    slot.key = key;
+    *out = slot.map;
+    return B200_HGEMM_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// plans
+// ------------------------------------------------------------------------------------------
+static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) {
+    return static_cast<uint32_t>((a + b - 1) / b);
+}
+
+static bool plan_is_tensor(const b200_hgemm_plan &pl) {
+    return pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_CTA2 || pl.variant == B200_VARIANT_STREAMK;
+}
+
+static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
+    if (pl.variant == B200_VARIANT_SIMT) return B200_HGEMM_OK;
+    if (!plan_is_tensor(pl)) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 64) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
+    if (pl.tma_store && N % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (pl.parts < 0 || pl.group_m < 0 || pl.grid < 0) return B200_HGEMM_ERR_INVALID_ARG;
+    return B200_HGEMM_OK;
+}
+
+static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, uint32_t tiles, uint32_t k_blocks) {
+    uint64_t units = static_cast<uint64_t>(tiles) * k_blocks;
+    uint64_t parts = pl.parts > 0 ? static_cast<uint64_t>(pl.parts) : static_cast<uint64_t>(st.sm_count);
+    if (parts > units) parts = units;
+    if (parts < 1) parts = 1;
+    return static_cast<uint32_t>(parts);
+}
+
+// Shape -> plan. Large problems run whole 128x256 (or 256x256 per CTA pair) tiles; problems
+// that leave SMs idle in their last (or only) wave split k-ranges evenly over all SMs.
+static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
+    memset(pl, 0, sizeof(*pl));
+    if (K % 8 != 0) {
+        pl->variant = B200_VARIANT_SIMT;
+        return;
+    }
+    const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
+    pl->tma_store = (N % 8 == 0) ? 1 : 0;
+    pl->group_m = 0;
+    const uint32_t m_blocks = ceil_div_u32(M, 128);
+    const uint32_t k_blocks = ceil_div_u32(K, 64);
+
+    // Efficiency of running whole tiles of width bn: useful tiles / (waves * SMs), discounted
+    // for narrow tiles, whose main loop re-reads the A slab more often per flop.
+    double best_score = -1.0;
+    int best_bn = 256;
+    const int bns[3] = {256, 128, 64};
+    const double width_factor[3] = {1.0, 0.88, 0.62};
+    for (int i = 0; i < 3; ++i) {
+        const uint64_t tiles = static_cast<uint64_t>(m_blocks) * ceil_div_u32(N, bns[i]);
+        const uint64_t waves = (tiles + sms - 1) / sms;
+        const double fill = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+        const double score = fill * width_factor[i];
+        if (score > best_score) {
+            best_score = score;
+            best_bn = bns[i];
+        }
+    }
+    if (best_score >= 0.80) {
+        pl->bn = best_bn;
+        const uint64_t tiles256 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 256);
+        if (best_bn == 256 && M % 256 == 0 && tiles256 >= 2ull * (sms / 2)) {
+            pl->variant = B200_VARIANT_CTA2;
+        } else {
+            pl->variant = B200_VARIANT_CTA1;
+        }
+        return;
+    }
+    // Not enough whole tiles: split k-ranges. Narrower tiles when there is little k to split.
+    pl->variant = B200_VARIANT_STREAMK;
+    pl->bn = 128;
+    const uint64_t tiles128 = static_cast<uint64_t>(m_blocks) * ceil_div_u32(N, 128);
+    if (tiles128 * k_blocks < 4ull * sms) pl->bn = 64;
+    pl->parts = 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// launch
+// ------------------------------------------------------------------------------------------
+template <int BN, int STAGES, int CG, int MODE>
+static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
+    using T = KernelTraits<BN, STAGES, CG>;
+    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE>;
+    if (!st.attr_set[attr_slot]) {
+        std::lock_guard<std::mutex> lock(st.mu);
+        if (!st.attr_set[attr_slot]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) != cudaSuccess) {
+                return B200_HGEMM_ERR_CUDA;
+            }
+            st.attr_set[attr_slot] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = T::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    int n_attrs = 0;
+    if (CG == 2) {
+        attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[n_attrs].val.clusterDim.x = 2;
+        attrs[n_attrs].val.clusterDim.y = 1;
+        attrs[n_attrs].val.clusterDim.z = 1;
+        ++n_attrs;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n_attrs;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_HGEMM_OK;
+}
+
+static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, size_t K, const b200_hgemm_plan &pl) {
+    if (pl.variant != B200_VARIANT_STREAMK) return 0;
+    const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, pl.bn);
+    const uint32_t parts = streamk_parts(pl, st, tiles, ceil_div_u32(K, 64));
+    return kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * pl.bn * sizeof(float));
+}
+
+static int ensure_workspace(DeviceState &st, size_t need) {
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (st.ws && st.ws_bytes >= need) return B200_HGEMM_OK;
+    if (st.ws && !st.ws_owned) return B200_HGEMM_ERR_WORKSPACE;  // caller-provided and too small
+    if (need > kMaxOwnedWorkspace) return B200_HGEMM_ERR_WORKSPACE;
+    if (st.ws) {
+        if (cudaFree(st.ws) != cudaSuccess) return B200_HGEMM_ERR_CUDA;  // synchronises the device
+        st.ws = nullptr;
+        st.ws_bytes = 0;
+    }
+    size_t bytes = need < (size_t(32) << 20) ? (size_t(32) << 20) : need;
+    if (cudaMalloc(&st.ws, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_WORKSPACE;
+    }
+    if (cudaMemset(st.ws, 0, kCounterBytes) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    st.ws_bytes = bytes;
+    st.ws_owned = true;
+    return B200_HGEMM_OK;
+}
+
+// Any-shape CUDA-core kernel: one thread per C element, FP32 accumulate.
+__global__ void hgemm_simt_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ c,
+                                  size_t m, size_t n, size_t k) {
+    const size_t col = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const size_t row = blockIdx.y * static_cast<size_t>(blockDim.y) + threadIdx.y;
+    if (row >= m || col >= n) return;
+    const __half *ar = a + row * k;
+    const __half *br = b + col * k;
+    float acc = 0.f;
+    for (size_t i = 0; i < k; ++i) acc = fmaf(__half2float(ar[i]), __half2float(br[i]), acc);
+    c[row * n + col] = __float2half_rn(acc);
+}
+
+static int run_simt(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, cudaStream_t stream) {
+    dim3 block(32, 8);
+    dim3 grid(static_cast<unsigned>((N + block.x - 1) / block.x), static_cast<unsigned>((M + block.y - 1) / block.y));
+    if (grid.y > 65535u) return B200_HGEMM_ERR_UNSUPPORTED;
+    hgemm_simt_kernel<<<grid, block, 0, stream>>>(static_cast<const __half *>(A), static_cast<const __half *>(B),
+                                                  static_cast<__half *>(C), M, N, K);
+    if (cudaGetLastError() != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_HGEMM_OK;
+}
+
+static int check_args(const void *A, const void *B, const void *C, size_t M, size_t N, size_t K) {
+    if (!A || !B || !C || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return B200_HGEMM_ERR_UNSUPPORTED;
+    return B200_HGEMM_OK;
+}
+
+static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+                    const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes) {
+    int rc = validate_plan(pl, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (pl.variant == B200_VARIANT_SIMT) return run_simt(A, B, C, M, N, K, stream);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u) {
+        return B200_HGEMM_ERR_MISALIGNED;
+    }
+    const int cg = (pl.variant == B200_VARIANT_CTA2) ? 2 : 1;
+    const int bn = pl.bn;
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.c = static_cast<__half *>(C);
+    p.error_word = st.error_word;
+    p.m = static_cast<uint32_t>(M);
+    p.n = static_cast<uint32_t>(N);
+    p.k = static_cast<uint32_t>(K);
+    p.m_blocks = ceil_div_u32(M, 128u * cg);
+    p.n_blocks = ceil_div_u32(N, bn);
+    p.k_blocks = ceil_div_u32(K, 64);
+    const uint64_t tiles64 = static_cast<uint64_t>(p.m_blocks) * p.n_blocks;
+    if (tiles64 > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
+    p.tiles = static_cast<uint32_t>(tiles64);
+    p.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : (cg == 2 ? 8u : 16u);
+    if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
+    p.tma_store = pl.tma_store ? 1u : 0u;
+    p.c_vec_ok = (N % 8 == 0) ? 1u : 0u;
+
+    rc = get_tensor_map(st, A, M, K, 128, 64, &p.tm_a);
+    if (rc != B200_HGEMM_OK) return rc;
+    rc = get_tensor_map(st, B, N, K, static_cast<uint32_t>(bn / cg), 64, &p.tm_b);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (p.tma_store) {
+        rc = get_tensor_map(st, C, M, N, 32, 64, &p.tm_c);
+        if (rc != B200_HGEMM_OK) return rc;
+    }
+
+    uint32_t grid = 0;
+    if (pl.variant == B200_VARIANT_STREAMK) {
+        if (p.tiles > kMaxCountedTiles) return B200_HGEMM_ERR_UNSUPPORTED;
+        const uint32_t parts = streamk_parts(pl, st, p.tiles, p.k_blocks);
+        const size_t need = kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * bn * sizeof(float));
+        uint8_t *ws = nullptr;
+        if (ws_override) {
+            if (ws_override_bytes < need) return B200_HGEMM_ERR_WORKSPACE;
+            ws = static_cast<uint8_t *>(ws_override);
+        } else {
+            rc = ensure_workspace(st, need);
+            if (rc != B200_HGEMM_OK) return rc;
+            ws = static_cast<uint8_t *>(st.ws);
+        }
+        p.tile_counters = reinterpret_cast<uint32_t *>(ws);
+        p.partials = reinterpret_cast<float4 *>(ws + kCounterBytes);
+        grid = parts;
+    } else {
+        const uint32_t max_workers = (cg == 2) ? static_cast<uint32_t>(st.sm_count / 2) : static_cast<uint32_t>(st.sm_count);
+        uint32_t workers = pl.grid > 0 ? static_cast<uint32_t>(pl.grid) / cg : max_workers;
+        if (workers > p.tiles) workers = p.tiles;
+        if (workers < 1) workers = 1;
+        grid = workers * cg;
+    }
+
+    if (pl.variant == B200_VARIANT_CTA1) {
+        if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles>(st, 0, p, grid, stream);
+        if (bn == 128) return launch_kernel<128, 6, 1, kModeTiles>(st, 1, p, grid, stream);
+        return launch_kernel<64, 8, 1, kModeTiles>(st, 2, p, grid, stream);
+    }
+    if (pl.variant == B200_VARIANT_CTA2) {
+        if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
+        return launch_kernel<128, 8, 2, kModeTiles>(st, 4, p, grid, stream);
+    }
+    if (bn == 256) return launch_kernel<256, 4, 1, kModeStreamK>(st, 5, p, grid, stream);
+    if (bn == 128) return launch_kernel<128, 6, 1, kModeStreamK>(st, 6, p, grid, stream);
+    return launch_kernel<64, 8, 1, kModeStreamK>(st, 7, p, grid, stream);
+}
+
+static int entry(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_plan *fixed,
+                 int force_variant, cudaStream_t stream) {
+    int rc = check_args(A, B, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    b200_hgemm_plan pl;
+    if (fixed) {
+        pl = *fixed;
+    } else {
+        select_plan(*st, M, N, K, &pl);
+        if (force_variant >= 0 && pl.variant != B200_VARIANT_SIMT) {
+            if (force_variant == B200_VARIANT_SIMT) {
+                pl.variant = B200_VARIANT_SIMT;
+            } else if (force_variant == B200_VARIANT_CTA1) {
+                if (pl.variant != B200_VARIANT_CTA1) pl.bn = 256;
+                pl.variant = B200_VARIANT_CTA1;
+                pl.parts = 0;
+            } else if (force_variant == B200_VARIANT_CTA2) {
+                pl.variant = B200_VARIANT_CTA2;
+                pl.bn = 256;
+                pl.parts = 0;
+            } else if (force_variant == B200_VARIANT_STREAMK) {
+                if (pl.variant != B200_VARIANT_STREAMK) pl.bn = 128;
+                pl.variant = B200_VARIANT_STREAMK;
+                pl.parts = 0;
+            }
+        } else if (force_variant == B200_VARIANT_SIMT) {
+            pl.variant = B200_VARIANT_SIMT;
+        }
+    }
+    return run_plan(*st, A, B, C, M, N, K, pl, stream, nullptr, 0);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// ------------------------------------------------------------------------------------------
+// extern "C"
+// ------------------------------------------------------------------------------------------
+extern "C" {
+
+int b200_hgemm(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    return entry(A, B, C, M, N, K, nullptr, -1, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200_hgemm_cta1(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    return entry(A, B, C, M, N, K, nullptr, B200_VARIANT_CTA1, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200_hgemm_cta2(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    return entry(A, B, C, M, N, K, nullptr, B200_VARIANT_CTA2, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200_hgemm_streamk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    return entry(A, B, C, M, N, K, nullptr, B200_VARIANT_STREAMK, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Split-k with a fixed number of k-slices per tile: the stream-k kernel launched with
+// tiles x slices equal ranges, so that every CTA owns exactly one slice of one tile.
+int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    int rc = check_args(A, B, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    b200_hgemm_plan pl;
+    select_plan(*st, M, N, K, &pl);
+    if (pl.variant != B200_VARIANT_SIMT) {
+        pl.variant = B200_VARIANT_STREAMK;
+        pl.bn = 128;
+        const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, 128);
+        const uint32_t k_blocks = ceil_div_u32(K, 64);
+        uint32_t slices = (static_cast<uint32_t>(st->sm_count) + tiles - 1) / tiles;
+        if (slices < 2) slices = 2;
+        while (slices > 1 && k_blocks % slices != 0) --slices;  // equal slices only
+        if (slices > k_blocks) slices = k_blocks;
+        pl.parts = static_cast<int32_t>(tiles * slices);
+    }
+    return run_plan(*st, A, B, C, M, N, K, pl, reinterpret_cast<cudaStream_t>(stream), nullptr, 0);
+}
+
+int b200_hgemm_simt(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    return entry(A, B, C, M, N, K, nullptr, B200_VARIANT_SIMT, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_plan *plan,
+                  b200_stream_t stream) {
+    if (!plan) return B200_HGEMM_ERR_INVALID_ARG;
+    return entry(A, B, C, M, N, K, plan, -1, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {
+    if (!plan || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceState *st = nullptr;
+    int rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) {
+        // no usable device: still answer, for a nominal 148-SM part, so that planning can be tested on the host
+        cudaGetLastError();
+        static DeviceState nominal;
+        nominal.sm_count = 148;
+        select_plan(nominal, M, N, K, plan);
+        return B200_HGEMM_OK;
+    }
+    select_plan(*st, M, N, K, plan);
+    return B200_HGEMM_OK;
+}
+
+size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan) {
+    if (!plan || M == 0 || N == 0 || K == 0) return 0;
+    if (plan->variant != B200_VARIANT_STREAMK) return 0;
+    if (plan->bn != 64 && plan->bn != 128 && plan->bn != 256) return 0;
+    DeviceState *st = nullptr;
+    if (current_state(&st) != B200_HGEMM_OK) {
+        cudaGetLastError();
+        static DeviceState nominal;
+        nominal.sm_count = 148;
+        return plan_workspace_bytes(nominal, M, N, K, *plan);
+    }
+    return plan_workspace_bytes(*st, M, N, K, *plan);
+}
+
+int b200_hgemm_set_workspace(void *workspace, size_t bytes) {
+    DeviceState *st = nullptr;
+    int rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (workspace && ((reinterpret_cast<uintptr_t>(workspace) & 255u) || bytes < kCounterBytes)) {
+        return B200_HGEMM_ERR_WORKSPACE;
+    }
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (st->ws && st->ws_owned) {
+        if (cudaFree(st->ws) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    }
+    st->ws = workspace;
+    st->ws_bytes = workspace ? bytes : 0;
+    st->ws_owned = false;
+    return B200_HGEMM_OK;
+}
+
+int b200_hgemm_last_device_error(void) {
+    DeviceState *st = nullptr;
+    int rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    if (cudaDeviceSynchronize() != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    uint32_t word = 0;
+    if (cudaMemcpy(&word, st->error_word, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        return B200_HGEMM_ERR_CUDA;
+    }
+    if (word != 0) {
+        cudaMemset(st->error_word, 0, sizeof(word));
+        // a kernel that gave up may have left tile counters half-counted
+        std::lock_guard<std::mutex> lock(st->mu);
+        if (st->ws) cudaMemset(st->ws, 0, kCounterBytes);
+    }
+    return static_cast<int>(word);
+}
+
+const char *b200_hgemm_status_string(int status) {
+    switch (status) {
+        case B200_HGEMM_OK: return "ok";
+        case B200_HGEMM_ERR_INVALID_ARG: return "invalid argument (null pointer or zero dimension)";
+        case B200_HGEMM_ERR_UNSUPPORTED: return "unsupported shape or plan";
+        case B200_HGEMM_ERR_MISALIGNED: return "pointer not 16-byte aligned";
+        case B200_HGEMM_ERR_NO_SM100: return "current device is not an sm_100 GPU (no fallback exists)";
+        case B200_HGEMM_ERR_CUDA: return "CUDA call failed";
+        case B200_HGEMM_ERR_WORKSPACE: return "split-k workspace missing or too small";
+        case B200_HGEMM_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
+        case B200_HGEMM_ERR_TOO_LARGE: return "size beyond the entry point's stated maximum";
+        default: return "unknown status";
+    }
+}
+
+const char *b200_hgemm_version(void) {
+    return "b200_hgemm 0.1 (sm_100a, tcgen05/TMEM/TMA)";
+}
+
+uint64_t b200_hgemm_launch_count(void) {
+    return g_launches.load(std::memory_order_relaxed);
+}
+
+// ---- host-pointer entry point -----------------------------------------------------------
+static int grow(void **ptr, size_t *have, size_t need) {
+    if (*have >= need) return B200_HGEMM_OK;
+    if (*ptr) {
+        if (cudaFree(*ptr) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+        *ptr = nullptr;
+        *have = 0;
+    }
+    if (cudaMalloc(ptr, need) != cudaSuccess) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_CUDA;
+    }
+    *have = need;
+    return B200_HGEMM_OK;
+}
+
+int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t M, size_t N, size_t K) {
+    int rc = check_args(A_host, B_host, C_host, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    const size_t a_bytes = M * K * sizeof(__half), b_bytes = N * K * sizeof(__half), c_bytes = M * N * sizeof(__half);
+    {
+        std::lock_guard<std::mutex> lock(st->mu);
+        if ((rc = grow(&st->host_a, &st->host_a_bytes, a_bytes)) != B200_HGEMM_OK) return rc;
+        if ((rc = grow(&st->host_b, &st->host_b_bytes, b_bytes)) != B200_HGEMM_OK) return rc;
+        if ((rc = grow(&st->host_c, &st->host_c_bytes, c_bytes)) != B200_HGEMM_OK) return rc;
+        for (int i = 0; i < 2; ++i) {
+            if (!st->host_stream[i] && cudaStreamCreateWithFlags(&st->host_stream[i], cudaStreamNonBlocking) != cudaSuccess)
+                return B200_HGEMM_ERR_CUDA;
+            if (!st->host_event[i] && cudaEventCreateWithFlags(&st->host_event[i], cudaEventDisableTiming) != cudaSuccess)
+                return B200_HGEMM_ERR_CUDA;
+        }
+    }
+    // B first (every row slab needs all of it), then A and C move in row slabs so that the
+    // upload of slab i+1 and the download of slab i-1 overlap the GEMM of slab i.
+    cudaStream_t s_up = st->host_stream[0], s_run = st->host_stream[1];
+    if (cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    size_t slabs = 1;
+    if (M >= 2048 && M % 128 == 0) {
+        slabs = 4;
+        while (slabs > 1 && (M / 128) % slabs != 0) --slabs;
+    }
+    const size_t rows = M / slabs;
+    for (size_t s = 0; s < slabs; ++s) {
+        const char *a_src = static_cast<const char *>(A_host) + s * rows * K * sizeof(__half);
+        char *a_dst = static_cast<char *>(st->host_a) + s * rows * K * sizeof(__half);
+        char *c_dev = static_cast<char *>(st->host_c) + s * rows * N * sizeof(__half);
+        char *c_dst = static_cast<char *>(C_host) + s * rows * N * sizeof(__half);
+        if (cudaMemcpyAsync(a_dst, a_src, rows * K * sizeof(__half), cudaMemcpyHostToDevice, s_up) != cudaSuccess)
+            return B200_HGEMM_ERR_CUDA;
+        if (cudaEventRecord(st->host_event[0], s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+        if (cudaStreamWaitEvent(s_run, st->host_event[0], 0) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+        rc = entry(a_dst, st->host_b, c_dev, rows, N, K, nullptr, -1, s_run);
+        if (rc != B200_HGEMM_OK) return rc;
+        if (cudaMemcpyAsync(c_dst, c_dev, rows * N * sizeof(__half), cudaMemcpyDeviceToHost, s_run) != cudaSuccess)
+            return B200_HGEMM_ERR_CUDA;
+    }
+    if (cudaStreamSynchronize(s_run) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (cudaStreamSynchronize(s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    return B200_HGEMM_OK;
+}
+
+// ---- host-side helpers for tests --------------------------------------------------------
+void b200_sched_tile_coord(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
+                           uint32_t *n_blk) {
+    TileCoord c = tile_coord(tile, m_blocks, n_blocks, group_m);
+    *m_blk = c.m_blk;
+    *n_blk = c.n_blk;
+}
+
+uint32_t b200_sched_segments(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *out,
+                             uint32_t cap) {
+    SegmentWalker w(part, parts, tiles, k_blocks);
+    Segment s;
+    uint32_t n = 0;
+    while (w.next(s)) {
+        if (n < cap) {
+            out[3 * n + 0] = s.tile;
+            out[3 * n + 1] = s.kb0;
+            out[3 * n + 2] = s.kb1;
+        }
+        ++n;
+    }
+    return n;
+}
+
+void b200_sched_contributors(uint32_t tile, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *first,
+                             uint32_t *last) {
+    const uint64_t total = static_cast<uint64_t>(tiles) * k_blocks;
+    const uint64_t u0 = static_cast<uint64_t>(tile) * k_blocks;
+    *first = part_of_unit(u0, parts, total);
+    *last = part_of_unit(u0 + k_blocks - 1, parts, total);
+}
+
+uint32_t b200_sched_partial_slot(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t tile) {
+    return partial_slot(part, parts, tiles, k_blocks, tile);
+}
+
+uint32_t b200_debug_idesc(uint32_t m, uint32_t n) {
+    return umma_idesc_f16_f32(m, n);
+}
+
+uint64_t b200_debug_smem_desc(uint32_t smem_addr) {
+    return umma_smem_desc_sw128(smem_addr);
+}
+
+}  // extern "C"

@@ -1,0 +1,96 @@
+// Work decomposition shared by host code and the kernels: tile rasterisation for L2 reuse,
+// and the contiguous unit ranges ("stream-K") that let every SM get an equal share of
+// k-blocks when the tile count does not fill the GPU.
+//
+// The reference maps blocks to tiles in 16-wide serpentine super-columns
+// (src/mma/mma_async_stage4.cu:60-62); the grouped order below is the same idea with the
+// group running along M and a width chosen per shape.
+#pragma once
+
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define B200_HD __host__ __device__ __forceinline__
+#else
+#define B200_HD inline
+#endif
+
+namespace b200 {
+
+struct TileCoord {
+    uint32_t m_blk;
+    uint32_t n_blk;
+};
+
+// Linear tile id -> (m_blk, n_blk). Tiles are walked in bands of `group_m` row blocks; inside
+// a band the row block moves fastest, and odd bands walk the columns backwards so the column
+// tiles at a band boundary are still in L2.
+B200_HD TileCoord tile_coord(uint32_t t, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m) {
+    const uint32_t per_band = group_m * n_blocks;
+    const uint32_t band = t / per_band;
+    const uint32_t first_m = band * group_m;
+    const uint32_t rows_here = (m_blocks - first_m < group_m) ? (m_blocks - first_m) : group_m;
+    const uint32_t r = t - band * per_band;
+    TileCoord c;
+    c.m_blk = first_m + r % rows_here;
+    uint32_t n = r / rows_here;
+    c.n_blk = (band & 1u) ? (n_blocks - 1u - n) : n;
+    return c;
+}
+
+// One contiguous piece of work: k-blocks [kb0, kb1) of output tile `tile`.
+struct Segment {
+    uint32_t tile;
+    uint32_t kb0;
+    uint32_t kb1;
+};
+
+// Stream-K: the `tiles * k_blocks` units (tile-major, k-minor) are cut into `parts` equal
+// contiguous ranges; part p owns units [unit_begin(p), unit_begin(p+1)).
+B200_HD uint64_t unit_begin(uint32_t part, uint32_t parts, uint64_t total_units) {
+    return (static_cast<uint64_t>(part) * total_units) / parts;
+}
+
+// The part whose range contains unit u (largest p with unit_begin(p) <= u).
+B200_HD uint32_t part_of_unit(uint64_t u, uint32_t parts, uint64_t total_units) {
+    // unit_begin(p) <= u  <=>  p * total < (u + 1) * parts  <=>  p <= ceil((u+1)*parts/total) - 1
+    uint64_t p = ((u + 1) * parts + total_units - 1) / total_units - 1;
+    return static_cast<uint32_t>(p);
+}
+
+// Iterates the segments of one part in order.
+struct SegmentWalker {
+    uint64_t cur;
+    uint64_t end;
+    uint32_t k_blocks;
+
+    B200_HD SegmentWalker(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks_) {
+        const uint64_t total = static_cast<uint64_t>(tiles) * k_blocks_;
+        cur = unit_begin(part, parts, total);
+        end = unit_begin(part + 1, parts, total);
+        k_blocks = k_blocks_;
+    }
+
+    B200_HD bool next(Segment &s) {
+        if (cur >= end) return false;
+        const uint32_t tile = static_cast<uint32_t>(cur / k_blocks);
+        const uint32_t kb0 = static_cast<uint32_t>(cur - static_cast<uint64_t>(tile) * k_blocks);
+        const uint64_t tile_end = (static_cast<uint64_t>(tile) + 1) * k_blocks;
+        const uint64_t stop = tile_end < end ? tile_end : end;
+        s.tile = tile;
+        s.kb0 = kb0;
+        s.kb1 = kb0 + static_cast<uint32_t>(stop - cur);
+        cur = stop;
+        return true;
+    }
+};
+
+// Workspace slot a part writes its partial tile to: slot 0 for the first tile its range
+// touches, slot 1 for any other (only the last tile of a range can also be partial).
+B200_HD uint32_t partial_slot(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t tile) {
+    const uint64_t total = static_cast<uint64_t>(tiles) * k_blocks;
+    const uint32_t first_tile = static_cast<uint32_t>(unit_begin(part, parts, total) / k_blocks);
+    return 2u * part + (tile == first_tile ? 0u : 1u);
+}
+
+}  // namespace b200

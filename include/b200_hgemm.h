@@ -1,0 +1,137 @@
+/*
+ * b200_hgemm -- C ABI of the sm_100a half-precision GEMM library.
+ *
+ *   C[M x N] = A[M x K] * B      FP16 in, FP32 accumulate (tensor memory), FP16 out
+ *
+ * Operand layouts are those of the cuda_hgemm entry points
+ * `void kernel(half *A, half *B, half *C, size_t M, size_t N, size_t K)` (reference
+ * src/main.cu:11-33; layouts src/common/tester.h:117-119):
+ *   A  row-major, M rows of K contiguous halves            (lda = K)
+ *   B  "col-major K x N": N rows of K contiguous halves    (ldb = K), element (k, n) at B[n*K + k]
+ *   C  row-major, M rows of N contiguous halves            (ldc = N), fully overwritten (beta = 0)
+ * alpha = 1, beta = 0, no batching and no strides, exactly like the reference kernels.
+ *
+ * All pointers are DEVICE pointers unless a function says otherwise. Calls are asynchronous
+ * on `stream` and never synchronise; they may be issued back to back on one stream.
+ * There is no CPU fallback and no alternate backend: on a device that is not sm_100 every
+ * compute entry point returns B200_HGEMM_ERR_NO_SM100.
+ *
+ * Preconditions (checked, reported by return code): A, B, C 16-byte aligned; K % 8 == 0;
+ * M, N, K >= 1. Tails in M, N and K (to a multiple of 8) are handled inside the kernels.
+ */
+#ifndef B200_HGEMM_H_
+#define B200_HGEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same type as cudaStream_t / CUstream; spelled out so that C callers need no CUDA headers. */
+typedef struct CUstream_st *b200_stream_t;
+
+enum {
+    B200_HGEMM_OK = 0,
+    B200_HGEMM_ERR_INVALID_ARG = -1,  /* null pointer or zero dimension */
+    B200_HGEMM_ERR_UNSUPPORTED = -2,  /* shape or plan outside what the kernels implement */
+    B200_HGEMM_ERR_MISALIGNED = -3,   /* pointer not 16-byte aligned */
+    B200_HGEMM_ERR_NO_SM100 = -4,     /* current device is not compute capability 10.x */
+    B200_HGEMM_ERR_CUDA = -5,         /* a CUDA runtime / driver call failed */
+    B200_HGEMM_ERR_WORKSPACE = -6,    /* split-k workspace missing or too small */
+    B200_HGEMM_ERR_DEVICE_WAIT = -7,  /* a kernel gave up on a bounded wait (see last_device_error) */
+    B200_HGEMM_ERR_TOO_LARGE = -8     /* size beyond a stated maximum of the entry point */
+};
+
+/* Kernel family a plan selects. */
+enum {
+    B200_VARIANT_CTA1 = 0,    /* tcgen05.mma cta_group::1, whole tiles, persistent */
+    B200_VARIANT_CTA2 = 1,    /* tcgen05.mma cta_group::2 (CTA pair on a 256-row tile) */
+    B200_VARIANT_STREAMK = 2, /* cta_group::1, k-ranges split across CTAs, FP32 workspace reduce */
+    B200_VARIANT_SIMT = 3     /* CUDA-core kernel for shapes the tensor path rejects (K % 8 != 0) */
+};
+
+/* The dispatch decision for one shape. All fields are filled by b200_hgemm_select(); a
+ * caller may edit them and pass the plan to b200_hgemm_ex(). */
+typedef struct b200_hgemm_plan {
+    int32_t variant;   /* B200_VARIANT_* */
+    int32_t bn;        /* tile width in N: 64, 128 or 256 (tile height is 128, or 256 per CTA pair) */
+    int32_t parts;     /* STREAMK: number of equal k-ranges = CTAs launched; 0 = one per SM */
+    int32_t group_m;   /* rasterisation band height in row blocks; 0 = library default */
+    int32_t tma_store; /* 1: epilogue writes C with TMA stores (needs N % 8 == 0); 0: plain stores */
+    int32_t grid;      /* CTA1/CTA2: CTAs launched (0 = min(tiles, SMs)); informational for STREAMK */
+} b200_hgemm_plan;
+
+/* ---- compute entry points: each replaces one reference HGEMM_FUNC symbol ----------------
+ * Reference interface replaced: src/main.cu:11 `HGEMM_FUNC(name)` and its 19 instances
+ * (src/main.cu:13-33), called from src/common/tester.h:61 and :93. */
+
+/* Auto-dispatching GEMM: picks a plan with b200_hgemm_select() and runs it.
+ * Replaces the role of the reference's best kernel, mmaAsyncStage4 (src/mma/mma_async_stage4.cu:637-644). */
+int b200_hgemm(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+
+/* Fixed-variant entry points (log names B200-Tcgen05-1Cta / -2Cta / -SplitK / -StreamK); they
+ * stand where the reference registers one symbol per kernel variant (src/main.cu:106-123). */
+int b200_hgemm_cta1(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+int b200_hgemm_cta2(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+int b200_hgemm_streamk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+
+/* Any-shape CUDA-core kernel with FP32 accumulation: the counterpart of the reference's
+ * simtNaive (src/simt_naive.cu:9-32), with the bounds guard corrected. */
+int b200_hgemm_simt(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+
+/* Run an explicit plan. */
+int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_plan *plan,
+                  b200_stream_t stream);
+
+/* HOST-pointer GEMM: copies A and B to the device, runs b200_hgemm, copies C back and
+ * synchronises. This is the path of reference Matrix (src/common/matrix.h:23-35 upload,
+ * :83-85 moveToHost) + one kernel call, behind one entry point. Returns after C_host is complete. */
+int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t M, size_t N, size_t K);
+
+/* ---- planning, workspace, status ------------------------------------------------------- */
+
+/* Fills *plan with the library's choice for (M, N, K) on the current device. */
+int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan);
+
+/* Bytes of device workspace `plan` needs for this shape (0 for whole-tile variants). */
+size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan);
+
+/* Hands the library a caller-owned, zero-initialised device workspace for the current device
+ * (256-byte aligned). With no workspace set the library allocates and grows its own on
+ * first need (cudaMalloc outside any stream capture). Pass (NULL, 0) to go back to that. */
+int b200_hgemm_set_workspace(void *workspace, size_t bytes);
+
+/* Synchronises the current device and returns the device-side error word (0 = none,
+ * 1 = a bounded wait expired), clearing it. */
+int b200_hgemm_last_device_error(void);
+
+const char *b200_hgemm_status_string(int status);
+const char *b200_hgemm_version(void);
+
+/* Number of kernels this library has launched in this process (for launch accounting). */
+uint64_t b200_hgemm_launch_count(void);
+
+/* ---- host-side helpers exposed for tests (no GPU needed) -------------------------------- */
+
+/* Tile rasterisation: linear tile id -> (m_blk, n_blk). */
+void b200_sched_tile_coord(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
+                           uint32_t *n_blk);
+/* Stream-K: writes up to `cap` segments {tile, kb0, kb1} of part `part` to out[3*i..]; returns the count. */
+uint32_t b200_sched_segments(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *out,
+                             uint32_t cap);
+/* Stream-K: first and last part contributing to `tile`, and the workspace slot of (part, tile). */
+void b200_sched_contributors(uint32_t tile, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *first,
+                             uint32_t *last);
+uint32_t b200_sched_partial_slot(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t tile);
+/* tcgen05 descriptor encoders (instruction descriptor; shared-memory matrix descriptor). */
+uint32_t b200_debug_idesc(uint32_t m, uint32_t n);
+uint64_t b200_debug_smem_desc(uint32_t smem_addr);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_HGEMM_H_ */

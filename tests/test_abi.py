@@ -1,0 +1,99 @@
+"""The C-ABI library loads and exports every symbol include/b200_hgemm.h declares; argument
+checking answers before any device is touched. CPU only: no compute call is made."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from cuda_hgemm_b200 import _native
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "b200_hgemm.h"
+
+
+def declared_functions():
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    assert declared_functions() == sorted(_native.EXPORTED_SYMBOLS)
+
+
+def test_every_declared_symbol_is_exported(native_lib):
+    for name in declared_functions():
+        assert hasattr(native_lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_version_and_status_strings(native_lib):
+    assert b"sm_100a" in native_lib.b200_hgemm_version()
+    seen = set()
+    for code in (0, -1, -2, -3, -4, -5, -6, -7, -8):
+        s = native_lib.b200_hgemm_status_string(code)
+        assert s and s not in seen
+        seen.add(s)
+    assert native_lib.b200_hgemm_status_string(-99) == b"unknown status"
+
+
+def test_argument_errors_come_before_any_device_work(native_lib):
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    for fn in (native_lib.b200_hgemm, native_lib.b200_hgemm_cta1, native_lib.b200_hgemm_cta2,
+               native_lib.b200_hgemm_splitk, native_lib.b200_hgemm_streamk, native_lib.b200_hgemm_simt):
+        assert fn(None, p, p, 8, 8, 8, None) == _native.ERR_INVALID_ARG
+        assert fn(p, p, p, 0, 8, 8, None) == _native.ERR_INVALID_ARG
+        assert fn(p, p, p, 8, 8, 0, None) == _native.ERR_INVALID_ARG
+    assert native_lib.b200_hgemm_ex(p, p, p, 8, 8, 8, None, None) == _native.ERR_INVALID_ARG
+    assert native_lib.b200_hgemm_host(None, p, p, 8, 8, 8) == _native.ERR_INVALID_ARG
+
+
+def test_no_silent_fallback_without_a_gpu(native_lib):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; the no-device answer cannot be observed")
+    buf = ctypes.create_string_buffer(4096)
+    p = (ctypes.addressof(buf) + 15) & ~15
+    # valid arguments, no device: the call must fail loudly, never compute on the host
+    assert native_lib.b200_hgemm(p, p, p, 8, 8, 8, None) in (_native.ERR_CUDA, _native.ERR_NO_SM100)
+    with pytest.raises(_native.HgemmError):
+        _native.check(native_lib.b200_hgemm(p, p, p, 8, 8, 8, None))
+
+
+def test_missing_library_raises(monkeypatch, tmp_path):
+    monkeypatch.setattr(_native, "_lib", None)
+    monkeypatch.setattr(_native, "LIB_PATH", tmp_path / "absent.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _native.load()
+
+
+def test_descriptor_encoders(native_lib):
+    # instruction descriptor: D=F32 (bit 4), A/B=F16 K-major (zeros), N>>3 at bit 17, M>>4 at bit 24
+    assert native_lib.b200_debug_idesc(128, 256) == (1 << 4) | (32 << 17) | (8 << 24)
+    assert native_lib.b200_debug_idesc(256, 256) == (1 << 4) | (32 << 17) | (16 << 24)
+    assert native_lib.b200_debug_idesc(128, 64) == (1 << 4) | (8 << 17) | (8 << 24)
+    # shared-memory descriptor: addr>>4 | LBO 1 | SBO 1024>>4 | version 1 | 128-byte swizzle (2)
+    d = native_lib.b200_debug_smem_desc(0x12400)
+    assert d & 0x3FFF == 0x12400 >> 4
+    assert (d >> 16) & 0x3FFF == 1
+    assert (d >> 32) & 0x3FFF == 64
+    assert (d >> 46) & 0x3 == 1
+    assert (d >> 61) & 0x7 == 2
+    # stepping 16 halves (32 bytes) along K adds 2 to the address field
+    assert native_lib.b200_debug_smem_desc(0x12400 + 32) - d == 2
+
+
+def test_plan_selection_covers_the_benchmark_shapes(native_lib):
+    from cuda_hgemm_b200 import api
+
+    big = api.select_plan(8192, 8192, 8192)
+    assert big.variant in (_native.VARIANT_CTA1, _native.VARIANT_CTA2) and big.bn == 256
+    skinny = api.select_plan(16, 14336, 4096)
+    assert skinny.variant == _native.VARIANT_STREAMK
+    assert api.workspace_bytes(16, 14336, 4096, skinny) > 0
+    assert api.workspace_bytes(8192, 8192, 8192, big) == 0
+    odd = api.select_plan(48, 40, 100)
+    assert odd.variant == _native.VARIANT_SIMT  # K % 8 != 0: no TMA row pitch
+    ragged_n = api.select_plan(512, 1001, 512)
+    assert ragged_n.tma_store == 0

@@ -1,0 +1,258 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI, on a B200.
+
+Tolerance (stated by the task this library is built to): max-norm relative error <= 1e-2 on the
+FP16 output against the FP32-accumulate product of the same seeded inputs; ``assert_close_to_oracle``
+additionally holds the kernels to 2e-3, what FP32 accumulation with one rounding should reach.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from cuda_hgemm_b200 import _native, api
+from oracle import hgemm_oracle as oracle
+from tests.helpers import assert_close_to_oracle, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+POISON = 0x7E00  # FP16 NaN: an element the kernel never wrote stays non-finite
+
+
+def to_dev(x, device):
+    import torch
+
+    return torch.from_numpy(x).to(device)
+
+
+def poisoned(M, N, device, extra_rows=0):
+    import torch
+
+    c = torch.full(((M + extra_rows) * N,), POISON, dtype=torch.int16, device=device).view(torch.float16)
+    return c
+
+
+def run(fn, A, B, device, plan=None):
+    """Runs one entry point on poisoned C with canary rows behind it; returns C as numpy."""
+    import torch
+
+    M, K = A.shape
+    N = B.shape[0]
+    dA, dB = to_dev(A, device), to_dev(B, device)
+    flat = poisoned(M, N, device, extra_rows=4)
+    C = flat[: M * N].view(M, N)
+    if plan is not None:
+        api.hgemm_ex(dA, dB, C, plan)
+    else:
+        fn(dA, dB, C)
+    torch.cuda.synchronize(device)
+    assert api.last_device_error() == 0
+    canary = flat[M * N:].view(torch.int16).cpu().numpy()
+    assert (canary == POISON).all(), "kernel wrote past the end of C"
+    return C.cpu().numpy()
+
+
+def plan_of(variant, bn, parts=0, tma_store=1, group_m=0, grid=0):
+    p = _native.Plan()
+    p.variant, p.bn, p.parts, p.tma_store, p.group_m, p.grid = variant, bn, parts, tma_store, group_m, grid
+    return p
+
+
+SMALL_SHAPES = [
+    (128, 256, 64),     # one tile, one k-block
+    (128, 256, 256),    # one tile, ring of 4 stages exactly once
+    (256, 256, 256),    # configuration 1 of the benchmark
+    (384, 512, 320),    # 5 k-blocks: not a multiple of any stage count
+    (512, 2048, 1024),  # the reference driver's default shape (reference src/main.cu:35-37)
+    (200, 264, 136),    # tails in M, N and K
+    (8, 8, 8),          # smaller than every tile dimension
+    (1024, 1024, 1024),
+]
+
+
+@pytest.mark.parametrize("shape", SMALL_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_auto_dispatch_matches_oracle(cuda_device, shape):
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=2023)
+    C = run(api.b200Hgemm, A, B, cuda_device)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"auto {shape}")
+
+
+@pytest.mark.parametrize("tma_store", [0, 1])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (384, 512, 320), (200, 264, 136), (1024, 1536, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_single_cta_tiles(cuda_device, shape, bn, tma_store):
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=1)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA1, bn, tma_store=tma_store))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta1 bn={bn} tma_store={tma_store} {shape}")
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (256, 512, 320), (512, 2048, 1024), (328, 264, 136), (2048, 2048, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_cta_pair_tiles(cuda_device, shape, bn):
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=2)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2, bn))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta2 bn={bn} {shape}")
+
+
+@pytest.mark.parametrize("parts", [0, 1, 7, 33, 148, 400])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_stream_k_ranges(cuda_device, bn, parts):
+    M, N, K = 200, 1032, 1096  # tails everywhere; 18 k-blocks
+    A, B = make_inputs(M, N, K, seed=3)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_STREAMK, bn, parts=parts))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"stream-k bn={bn} parts={parts}")
+
+
+@pytest.mark.parametrize("M", [16, 32, 64, 128])
+def test_skinny_decode_shapes(cuda_device, M):
+    # decode-like: activations ~ N(0,1), weights ~ N(0, 1/K); N and K scaled down 4x from 14336 x 4096
+    for N, K in ((3584, 1024), (1024, 3584)):
+        A, B = make_inputs(M, N, K, seed=4, dist="normal")
+        ref = oracle.gemm_f32(A, B)
+        for fn in (api.b200Hgemm, api.b200HgemmStreamK, api.b200HgemmSplitK):
+            C = run(fn, A, B, cuda_device)
+            assert_close_to_oracle(C, ref, f"{fn.__name__} {M}x{N}x{K}")
+
+
+def test_fixed_variant_entry_points(cuda_device):
+    M, N, K = 512, 768, 512
+    A, B = make_inputs(M, N, K, seed=5)
+    ref = oracle.gemm_f32(A, B)
+    for fn in (api.b200Hgemm, api.b200HgemmCta1, api.b200HgemmCta2, api.b200HgemmSplitK, api.b200HgemmStreamK,
+               api.b200HgemmSimt):
+        assert_close_to_oracle(run(fn, A, B, cuda_device), ref, fn.__name__)
+
+
+def test_any_shape_goes_through_the_cuda_core_kernel(cuda_device):
+    # K % 8 != 0: no TMA row pitch; the library still computes on the GPU
+    g = np.load(str(__import__("pathlib").Path(__file__).parent / "golden" / "odd_k_48x40x100.npz"))
+    C = run(api.b200Hgemm, g["A"], g["B"], cuda_device)
+    assert_close_to_oracle(C, g["ref_f32"], "odd K")
+
+
+def test_golden_fixtures_on_device(cuda_device):
+    from pathlib import Path
+
+    for path in sorted((Path(__file__).parent / "golden").glob("*.npz")):
+        g = np.load(path)
+        C = run(api.b200Hgemm, g["A"], g["B"], cuda_device)
+        assert_close_to_oracle(C, g["ref_f32"], path.stem)
+        # against the float64 product rounded to FP16: at most one FP16 step of each value
+        g16 = g["ref_f16"].astype(np.float64)
+        step = 2.0 ** -10 * np.abs(g16) + 1e-4 * np.abs(g16).max()
+        assert (np.abs(C.astype(np.float64) - g16) <= step).all(), path.stem
+
+
+def test_results_are_reproducible_bit_for_bit(cuda_device):
+    M, N, K = 256, 1024, 2048
+    A, B = make_inputs(M, N, K, seed=6)
+    for plan in (plan_of(_native.VARIANT_CTA1, 256), plan_of(_native.VARIANT_CTA2, 256),
+                 plan_of(_native.VARIANT_STREAMK, 128), plan_of(_native.VARIANT_STREAMK, 64, parts=97)):
+        first = run(None, A, B, cuda_device, plan).view(np.uint16)
+        for _ in range(3):
+            again = run(None, A, B, cuda_device, plan).view(np.uint16)
+            assert np.array_equal(first, again), f"variant {plan.variant} is not deterministic"
+
+
+def test_row_slabs_equal_rows_of_the_full_product(cuda_device):
+    # the multi-GPU partition: each slab is computed by the same tile code as the full problem
+    from cuda_hgemm_b200.partition import row_slabs
+
+    M, N, K = 2048, 1024, 512
+    A, B = make_inputs(M, N, K, seed=8)
+    plan = plan_of(_native.VARIANT_CTA1, 256)
+    full = run(None, A, B, cuda_device, plan).view(np.uint16)
+    for lo, hi in row_slabs(M, 4):
+        slab = run(None, A[lo:hi], B, cuda_device, plan).view(np.uint16)
+        assert np.array_equal(slab, full[lo:hi])
+
+
+def test_linearity_at_full_size(cuda_device):
+    """Size-independent property at a benchmark-size shape: (A1 + A2) * B = A1*B + A2*B when the
+    sums are exact in FP16 (small integers), checked on all of C; plus sampled rows vs the oracle."""
+    import torch
+
+    M = N = K = 4096
+    rng = np.random.default_rng(9)
+    A1 = rng.integers(-2, 3, size=(M, K)).astype(np.float16)
+    A2 = rng.integers(-2, 3, size=(M, K)).astype(np.float16)
+    B = (rng.integers(-2, 3, size=(N, K)) / 64.0).astype(np.float16)
+    dB = to_dev(B, cuda_device)
+    outs = []
+    for a in (A1, A2, A1 + A2):
+        C = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+        api.b200Hgemm(to_dev(a, cuda_device), dB, C)
+        outs.append(C)
+    torch.cuda.synchronize()
+    assert api.last_device_error() == 0
+    # every partial sum is a multiple of 1/64 below 2^11/64: exact in FP32, and the outputs are exact
+    # in FP16 whenever |C| < 32, so linearity must hold bit for bit there
+    c1, c2, c12 = (o.float() for o in outs)
+    exact = (c1.abs() < 16) & (c2.abs() < 16)
+    assert torch.equal((c1 + c2)[exact], c12[exact])
+    rows = [0, 127, 128, 2049, M - 1]
+    ref = np.stack([oracle.gemm_f32_rows(A1 + A2, B, r, 1)[0] for r in rows])
+    assert_close_to_oracle(outs[2][rows].cpu().numpy(), ref, "4096^3 sampled rows")
+
+
+def test_large_square_sampled_rows(cuda_device):
+    import torch
+
+    M = N = K = 8192
+    A, B = make_inputs(M, N, K, seed=10)
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    C = poisoned(M, N, cuda_device).view(M, N)
+    api.b200Hgemm(dA, dB, C)
+    torch.cuda.synchronize()
+    assert api.last_device_error() == 0
+    assert torch.isfinite(C).all()
+    # the first and last row block and one in the middle cover every column tile and k-block
+    for row0 in (0, 4096 + 128, M - 128):
+        ref = oracle.gemm_f32_rows(A, B, row0, 128)
+        assert_close_to_oracle(C[row0:row0 + 128].cpu().numpy(), ref, f"8192^3 rows {row0}..")
+    # the CTA-pair and single-CTA kernels agree on all of C to one FP16 step (same products, other order)
+    C1 = torch.empty_like(C)
+    api.b200HgemmCta1(dA, dB, C1)
+    torch.cuda.synchronize()
+    diff = (C.float() - C1.float()).abs()
+    assert (diff <= 2.0 ** -9 * C1.float().abs() + 1e-3).all()
+
+
+def test_host_pointer_entry_point(cuda_device):
+    import torch
+
+    for M, N, K in ((256, 256, 256), (2048, 512, 256), (300, 264, 136)):
+        A, B = make_inputs(M, N, K, seed=11)
+        hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+        hC = torch.full((M, N), float("nan"), dtype=torch.float16).pin_memory()
+        api.hgemm_host(hA, hB, hC)
+        assert_close_to_oracle(hC.numpy(), oracle.gemm_f32(A, B), f"host {M}x{N}x{K}")
+
+
+def test_error_codes_on_device(cuda_device):
+    import torch
+
+    lib = _native.load()
+    A = torch.zeros(64 * 64 + 8, dtype=torch.float16, device=cuda_device)
+    B = torch.zeros(64 * 64, dtype=torch.float16, device=cuda_device)
+    C = torch.zeros(64 * 64, dtype=torch.float16, device=cuda_device)
+    # a pointer 2 bytes off a 16-byte boundary
+    assert lib.b200_hgemm(A.data_ptr() + 2, B.data_ptr(), C.data_ptr(), 64, 64, 64, None) == _native.ERR_MISALIGNED
+    # tensor-core variants refuse K % 8 != 0 instead of computing something else
+    assert lib.b200_hgemm_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), 64, 64, 60,
+                             ctypes.byref(plan_of(_native.VARIANT_CTA1, 256)), None) == _native.ERR_UNSUPPORTED
+    assert lib.b200_hgemm_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), 64, 64, 64,
+                             ctypes.byref(plan_of(_native.VARIANT_CTA1, 96)), None) == _native.ERR_UNSUPPORTED
+    # a caller-provided workspace that is too small is reported, not outgrown
+    ws = torch.zeros(1 << 17, dtype=torch.uint8, device=cuda_device)
+    assert lib.b200_hgemm_set_workspace(ws.data_ptr(), ws.numel()) == 0
+    rc = lib.b200_hgemm_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), 64, 64, 64,
+                           ctypes.byref(plan_of(_native.VARIANT_STREAMK, 256, parts=8)), None)
+    assert rc == _native.ERR_WORKSPACE
+    assert lib.b200_hgemm_set_workspace(None, 0) == 0
+    torch.cuda.synchronize()
+    assert api.last_device_error() == 0
