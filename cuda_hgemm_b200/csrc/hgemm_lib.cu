@@ -57,6 +57,7 @@ struct DeviceState {
     cudaStream_t host_stream[2] = {nullptr, nullptr};
     cudaEvent_t host_event[2] = {nullptr, nullptr};
     bool attr_set[16] = {};
+    int max_clusters[16] = {};  // CTA pairs the device can keep resident at once, per pair kernel
     TensorMapSlot tm_cache[64];
 };
 
@@ -249,6 +250,23 @@ static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, ui
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n_attrs;
+    if (CG == 2) {
+        // A persistent grid must be fully resident: ask how many pairs fit (GPC boundaries can
+        // leave fewer than SMs / 2) and never launch more.
+        if (st.max_clusters[attr_slot] == 0) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+                cudaGetLastError();
+                return B200_HGEMM_ERR_CUDA;
+            }
+            std::lock_guard<std::mutex> lock(st.mu);
+            st.max_clusters[attr_slot] = n;
+        }
+        if (grid / 2 > static_cast<uint32_t>(st.max_clusters[attr_slot])) {
+            grid = 2u * static_cast<uint32_t>(st.max_clusters[attr_slot]);
+            cfg.gridDim = dim3(grid, 1, 1);
+        }
+    }
     if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
