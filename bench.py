@@ -1,0 +1,508 @@
+#!/usr/bin/env python
+"""HGEMM benchmark: TFLOP/s of C[M x N] = A[M x K] * B on B200, next to cuBLAS.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step is one GEMM of the workload. The default workload is the 16384^3 square HGEMM -- the
+largest point of the reference's square sweep (reference run_sample.sh:29-37) -- on one GPU; with
+N GPUs (one process per GPU under torchrun) the same problem is split into N row slabs of C
+(A sharded along M, B replicated, no data exchange), so the series over N is strong scaling.
+Inputs are synthetic: FP16 values uniform in [-1, 1) from a fixed seed, as the reference's own
+driver draws them (reference src/common/matrix.h:28-33, there unseeded).
+
+Rank 0 prints ONE JSON line. `value` is whole-job TFLOP/s with operands resident in HBM,
+timed with CUDA events on the launching stream (max over ranks); `e2e` is the same metric
+through the host-pointer entry point of the C ABI, copies included; `roofline` relates the
+kernel to the measured tensor-core peak; `cpu_baseline` is the FP32-accumulate host GEMM of the
+checker timed on this box's cores. `--impl reference` times the reference project's own kernels
+(compiled unmodified for sm_100a) on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+SEED = 2023
+NOMINAL_FP16_DENSE_TFLOPS = 2250.0
+
+WORKLOADS = {
+    # name: (M, N, K, distribution, description)
+    "square16384": (16384, 16384, 16384, "uniform", "square HGEMM M=N=K=16384, largest point of the 256..16384 sweep"),
+    "square8192": (8192, 8192, 8192, "uniform", "square HGEMM M=N=K=8192"),
+    "square4096": (4096, 4096, 4096, "uniform", "square HGEMM M=N=K=4096"),
+    "prefill": (8192, 28672, 8192, "normal", "prefill-style HGEMM M=8192 N=28672 K=8192"),
+    "skinny16": (16, 14336, 4096, "normal", "decode-style HGEMM M=16 N=14336 K=4096"),
+    "skinny128": (128, 14336, 4096, "normal", "decode-style HGEMM M=128 N=14336 K=4096"),
+    "skinny128t": (128, 4096, 14336, "normal", "decode-style HGEMM M=128 N=4096 K=14336"),
+}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)),
+                    "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+        except Exception:
+            pass
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._ok = False
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = None
+            try:
+                import torch
+
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+            except Exception:
+                pass
+            self.handle = None
+            if uuid:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    u = pynvml.nvmlDeviceGetUUID(h)
+                    u = u.decode() if isinstance(u, bytes) else u
+                    if uuid in u:
+                        self.handle = h
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self._ok = True
+        except Exception:
+            self._ok = False
+
+    REASONS = (("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40),
+               ("hw_power_brake_slowdown", 0x80), ("sw_power_cap", 0x4))
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else int(
+                    nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for name, bit in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._ok:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_inputs(torch, M, N, K, dist, device, row_lo, row_hi):
+    """Seeded operands on the device. Every rank draws the same B; the A slab is cut from the
+    same full-size draw a single GPU would use, so the job's inputs do not depend on N."""
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+    if dist == "uniform":
+        A = torch.rand((M, K), generator=g, device=device, dtype=torch.float32).mul_(2).sub_(1).to(torch.float16)
+        g.manual_seed(SEED + 1)
+        B = torch.rand((N, K), generator=g, device=device, dtype=torch.float32).mul_(2).sub_(1).to(torch.float16)
+    else:
+        A = torch.randn((M, K), generator=g, device=device, dtype=torch.float32).to(torch.float16)
+        g.manual_seed(SEED + 1)
+        B = (torch.randn((N, K), generator=g, device=device, dtype=torch.float32) / (K ** 0.5)).to(torch.float16)
+    return A[row_lo:row_hi].contiguous(), B
+
+
+def time_launches(torch, fn, warmup, steps):
+    """Mean milliseconds of `steps` back-to-back calls after `warmup` calls (events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def time_graph(torch, fn, launches=20, replays=5):
+    """Mean milliseconds per call when `launches` calls are captured into one CUDA graph: removes the
+    interpreter's per-call cost, which dominates kernels of a few microseconds."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            for _ in range(launches):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    torch.cuda.current_stream().wait_stream(s)
+    return e0.elapsed_time(e1) / (launches * replays)
+
+
+def load_compare():
+    from cuda_hgemm_b200 import build as pkg_build
+
+    if not pkg_build.COMPARE_SO.exists():
+        return None
+    lib = ctypes.CDLL(str(pkg_build.COMPARE_SO))
+    for name in ("hgemm_compare_cublas_fp16", "hgemm_compare_cublas_fp32"):
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_size_t] * 3 + [ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+    return lib
+
+
+def cublas_callable(torch, lib, which, A, B, C):
+    M, K = A.shape
+    N = B.shape[0]
+    fn = getattr(lib, which)
+    a, b, c = A.data_ptr(), B.data_ptr(), C.data_ptr()
+
+    def call():
+        rc = fn(a, b, c, M, N, K, torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"{which} failed with cuBLAS status {rc}")
+    return call
+
+
+def cpu_baseline(M, N, K, dist):
+    """FP32-accumulate host GEMM (the checker's code) on a bounded row sample of the workload."""
+    import numpy as np
+
+    from oracle import hgemm_oracle as oracle
+
+    rng = np.random.default_rng(SEED)
+    threads = oracle.max_threads()
+    probe_rows = min(M, 64)
+    rows_cap = min(M, 4096)
+    if dist == "uniform":
+        A = rng.uniform(-1, 1, size=(rows_cap, K)).astype(np.float16)
+        B = rng.uniform(-1, 1, size=(N, K)).astype(np.float16)
+    else:
+        A = rng.standard_normal(size=(rows_cap, K), dtype=np.float32).astype(np.float16)
+        B = (rng.standard_normal(size=(N, K), dtype=np.float32) / np.sqrt(K)).astype(np.float16)
+    t_probe = oracle.time_rows(A, B, probe_rows, threads)
+    # aim at about 10 s of CPU work
+    rows = int(max(probe_rows, min(rows_cap, probe_rows * 10.0 / max(t_probe, 1e-6))))
+    rows = max(1, (rows // 8) * 8) if rows >= 8 else rows
+    t = oracle.time_rows(A, B, rows, threads)
+    tflops = 2.0 * rows * N * K / t / 1e12
+    return {"value": round(tflops, 6), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"first {rows} of {M} rows of C (rows x {N} x {K}), {t:.2f} s wall; whole-matrix time scales linearly in M"}
+
+
+def dist_setup(torch, n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(local)
+    return rank, world, local
+
+
+def barrier(torch, world):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(torch, value, world, device):
+    if world == 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_ours(args):
+    import torch
+
+    from cuda_hgemm_b200 import api
+    from cuda_hgemm_b200.partition import row_slabs
+
+    rank, world, local = dist_setup(torch, args.gpus)
+    device = torch.device("cuda", local)
+    M, N, K, dist_name, desc = WORKLOADS[args.workload]
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    lo, hi = row_slabs(M, world)[rank]
+    A, B = make_inputs(torch, M, N, K, dist_name, device, lo, hi)
+    C = torch.empty((hi - lo, N), dtype=torch.float16, device=device)
+    rows = hi - lo
+    plan = api.select_plan(rows, N, K) if rows else None
+
+    def step():
+        if rows:
+            api.b200Hgemm(A, B, C)
+
+    # ---- device-resident timing: the headline kernel number ----
+    launches_before = api.launch_count()
+    for _ in range(warmup):
+        step()
+    barrier(torch, world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as sampler:
+        launches_timed0 = api.launch_count()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        launches_timed = api.launch_count() - launches_timed0
+    barrier(torch, world)
+    ms_total = max_over_ranks(torch, e0.elapsed_time(e1), world, device)
+    if api.last_device_error() != 0:
+        raise RuntimeError("a kernel gave up on a bounded wait")
+    ms_per_step = ms_total / steps
+    flops_job = 2.0 * M * N * K
+    value = flops_job / (ms_per_step * 1e-3) / 1e12
+    clocks = sampler.summary()
+
+    # ---- end to end through the host-pointer entry point ----
+    e2e_steps = max(1, min(steps, 5))
+    hA = torch.empty((rows, K), dtype=torch.float16).pin_memory()
+    hB = torch.empty((N, K), dtype=torch.float16).pin_memory()
+    hC = torch.empty((rows, N), dtype=torch.float16).pin_memory()
+    hA.copy_(A)
+    hB.copy_(B)
+    if rows:
+        api.hgemm_host(hA, hB, hC)  # warm-up: staging buffers and streams are created here
+    barrier(torch, world)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        if rows:
+            api.hgemm_host(hA, hB, hC)
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(torch, (time.perf_counter() - t0) / e2e_steps, world, device)
+    barrier(torch, world)
+    e2e_ok = bool(torch.equal(hC.to(device), C)) if rows else True
+
+    if rank != 0:
+        return
+    peaks = measured_peaks()
+    # roofline of the dominant kernel: algorithmic flops of one launch (this rank's slab) over its mean duration
+    flops_launch = 2.0 * rows * N * K
+    achieved = flops_launch / (ms_per_step * 1e-3) / 1e12
+    out = {
+        "metric": "HGEMM TFLOP/s vs cuBLAS and % FP16 TC peak",
+        "value": round(value, 2),
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f16 (FP32 accumulate in tensor memory, FP16 out)",
+        "data": f"synthetic: FP16 {dist_name} from seed {SEED}",
+        "config": {"workload": f"{args.workload}: {desc}", "M": M, "N": N, "K": K,
+                   "partition": f"{world} row slab(s) of C, B replicated, no collective",
+                   "l2": "operands larger than L2 (A, B, C slabs >= 64 MiB each)" if rows * K * 2 + N * K * 2 > (126 << 20)
+                   else "operands fit in L2; B rotated is not applied (see skinny workloads in profiles/)",
+                   "plan": plan.as_dict() if plan else None},
+        "gpu_launches": int(launches_timed),
+        "pct_fp16_dense_peak": round(100.0 * value / (NOMINAL_FP16_DENSE_TFLOPS * world), 2),
+        "clocks": clocks,
+        "e2e": {"value": round(flops_job / e2e_s / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int((rows * K + N * K) * 2), "d2h_bytes_per_step": int(rows * N * 2),
+                "steps": e2e_steps, "matches_device_result": e2e_ok,
+                "api": "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": round(achieved / peaks["tflops"], 4),
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst; sustained {peaks['tflops_sustained']}",
+                     "frac_of_sustained": round(achieved / peaks["tflops_sustained"], 4) if peaks["tflops_sustained"] else None,
+                     "traffic": args.traffic_bytes},
+    }
+
+    # ---- comparisons on the same operands (outside the timed region) ----
+    cmp_lib = load_compare()
+    if cmp_lib is not None and rows:
+        Cc = torch.empty_like(C)
+        for key, sym in (("cublas_fp16_compute_tflops", "hgemm_compare_cublas_fp16"),
+                         ("cublas_fp32_compute_tflops", "hgemm_compare_cublas_fp32")):
+            ms = time_launches(torch, cublas_callable(torch, cmp_lib, sym, A, B, Cc), warmup, steps)
+            out[key] = round(world * flops_launch / (ms * 1e-3) / 1e12, 2)
+        best = max(out["cublas_fp16_compute_tflops"], out["cublas_fp32_compute_tflops"])
+        out["vs_cublas_best"] = round(value / best, 4)
+        out["vs_cublas_fp32_compute"] = round(value / out["cublas_fp32_compute_tflops"], 4)
+
+    if world == 1 and not args.no_sweep and cmp_lib is not None:
+        sweep = []
+        for n in (256, 512, 1024, 2048, 4096, 8192):
+            a, b = make_inputs(torch, n, n, n, "uniform", device, 0, n)
+            c = torch.empty((n, n), dtype=torch.float16, device=device)
+            ours = time_graph(torch, lambda: api.b200Hgemm(a, b, c))
+            cub32 = time_graph(torch, cublas_callable(torch, cmp_lib, "hgemm_compare_cublas_fp32", a, b, c))
+            cub16 = time_graph(torch, cublas_callable(torch, cmp_lib, "hgemm_compare_cublas_fp16", a, b, c))
+            f = 2.0 * n ** 3 / 1e9
+            sweep.append({"n": n, "tflops": round(f / ours, 2), "cublas_fp32_compute": round(f / cub32, 2),
+                          "cublas_fp16_compute": round(f / cub16, 2)})
+        out["sweep_points"] = sweep
+        out["sweep_note"] = "20 launches per CUDA graph, 5 replays; operands of the small sizes stay in L2 for every library alike"
+
+    if world == 1:
+        out["cpu_baseline"] = cpu_baseline(M, N, K, dist_name)
+    print(json.dumps(out), flush=True)
+
+
+REF_ENABLED = ("wmmaPadding", "wmmaAsync", "wmmaAsyncPg2s", "wmmaAsyncPg2sPs2r", "wmmaAsyncStage2", "wmmaAsyncStage3",
+               "mmaPermuted", "mmaAsync", "mmaAsyncPg2s", "mmaAsyncPg2sPs2r", "mmaAsyncStage2", "mmaAsyncStage3",
+               "mmaAsyncStage4")
+REF_NAIVE = ("mmaNaive", "wmmaNaive")
+
+
+def run_reference(args):
+    """The reference project's own kernels (unmodified sources, built for sm_100a) on the same workload.
+
+    The reference has no CPU implementation of this path; its code IS the GPU kernels, so this arm
+    times them: every kernel its driver enables (reference src/main.cu:106-123), best one reported.
+    Only rank 0 works; the reference is single-GPU (its only device knob is -gpu_rank)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    from oracle import build as oracle_build
+
+    M, N, K, dist_name, desc = WORKLOADS[args.workload]
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    base = {"impl": "reference", "metric": "HGEMM TFLOP/s vs cuBLAS and % FP16 TC peak", "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 (FP16 accumulate, as the reference's kernels compute)",
+            "data": f"synthetic: FP16 {dist_name} from seed {SEED}",
+            "config": {"workload": f"{args.workload}: {desc}", "M": M, "N": N, "K": K}}
+    if not oracle_build.REF_SO.exists() or not torch.cuda.is_available():
+        # no build of the reference's kernels travelled here: time the CPU restatement instead
+        cb = cpu_baseline(M, N, K, dist_name)
+        base.update({"value": cb["value"], "ms_per_step": None, "cpu_baseline": cb, "gpu_launches": 0,
+                     "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                     "note": "reference kernel library absent; value is the CPU port of the checker"})
+        print(json.dumps(base), flush=True)
+        return
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    lib = ctypes.CDLL(str(oracle_build.REF_SO))
+    A, B = make_inputs(torch, M, N, K, dist_name, device, 0, M)
+    C = torch.empty((M, N), dtype=torch.float16, device=device)
+    names = REF_ENABLED if (M % 256 == 0 and N % 128 == 0 and K % 32 == 0 and K >= 128) else REF_NAIVE
+    flops = 2.0 * M * N * K
+    per_kernel = {}
+    launches = 0
+    for name in names:
+        fn = getattr(lib, oracle_build.mangled(name))
+        fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_size_t] * 3
+        fn.restype = None
+        a, b, c = A.data_ptr(), B.data_ptr(), C.data_ptr()
+        ms = time_launches(torch, lambda: fn(a, b, c, M, N, K), warmup, steps)  # launches on the default stream
+        launches += steps
+        per_kernel[oracle_build.REF_KERNELS[name]] = round(flops / (ms * 1e-3) / 1e12, 2)
+    best_name = max(per_kernel, key=per_kernel.get)
+    best_fn = getattr(lib, oracle_build.mangled([n for n in names if oracle_build.REF_KERNELS[n] == best_name][0]))
+    # end to end the way the reference's Matrix does it: blocking uploads, kernel, blocking download
+    hA = torch.empty((M, K), dtype=torch.float16).pin_memory().copy_(A)
+    hB = torch.empty((N, K), dtype=torch.float16).pin_memory().copy_(B)
+    hC = torch.empty((M, N), dtype=torch.float16).pin_memory()
+    e2e_steps = max(1, min(steps, 5))
+
+    def e2e_once():
+        A.copy_(hA)
+        B.copy_(hB)
+        best_fn(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K)
+        hC.copy_(C)
+        torch.cuda.synchronize()
+    e2e_once()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_once()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    value = per_kernel[best_name]
+    base.update({"value": value, "ms_per_step": round(flops / value / 1e9, 5), "best_kernel": best_name,
+                 "kernels": per_kernel, "gpu_launches": launches,
+                 "e2e": {"value": round(flops / e2e_s / 1e12, 2), "unit": "TFLOP/s",
+                         "h2d_bytes_per_step": int((M * K + N * K) * 2), "d2h_bytes_per_step": int(M * N * 2)},
+                 "cpu_baseline": cpu_baseline(M, N, K, dist_name),
+                 "note": "reference = its own CUDA kernels built unmodified for sm_100a (it has no CPU path); "
+                         "cpu_baseline is the checker's host GEMM"})
+    print(json.dumps(base), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square16384")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the extra square sizes measured after the timed region")
+    ap.add_argument("--traffic-bytes", type=float, default=None,
+                    help="DRAM bytes per launch from an ncu capture of this workload (reported as roofline.traffic)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
