@@ -15,7 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200_hgemm.so"
 # every symbol include/b200_hgemm.h declares
 EXPORTED_SYMBOLS = (
     "b200_hgemm", "b200_hgemm_cta1", "b200_hgemm_cta2", "b200_hgemm_splitk", "b200_hgemm_streamk",
-    "b200_hgemm_simt", "b200_hgemm_ex", "b200_hgemm_host", "b200_hgemm_select", "b200_hgemm_workspace_bytes",
+    "b200_hgemm_simt", "b200_hgemm_streamk_static", "b200_hgemm_ex", "b200_hgemm_host", "b200_hgemm_select", "b200_hgemm_workspace_bytes",
     "b200_hgemm_set_workspace", "b200_hgemm_last_device_error", "b200_hgemm_status_string",
     "b200_hgemm_version", "b200_hgemm_launch_count", "b200_sched_tile_coord", "b200_sched_segments",
     "b200_sched_contributors", "b200_sched_partial_slot", "b200_debug_idesc", "b200_debug_smem_desc",
@@ -67,7 +67,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIB_PATH))
     gemm_args = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p]
     for name in ("b200_hgemm", "b200_hgemm_cta1", "b200_hgemm_cta2", "b200_hgemm_splitk", "b200_hgemm_streamk",
-                 "b200_hgemm_simt"):
+                 "b200_hgemm_simt", "b200_hgemm_streamk_static"):
         fn = getattr(lib, name)
         fn.argtypes = gemm_args
         fn.restype = c_int

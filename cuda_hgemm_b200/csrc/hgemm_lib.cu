@@ -334,7 +334,8 @@ static int check_args(const void *A, const void *B, const void *C, size_t M, siz
 }
 
 static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
-                    const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes) {
+                    const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes,
+                    uint32_t *error_word_override = nullptr) {
     int rc = validate_plan(pl, N, K);
     if (rc != B200_HGEMM_OK) return rc;
     if (pl.variant == B200_VARIANT_SIMT) return run_simt(A, B, C, M, N, K, stream);
@@ -347,7 +348,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     GemmParams p;
     memset(&p, 0, sizeof(p));
     p.c = static_cast<__half *>(C);
-    p.error_word = st.error_word;
+    p.error_word = error_word_override ? error_word_override : st.error_word;
     p.m = static_cast<uint32_t>(M);
     p.n = static_cast<uint32_t>(N);
     p.k = static_cast<uint32_t>(K);
@@ -446,6 +447,58 @@ static int entry(const void *A, const void *B, void *C, size_t M, size_t N, size
     return run_plan(*st, A, B, C, M, N, K, pl, stream, nullptr, 0);
 }
 
+// ------------------------------------------------------------------------------------------
+// allocation-free stream-k: scratch in a static device array
+// ------------------------------------------------------------------------------------------
+// Layout: [256 B error word | 64 KiB tile counters | 16 MiB FP32 partial-tile slots].
+// 16 MiB holds 2 slots of 128 x 128 floats for each of 128 k-ranges, which is the most the
+// entry point launches. Every GPU on which this library is loaded keeps these 16.06 MiB
+// reserved until the process exits, whether or not the entry point is ever called.
+constexpr size_t kStaticHeaderBytes = 256;
+constexpr size_t kStaticPartialBytes = size_t(16) << 20;
+constexpr size_t kStaticScratchBytes = kStaticHeaderBytes + kCounterBytes + kStaticPartialBytes;
+constexpr int kStaticBn = 128;
+constexpr uint32_t kStaticMaxParts = kStaticPartialBytes / (2u * 128u * kStaticBn * sizeof(float));  // 128
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// What the allocation-free entry point knows about a device. In host code the name
+// g_static_scratch is only the runtime's handle for the array, not an address a kernel can
+// use: the device address is asked for once per device, while that device is current.
+struct StaticDevice {
+    bool ready = false;
+    bool sm100 = false;
+    int sm_count = 0;
+    unsigned char *scratch = nullptr;
+};
+static std::mutex g_static_mu;
+static StaticDevice g_static_dev[kMaxDevices];
+
+static int static_device(int dev, StaticDevice *out) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDevice &sd = g_static_dev[dev];
+    if (!sd.ready) {
+        int major = 0, sms = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            return B200_HGEMM_ERR_CUDA;
+        }
+        sd.sm100 = (major == 10);
+        sd.sm_count = sms;
+        if (sd.sm100) {
+            void *ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return B200_HGEMM_ERR_CUDA;
+            }
+            sd.scratch = static_cast<unsigned char *>(ptr);
+        }
+        sd.ready = true;
+    }
+    *out = sd;
+    return B200_HGEMM_OK;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -494,6 +547,58 @@ int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N,
         pl.parts = static_cast<int32_t>(tiles * slices);
     }
     return run_plan(*st, A, B, C, M, N, K, pl, reinterpret_cast<cudaStream_t>(stream), nullptr, 0);
+}
+
+
+// Stream-k GEMM that allocates nothing. It is meant for callers that cannot call cudaMalloc at
+// the point where they need a GEMM: code running under a memory pool that owns all device
+// memory, a latency-critical serving loop in which an allocation (which may synchronise the
+// device) is not acceptable, or a plugin whose host forbids allocations after start-up. The
+// other entry points create or grow a workspace on first use; this one keeps its scratch in
+// the static device array above and calls no allocating routine.
+//
+//  * Limits: K % 8 == 0 (as for every tensor-core variant) and at most 16384 output tiles of
+//    128 x 128, i.e. ceil(M/128) * ceil(N/128) <= 16384; beyond that the call returns
+//    B200_HGEMM_ERR_TOO_LARGE. The k-ranges are capped at 128 so that their partial tiles fit
+//    the 16 MiB array.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress),
+//    sets the kernel's shared-memory attribute and encodes tensor maps. Make that first call
+//    outside any stream capture.
+//  * All calls on a device share the one array, which keeps whatever the last call left in it.
+//    Each call clears the error word and the tile counters, stream-ordered, before its kernel;
+//    partial tiles are always written before they are read. Two calls whose kernels overlap on
+//    the GPU (different streams with no dependency between them) race on the array: serialise them.
+//  * A bounded wait that expires inside this variant is recorded in the first word of the
+//    array, not in the word b200_hgemm_last_device_error() reads.
+int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+                              b200_stream_t stream) {
+    int rc = check_args(A, B, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;
+    const uint64_t tiles = static_cast<uint64_t>(ceil_div_u32(M, 128)) * ceil_div_u32(N, kStaticBn);
+    if (tiles > kMaxCountedTiles) return B200_HGEMM_ERR_TOO_LARGE;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_HGEMM_ERR_CUDA;
+    StaticDevice sd;
+    rc = static_device(dev, &sd);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!sd.sm100) return B200_HGEMM_ERR_NO_SM100;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    // the error word and the tile counters have to start at zero
+    if (cudaMemsetAsync(sd.scratch, 0, kStaticHeaderBytes + kCounterBytes, s) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+
+    b200_hgemm_plan pl;
+    memset(&pl, 0, sizeof(pl));
+    pl.variant = B200_VARIANT_STREAMK;
+    pl.bn = kStaticBn;
+    pl.tma_store = (N % 8 == 0) ? 1 : 0;
+    uint32_t parts = static_cast<uint32_t>(sd.sm_count);
+    if (parts > kStaticMaxParts) parts = kStaticMaxParts;
+    pl.parts = static_cast<int32_t>(parts);
+    // g_dev[dev] serves as the cache of tensor maps and kernel attributes; nothing in it is allocated here
+    return run_plan(g_dev[dev], A, B, C, M, N, K, pl, s, sd.scratch + kStaticHeaderBytes,
+                    kCounterBytes + kStaticPartialBytes, reinterpret_cast<uint32_t *>(sd.scratch));
 }
 
 int b200_hgemm_simt(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {

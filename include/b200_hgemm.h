@@ -78,6 +78,19 @@ int b200_hgemm_cta2(const void *A, const void *B, void *C, size_t M, size_t N, s
 int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
 int b200_hgemm_streamk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
 
+/* Stream-k GEMM that never allocates: its scratch (tile counters and FP32 partial tiles) is a
+ * static 16.06 MiB device array inside the library, held by every GPU the library is loaded on.
+ * It has no counterpart in the reference, whose kernels need no scratch memory; it exists for
+ * callers that may not call cudaMalloc where they need the GEMM (all device memory owned by a
+ * pool, a serving loop that cannot afford an allocation's implicit synchronisation, a host
+ * application that forbids allocations after start-up).
+ * Limits: K % 8 == 0; ceil(M/128) * ceil(N/128) <= 16384 tiles, else B200_HGEMM_ERR_TOO_LARGE.
+ * The first call on a device resolves the array's device address and should come before any
+ * stream capture. Calls share the array: kernels of two calls that overlap on the GPU race.
+ * A device-side wait expiry in this variant is recorded in the array's first word only. */
+int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+                              b200_stream_t stream);
+
 /* Any-shape CUDA-core kernel with FP32 accumulation: the counterpart of the reference's
  * simtNaive (src/simt_naive.cu:9-32), with the bounds guard corrected. */
 int b200_hgemm_simt(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
