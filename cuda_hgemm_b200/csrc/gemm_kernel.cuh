@@ -60,7 +60,21 @@ struct alignas(64) GemmParams {
     uint32_t group_m;
     uint32_t tma_store;  // 1: epilogue uses TMA stores (needs N % 8 == 0)
     uint32_t c_vec_ok;   // 1: 16-byte vector stores to C are aligned (N % 8 == 0)
+#ifdef B200_TIMELINE
+    unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
+#endif
 };
+
+#ifdef B200_TIMELINE
+#define B200_STAMP(slot)                                                                                  \
+    do {                                                                                                  \
+        if (p.timeline) p.timeline[blockIdx.x * 16 + (slot)] = global_timer_ns();                         \
+    } while (0)
+#else
+#define B200_STAMP(slot) \
+    do {                 \
+    } while (0)
+#endif
 
 template <int BN, int STAGES, int CG>
 struct KernelTraits {
@@ -158,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     const uint32_t worker = blockIdx.x / CG;
     const uint32_t workers = gridDim.x / CG;
 
+    if (threadIdx.x == 0) B200_STAMP(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar + 8u * s, 1);
@@ -181,10 +196,24 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         tmem_relinquish<CG>();
     }
     tcgen05_fence_before_sync();
-    __syncthreads();
-    if (CG == 2) cluster_sync_all();
+    if (CG == 2) {
+        // the peer's copies and arrivals target this CTA's barriers: both CTAs must have set up
+        __syncthreads();
+        cluster_sync_all();
+    } else {
+        // The producer warp initialised the barriers itself and needs no tensor memory: it
+        // only announces its arrival and starts loading while the allocation completes.
+        if (warp == 0) {
+            __threadfence_block();
+            named_bar_arrive(2, kThreads);
+        } else {
+            named_bar_sync(2, kThreads);
+        }
+    }
     tcgen05_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = (CG == 1 && warp == 0) ? 0u : *tmem_slot;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) B200_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -193,6 +222,10 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             Segment seg;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+#ifdef B200_TIMELINE
+            bool stamped_first_load = false;
+#endif
+            pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
             while (ok && work.next(seg)) {
                 const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
                 const int32_t row_a = static_cast<int32_t>((tc.m_blk * CG + cta_rank) * kBM);
@@ -221,8 +254,15 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         stage = 0;
                         phase ^= 1u;
                     }
+#ifdef B200_TIMELINE
+                    if (!stamped_first_load) {
+                        B200_STAMP(2);
+                        stamped_first_load = true;
+                    }
+#endif
                 }
             }
+            B200_STAMP(3);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -245,6 +285,9 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         break;
                     }
                     tcgen05_fence_after_sync();
+#ifdef B200_TIMELINE
+                    if (it == 0 && kb == seg.kb0) B200_STAMP(4);
+#endif
                     const uint32_t sa = base + stage * T::kStageBytes;
                     const uint64_t da = umma_smem_desc_sw128(sa);
                     const uint64_t db = umma_smem_desc_sw128(sa + T::kABytes);
@@ -271,6 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 }
                 ++it;
             }
+            B200_STAMP(5);
         }
         __syncwarp();
     } else {
@@ -282,6 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         WorkWalker<MODE> work(p, worker, workers);
         Segment seg;
         uint32_t it = 0, store_buf = 0;
+        pdl_wait_prior_grids();  // C, the workspace and its counters may still be in use by the previous kernel
         while (work.next(seg)) {
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;
@@ -290,6 +335,9 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             const uint32_t n0 = tc.n_blk * BN;
             if (!mbar_wait(tfull_bar + 8u * acc, acc_phase, abort_flag)) break;
             tcgen05_fence_after_sync();
+#ifdef B200_TIMELINE
+            if (epi_tid == 0) B200_STAMP(it == 0 ? 6 : 7);
+#endif
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
             const uint32_t row_in_tile = q * 32u + lane;
             const bool whole_tile = (MODE == kModeTiles) || (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
@@ -397,36 +445,48 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                     const uint64_t u0 = static_cast<uint64_t>(seg.tile) * p.k_blocks;
                     const uint32_t part_first = part_of_unit(u0, workers, total_units);
                     const uint32_t part_last = part_of_unit(u0 + p.k_blocks - 1, workers, total_units);
-                    if (row_live) {
-#pragma unroll 1
-                        for (uint32_t c = 0; c < BN / 32; ++c) {
-                            if ((n0 + c * 32u) >= p.n) break;
-                            float4 sum[8];
+                    // All 128 epilogue threads share the live part of the tile as a flat list of
+                    // 16-byte words in the workspace order (row fastest), so that every load is
+                    // coalesced and several are in flight per thread. The contributing ranges are
+                    // summed in range order: the result does not depend on who finished last.
+                    const uint32_t rows_live = (p.m - m0) < static_cast<uint32_t>(kBM) ? (p.m - m0) : kBM;
+                    const uint32_t cols_left = p.n - n0;
+                    const uint32_t words_per_row = ((cols_left < static_cast<uint32_t>(BN) ? cols_left : BN) + 3u) / 4u;
+                    const uint32_t total_words = rows_live * words_per_row;
+                    const uint32_t n_parts = part_last - part_first + 1u;
+                    const uint32_t slot_first = partial_slot(part_first, workers, p.tiles, p.k_blocks, seg.tile);
+                    // Only the first contributor can own slot index 2*part+1 or 2*part; all later
+                    // contributors start inside this tile, so theirs is slot 2*part.
+                    const bool vec4_ok = (p.n % 4u) == 0;
+                    for (uint32_t i0 = epi_tid; i0 < total_words; i0 += 2u * kEpiThreads) {
+                        const uint32_t i1 = i0 + kEpiThreads;
+                        const bool two = i1 < total_words;
+                        const uint32_t w0 = i0 / rows_live, r0i = i0 - w0 * rows_live;
+                        const uint32_t w1 = two ? i1 / rows_live : w0, r1i = two ? i1 - w1 * rows_live : r0i;
+                        float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+                        for (uint32_t k = 0; k < n_parts; ++k) {
+                            const uint32_t s = (k == 0) ? slot_first : 2u * (part_first + k);
+                            const float4 *src = p.partials + static_cast<size_t>(s) * (kBM * BN / 4);
+                            const float4 v0 = ld_cg_f4(src + w0 * kBM + r0i);
+                            const float4 v1 = ld_cg_f4(src + w1 * kBM + r1i);
+                            acc0.x += v0.x; acc0.y += v0.y; acc0.z += v0.z; acc0.w += v0.w;
+                            acc1.x += v1.x; acc1.y += v1.y; acc1.z += v1.z; acc1.w += v1.w;
+                        }
 #pragma unroll
-                            for (uint32_t j = 0; j < 8; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            // fixed order over the contributing parts: the result does not depend
-                            // on which of them happened to finish last
-                            for (uint32_t part = part_first; part <= part_last; ++part) {
-                                const uint32_t s = partial_slot(part, workers, p.tiles, p.k_blocks, seg.tile);
-                                const float4 *src = p.partials + static_cast<size_t>(s) * (kBM * BN / 4);
-#pragma unroll
-                                for (uint32_t j = 0; j < 8; ++j) {
-                                    const float4 v = ld_cg_f4(src + (c * 8u + j) * kBM + row_in_tile);
-                                    sum[j].x += v.x;
-                                    sum[j].y += v.y;
-                                    sum[j].z += v.z;
-                                    sum[j].w += v.w;
-                                }
+                        for (int h = 0; h < 2; ++h) {
+                            if (h == 1 && !two) break;
+                            const float4 a = h ? acc1 : acc0;
+                            const uint32_t col = n0 + (h ? w1 : w0) * 4u;
+                            __half *dst = p.c + static_cast<size_t>(m0 + (h ? r1i : r0i)) * p.n + col;
+                            if (vec4_ok && col + 4u <= p.n) {
+                                uint2 v;
+                                v.x = pack_half2_rn(__float_as_uint(a.x), __float_as_uint(a.y));
+                                v.y = pack_half2_rn(__float_as_uint(a.z), __float_as_uint(a.w));
+                                *reinterpret_cast<uint2 *>(dst) = v;
+                            } else {
+                                const float vals[4] = {a.x, a.y, a.z, a.w};
+                                for (uint32_t e = 0; e < 4 && col + e < p.n; ++e) dst[e] = __float2half_rn(vals[e]);
                             }
-                            uint32_t r[32];
-#pragma unroll
-                            for (uint32_t j = 0; j < 8; ++j) {
-                                r[4 * j + 0] = __float_as_uint(sum[j].x);
-                                r[4 * j + 1] = __float_as_uint(sum[j].y);
-                                r[4 * j + 2] = __float_as_uint(sum[j].z);
-                                r[4 * j + 3] = __float_as_uint(sum[j].w);
-                            }
-                            store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
                         }
                     }
                     // leave the counter at zero for the next launch
@@ -436,9 +496,12 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             }
             ++it;
         }
-        // shared memory must stay valid until the last TMA store has read it
-        if (lane == 0) tma_store_wait_all<0>();
+        if (epi_tid == 0) B200_STAMP(8);
+        // shared memory must stay valid until the last TMA store has read it (the writes
+        // themselves are complete, like any store, when the kernel has finished)
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
+        if (epi_tid == 0) B200_STAMP(9);
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -457,6 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         tcgen05_fence_after_sync();
         tmem_dealloc<CG>(tmem_base, T::kTmemCols);
     }
+    if (threadIdx.x == 32) B200_STAMP(10);
 }
 
 }  // namespace b200

@@ -62,6 +62,11 @@ struct DeviceState {
 };
 
 static DeviceState g_dev[kMaxDevices];
+#ifdef B200_TIMELINE
+// profiling builds only: device buffer of per-CTA time stamps, set through b200_debug_set_timeline
+static unsigned long long *g_timeline = nullptr;
+extern "C" void b200_debug_set_timeline(unsigned long long *buf) { g_timeline = buf; }
+#endif
 static std::atomic<uint64_t> g_launches{0};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -169,8 +174,14 @@ static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, 
     return static_cast<uint32_t>(parts);
 }
 
-// Shape -> plan. Large problems run whole 128x256 (or 256x256 per CTA pair) tiles; problems
-// that leave SMs idle in their last (or only) wave split k-ranges evenly over all SMs.
+// Shape -> plan, from sweeps on B200 (square sizes 256..16384 and the skinny decode shapes):
+//  * CTA pairs on 256x256 tiles once there are enough of them to fill the 74 pairs about 1.35
+//    times over; this is the configuration whose operand traffic (64 B per SM clock at full
+//    tensor rate) the SM's L2 port sustains, so it is the one that runs tensor-bound;
+//  * below that, single-CTA tiles, as wide as still leaves 64 or more tiles: narrow tiles move
+//    more bytes per flop, but with few tiles the per-SM load rate is what limits;
+//  * M <= 128 (decode-like, HBM-bound): whole 128-wide tiles when they cover most SMs, else
+//    equal k-ranges over all SMs with the FP32 workspace reduce.
 static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
     memset(pl, 0, sizeof(*pl));
     if (K % 8 != 0) {
@@ -180,41 +191,39 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
     pl->tma_store = (N % 8 == 0) ? 1 : 0;
     pl->group_m = 0;
-    const uint32_t m_blocks = ceil_div_u32(M, 128);
-    const uint32_t k_blocks = ceil_div_u32(K, 64);
+    const uint64_t m_blocks = ceil_div_u32(M, 128);
+    const uint64_t k_blocks = ceil_div_u32(K, 64);
+    const uint64_t tiles256 = m_blocks * ceil_div_u32(N, 256);
+    const uint64_t tiles128 = m_blocks * ceil_div_u32(N, 128);
 
-    // Efficiency of running whole tiles of width bn: useful tiles / (waves * SMs), discounted
-    // for narrow tiles, whose main loop re-reads the A slab more often per flop.
-    double best_score = -1.0;
-    int best_bn = 256;
-    const int bns[3] = {256, 128, 64};
-    const double width_factor[3] = {1.0, 0.88, 0.62};
-    for (int i = 0; i < 3; ++i) {
-        const uint64_t tiles = static_cast<uint64_t>(m_blocks) * ceil_div_u32(N, bns[i]);
-        const uint64_t waves = (tiles + sms - 1) / sms;
-        const double fill = static_cast<double>(tiles) / static_cast<double>(waves * sms);
-        const double score = fill * width_factor[i];
-        if (score > best_score) {
-            best_score = score;
-            best_bn = bns[i];
-        }
-    }
-    if (best_score >= 0.80) {
-        pl->bn = best_bn;
-        const uint64_t tiles256 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 256);
-        if (best_bn == 256 && M % 256 == 0 && tiles256 >= 2ull * (sms / 2)) {
-            pl->variant = B200_VARIANT_CTA2;
+    if (M <= 128) {
+        if (tiles128 * 4 >= 3ull * sms) {  // e.g. N = 14336: 112 tiles on 148 SMs
+            pl->variant = B200_VARIANT_CTA1;
+            pl->bn = 128;
+        } else if (k_blocks >= 8) {
+            pl->variant = B200_VARIANT_STREAMK;
+            pl->bn = (tiles128 * k_blocks >= 4ull * sms) ? 128 : 64;
         } else {
             pl->variant = B200_VARIANT_CTA1;
+            pl->bn = 64;
         }
         return;
     }
-    // Not enough whole tiles: split k-ranges. Narrower tiles when there is little k to split.
-    pl->variant = B200_VARIANT_STREAMK;
-    pl->bn = 128;
-    const uint64_t tiles128 = static_cast<uint64_t>(m_blocks) * ceil_div_u32(N, 128);
-    if (tiles128 * k_blocks < 4ull * sms) pl->bn = 64;
-    pl->parts = 0;
+
+    const uint64_t pairs256 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 256);
+    if (pairs256 * 100 >= 135ull * (sms / 2)) {
+        pl->variant = B200_VARIANT_CTA2;
+        pl->bn = 256;
+        return;
+    }
+    pl->variant = B200_VARIANT_CTA1;
+    if (tiles256 >= 64) {
+        pl->bn = 256;
+    } else if (tiles128 >= 64) {
+        pl->bn = 128;
+    } else {
+        pl->bn = 64;
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -239,8 +248,14 @@ static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, ui
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = T::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     int n_attrs = 0;
+    // programmatic dependent launch: the kernel's prologue (barrier set-up, tensor-memory
+    // allocation) may overlap the tail of the previous kernel in the stream; every global
+    // access inside the kernel comes after griddepcontrol.wait
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
     if (CG == 2) {
         attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
         attrs[n_attrs].val.clusterDim.x = 2;
@@ -362,6 +377,9 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
     p.tma_store = pl.tma_store ? 1u : 0u;
     p.c_vec_ok = (N % 8 == 0) ? 1u : 0u;
+#ifdef B200_TIMELINE
+    p.timeline = g_timeline;
+#endif
 
     rc = get_tensor_map(st, A, M, K, 128, 64, &p.tm_a);
     if (rc != B200_HGEMM_OK) return rc;

@@ -57,6 +57,28 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 
 // ---------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------
+// Lets the next kernel in the stream (if it was launched with programmatic stream
+// serialization) start its prologue while this grid is still running.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Blocks until every grid this one depends on has completed and its memory is visible.
+// Must precede the first global-memory access that can conflict with the previous kernel.
+__device__ __forceinline__ void pdl_wait_prior_grids() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Named barrier among `count` threads: arrive without waiting / arrive and wait.
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t arrivals) {
