@@ -149,8 +149,27 @@ def make_inputs(torch, M, N, K, dist, device, row_lo, row_hi):
     return A[row_lo:row_hi].contiguous(), B
 
 
+PREHEAT_S = 0.3
+
+
+def preheat(torch, fn, seconds=PREHEAT_S):
+    """Untimed calls for about `seconds` of GPU time: clocks ramp up from idle and then settle under
+    the power cap within the first tens of milliseconds of a dense GEMM, so a short timed region that
+    starts cold measures that transient, not the kernel. Applied to every library measured, alike."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    one = max(e0.elapsed_time(e1) * 1e-3, 1e-6)
+    for _ in range(min(20000, int(seconds / one))):
+        fn()
+    torch.cuda.synchronize()
+
+
 def time_launches(torch, fn, warmup, steps):
     """Mean milliseconds of `steps` back-to-back calls after `warmup` calls (events on the current stream)."""
+    preheat(torch, fn)
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -186,6 +205,33 @@ def time_graph(torch, fn, launches=20, replays=5):
         torch.cuda.synchronize()
     torch.cuda.current_stream().wait_stream(s)
     return e0.elapsed_time(e1) / (launches * replays)
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
+# captures under profiles/, keyed by workload; scaled captures say so there.
+NCU_TRAFFIC_BYTES = {
+    "square8192": 1.168e9,
+}
+
+
+def roofline(workload, rows, N, K, ms_per_step, peaks):
+    """Roofline entry of the dominant kernel for one launch of this rank's slab."""
+    skinny = rows <= 128
+    if skinny:
+        algo = 2.0 * (rows * K + N * K + rows * N)
+        achieved = algo / (ms_per_step * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": f"{peaks['source']} copy bandwidth",
+                "traffic": NCU_TRAFFIC_BYTES.get(workload)}
+    achieved = 2.0 * rows * N * K / (ms_per_step * 1e-3) / 1e12
+    # the timed region follows a pre-heat and runs back to back under the power cap: the sustained
+    # cuBLAS figure is the matching denominator; the burst figure is printed beside it
+    peak = peaks["tflops_sustained"] or peaks["tflops"]
+    return {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak, "unit": "TFLOP/s",
+            "frac": round(achieved / peak, 4),
+            "peak_source": f"{peaks['source']} cuBLAS bf16, sustained (kernel timed in a back-to-back loop after a pre-heat)",
+            "frac_of_burst_peak": round(achieved / peaks["tflops"], 4), "burst_peak": peaks["tflops"],
+            "traffic": NCU_TRAFFIC_BYTES.get(workload)}
 
 
 def load_compare():
@@ -294,7 +340,7 @@ def run_ours(args):
             api.b200Hgemm(A, B, C)
 
     # ---- device-resident timing: the headline kernel number ----
-    launches_before = api.launch_count()
+    preheat(torch, step)
     for _ in range(warmup):
         step()
     barrier(torch, world)
@@ -338,9 +384,7 @@ def run_ours(args):
     if rank != 0:
         return
     peaks = measured_peaks()
-    # roofline of the dominant kernel: algorithmic flops of one launch (this rank's slab) over its mean duration
     flops_launch = 2.0 * rows * N * K
-    achieved = flops_launch / (ms_per_step * 1e-3) / 1e12
     out = {
         "metric": "HGEMM TFLOP/s vs cuBLAS and % FP16 TC peak",
         "value": round(value, 2),
@@ -366,11 +410,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": int((rows * K + N * K) * 2), "d2h_bytes_per_step": int(rows * N * 2),
                 "steps": e2e_steps, "matches_device_result": e2e_ok,
                 "api": "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
-        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": round(achieved / peaks["tflops"], 4),
-                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst; sustained {peaks['tflops_sustained']}",
-                     "frac_of_sustained": round(achieved / peaks["tflops_sustained"], 4) if peaks["tflops_sustained"] else None,
-                     "traffic": args.traffic_bytes},
+        "roofline": roofline(args.workload, rows, N, K, ms_per_step, peaks),
     }
 
     # ---- comparisons on the same operands (outside the timed region) ----
@@ -495,8 +535,6 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square16384")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra square sizes measured after the timed region")
-    ap.add_argument("--traffic-bytes", type=float, default=None,
-                    help="DRAM bytes per launch from an ncu capture of this workload (reported as roofline.traffic)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -760,7 +760,7 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     if (cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
     size_t slabs = 1;
     if (M >= 2048 && M % 128 == 0) {
-        slabs = 4;
+        slabs = M >= 8192 ? 8 : 4;
         while (slabs > 1 && (M / 128) % slabs != 0) --slabs;
     }
     const size_t rows = M / slabs;
