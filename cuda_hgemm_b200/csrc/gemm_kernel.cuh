@@ -333,7 +333,11 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
             const uint32_t m0 = (tc.m_blk * CG + cta_rank) * kBM;
             const uint32_t n0 = tc.n_blk * BN;
-            if (!mbar_wait(tfull_bar + 8u * acc, acc_phase, abort_flag)) break;
+            // one lane per warp polls the barrier; the other 31 park at the warp barrier
+            uint32_t ready = 1;
+            if (lane == 0) ready = mbar_wait(tfull_bar + 8u * acc, acc_phase, abort_flag) ? 1u : 0u;
+            ready = __shfl_sync(0xffffffffu, ready, 0);
+            if (!ready) break;
             tcgen05_fence_after_sync();
 #ifdef B200_TIMELINE
             if (epi_tid == 0) B200_STAMP(it == 0 ? 6 : 7);
