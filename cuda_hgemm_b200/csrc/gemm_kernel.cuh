@@ -12,7 +12,8 @@
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (UMMA 128*CG x BN x 16)
 //               and commits stage releases / accumulator hand-offs to mbarriers
 //   warps 2-5   epilogue: tcgen05.ld -> FP32 -> FP16 -> swizzled staging -> TMA store
-//               (or FP32 partials to the workspace when a tile's k-range is split)
+//               (or FP32 partials to the workspace when a tile's k-range is split; those are
+//               summed by streamk_reduce_kernel, which follows in the stream)
 //
 // Two accumulators live in TMEM, so the epilogue of one tile overlaps the main loop of the
 // next. CG = 2 runs a pair of CTAs (a 2-CTA cluster) on one 256 x BN tile: each CTA stages
@@ -49,8 +50,7 @@ struct alignas(64) GemmParams {
     CUtensorMap tm_b;  // B as {K, N}, box {64, BN / CG}
     CUtensorMap tm_c;  // C as {N, M}, box {64, 32} (only valid when tma_store != 0)
     __half *c;
-    float4 *partials;        // stream-K: 2 slots per part, each 128 x BN FP32
-    uint32_t *tile_counters; // stream-K: one per tile, zero between launches
+    float4 *partials;        // stream-K: 2 slots per k-range, each 128 x BN FP32
     uint32_t *error_word;
     uint32_t m, n, k;
     uint32_t m_blocks;  // number of (128 * CG)-row blocks
@@ -157,14 +157,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     uint8_t *staging_ptr = base_ptr + STAGES * T::kStageBytes;
     const uint32_t bars = staging + kStagingBytes;
     uint8_t *bars_ptr = staging_ptr + kStagingBytes;
-    // barrier area: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | tmem base | abort | last flag
+    // barrier area: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | tmem base | abort
     const uint32_t full_bar = bars;
     const uint32_t empty_bar = bars + 8u * STAGES;
     const uint32_t tfull_bar = bars + 16u * STAGES;
     const uint32_t tempty_bar = tfull_bar + 16u;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_ptr + 16u * STAGES + 32u);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    volatile uint32_t *last_flag = tmem_slot + 2;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
@@ -183,7 +182,6 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             mbar_init(tempty_bar + 8u * a, 4 * CG);  // one arrival per epilogue warp of every CTA of the pair
         }
         *abort_flag = 0;
-        *last_flag = 0;
         fence_mbar_init();
     }
     if (warp == 0 && lane == 0) {
@@ -320,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     } else {
         // ------------------------------------------------------------------ epilogue
         const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
-        const uint32_t epi_tid = threadIdx.x - 64u;
+        [[maybe_unused]] const uint32_t epi_tid = threadIdx.x - 64u;
         uint8_t *my_staging_ptr = staging_ptr + q * 8192u;
         const uint32_t my_staging = staging + q * 8192u;
         WorkWalker<MODE> work(p, worker, workers);
@@ -433,70 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar + 8u * acc);
 
-                // ---- count this contribution; whoever completes the tile reduces it
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (epi_tid == 0) {
-                    const uint32_t mine = seg.kb1 - seg.kb0;
-                    const uint32_t before = atomicAdd(p.tile_counters + seg.tile, mine);
-                    *last_flag = (before + mine == p.k_blocks) ? 1u : 0u;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const bool is_last = (*last_flag != 0);
-                if (is_last) {
-                    __threadfence();
-                    const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
-                    const uint64_t u0 = static_cast<uint64_t>(seg.tile) * p.k_blocks;
-                    const uint32_t part_first = part_of_unit(u0, workers, total_units);
-                    const uint32_t part_last = part_of_unit(u0 + p.k_blocks - 1, workers, total_units);
-                    // All 128 epilogue threads share the live part of the tile as a flat list of
-                    // 16-byte words in the workspace order (row fastest), so that every load is
-                    // coalesced and several are in flight per thread. The contributing ranges are
-                    // summed in range order: the result does not depend on who finished last.
-                    const uint32_t rows_live = (p.m - m0) < static_cast<uint32_t>(kBM) ? (p.m - m0) : kBM;
-                    const uint32_t cols_left = p.n - n0;
-                    const uint32_t words_per_row = ((cols_left < static_cast<uint32_t>(BN) ? cols_left : BN) + 3u) / 4u;
-                    const uint32_t total_words = rows_live * words_per_row;
-                    const uint32_t n_parts = part_last - part_first + 1u;
-                    const uint32_t slot_first = partial_slot(part_first, workers, p.tiles, p.k_blocks, seg.tile);
-                    // Only the first contributor can own slot index 2*part+1 or 2*part; all later
-                    // contributors start inside this tile, so theirs is slot 2*part.
-                    const bool vec4_ok = (p.n % 4u) == 0;
-                    for (uint32_t i0 = epi_tid; i0 < total_words; i0 += 2u * kEpiThreads) {
-                        const uint32_t i1 = i0 + kEpiThreads;
-                        const bool two = i1 < total_words;
-                        const uint32_t w0 = i0 / rows_live, r0i = i0 - w0 * rows_live;
-                        const uint32_t w1 = two ? i1 / rows_live : w0, r1i = two ? i1 - w1 * rows_live : r0i;
-                        float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
-                        for (uint32_t k = 0; k < n_parts; ++k) {
-                            const uint32_t s = (k == 0) ? slot_first : 2u * (part_first + k);
-                            const float4 *src = p.partials + static_cast<size_t>(s) * (kBM * BN / 4);
-                            const float4 v0 = ld_cg_f4(src + w0 * kBM + r0i);
-                            const float4 v1 = ld_cg_f4(src + w1 * kBM + r1i);
-                            acc0.x += v0.x; acc0.y += v0.y; acc0.z += v0.z; acc0.w += v0.w;
-                            acc1.x += v1.x; acc1.y += v1.y; acc1.z += v1.z; acc1.w += v1.w;
-                        }
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            if (h == 1 && !two) break;
-                            const float4 a = h ? acc1 : acc0;
-                            const uint32_t col = n0 + (h ? w1 : w0) * 4u;
-                            __half *dst = p.c + static_cast<size_t>(m0 + (h ? r1i : r0i)) * p.n + col;
-                            if (vec4_ok && col + 4u <= p.n) {
-                                uint2 v;
-                                v.x = pack_half2_rn(__float_as_uint(a.x), __float_as_uint(a.y));
-                                v.y = pack_half2_rn(__float_as_uint(a.z), __float_as_uint(a.w));
-                                *reinterpret_cast<uint2 *>(dst) = v;
-                            } else {
-                                const float vals[4] = {a.x, a.y, a.z, a.w};
-                                for (uint32_t e = 0; e < 4 && col + e < p.n; ++e) dst[e] = __float2half_rn(vals[e]);
-                            }
-                        }
-                    }
-                    // leave the counter at zero for the next launch
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (epi_tid == 0) p.tile_counters[seg.tile] = 0;
-                }
+                // the partial tiles of all ranges are summed by streamk_reduce_kernel, launched next
             }
             ++it;
         }
@@ -525,6 +460,77 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         tmem_dealloc<CG>(tmem_base, T::kTmemCols);
     }
     if (threadIdx.x == 32) B200_STAMP(10);
+}
+
+// ------------------------------------------------------------------------------------------
+// Sums the FP32 partial tiles a stream-k launch left in the workspace and writes FP16 C.
+// ------------------------------------------------------------------------------------------
+// grid = (chunks, tiles): block (x, t) handles the x-th share of tile t's live 16-byte words.
+// Tiles that one k-range covered completely were stored by the GEMM kernel itself and are
+// skipped. The contributing ranges are added in range order, so the result does not depend on
+// timing. The partials are laid out row-fastest ([16-byte column word][row]), which makes every
+// load here coalesced; being a kernel of its own, the reduction runs on all SMs at once instead
+// of on whichever CTA happened to finish a tile last.
+struct ReduceParams {
+    const float4 *partials;
+    __half *c;
+    uint32_t m, n;
+    uint32_t m_blocks, n_blocks, k_blocks, tiles, group_m;
+    uint32_t parts;
+    uint32_t bn;
+};
+
+constexpr int kReduceThreads = 256;
+
+__global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const ReduceParams p) {
+    const uint32_t tile = blockIdx.y;
+    const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
+    const uint64_t u0 = static_cast<uint64_t>(tile) * p.k_blocks;
+    const uint32_t part_first = part_of_unit(u0, p.parts, total_units);
+    const uint32_t part_last = part_of_unit(u0 + p.k_blocks - 1, p.parts, total_units);
+    pdl_wait_prior_grids();  // the partials are written by the GEMM kernel launched just before
+    if (part_first == part_last) return;
+
+    const TileCoord tc = tile_coord(tile, p.m_blocks, p.n_blocks, p.group_m);
+    const uint32_t m0 = tc.m_blk * kBM, n0 = tc.n_blk * p.bn;
+    const uint32_t rows_live = (p.m - m0) < static_cast<uint32_t>(kBM) ? (p.m - m0) : kBM;
+    const uint32_t cols_left = p.n - n0;
+    const uint32_t words_per_row = ((cols_left < p.bn ? cols_left : p.bn) + 3u) / 4u;
+    const uint32_t total_words = rows_live * words_per_row;
+    const uint32_t n_parts = part_last - part_first + 1u;
+    const size_t slot_words = static_cast<size_t>(kBM) * p.bn / 4;
+    // the first contributor may have entered this tile from an earlier one (its second slot);
+    // every later contributor starts inside this tile (its first slot)
+    const uint32_t slot_first = partial_slot(part_first, p.parts, p.tiles, p.k_blocks, tile);
+    const bool vec4_ok = (p.n % 4u) == 0;
+
+    for (uint32_t i = blockIdx.x * kReduceThreads + threadIdx.x; i < total_words; i += gridDim.x * kReduceThreads) {
+        const uint32_t w = i / rows_live, r = i - w * rows_live;
+        const size_t off = static_cast<size_t>(w) * kBM + r;
+        float4 acc = ld_cg_f4(p.partials + static_cast<size_t>(slot_first) * slot_words + off);
+        uint32_t k = 1;
+        for (; k + 1 < n_parts; k += 2) {  // two loads in flight per step
+            const float4 v0 = ld_cg_f4(p.partials + static_cast<size_t>(2u * (part_first + k)) * slot_words + off);
+            const float4 v1 = ld_cg_f4(p.partials + static_cast<size_t>(2u * (part_first + k + 1)) * slot_words + off);
+            acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+            acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+        }
+        if (k < n_parts) {
+            const float4 v0 = ld_cg_f4(p.partials + static_cast<size_t>(2u * (part_first + k)) * slot_words + off);
+            acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+        }
+        const uint32_t col = n0 + w * 4u;
+        __half *dst = p.c + static_cast<size_t>(m0 + r) * p.n + col;
+        if (vec4_ok && col + 4u <= p.n) {
+            uint2 v;
+            v.x = pack_half2_rn(__float_as_uint(acc.x), __float_as_uint(acc.y));
+            v.y = pack_half2_rn(__float_as_uint(acc.z), __float_as_uint(acc.w));
+            *reinterpret_cast<uint2 *>(dst) = v;
+        } else {
+            const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (uint32_t e = 0; e < 4 && col + e < p.n; ++e) dst[e] = __float2half_rn(vals[e]);
+        }
+    }
 }
 
 }  // namespace b200

@@ -405,7 +405,6 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
             if (rc != B200_HGEMM_OK) return rc;
             ws = static_cast<uint8_t *>(st.ws);
         }
-        p.tile_counters = reinterpret_cast<uint32_t *>(ws);
         p.partials = reinterpret_cast<float4 *>(ws + kCounterBytes);
         grid = parts;
     } else {
@@ -425,9 +424,58 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
         return launch_kernel<128, 8, 2, kModeTiles>(st, 4, p, grid, stream);
     }
-    if (bn == 256) return launch_kernel<256, 4, 1, kModeStreamK>(st, 5, p, grid, stream);
-    if (bn == 128) return launch_kernel<128, 6, 1, kModeStreamK>(st, 6, p, grid, stream);
-    return launch_kernel<64, 8, 1, kModeStreamK>(st, 7, p, grid, stream);
+    if (bn == 256) {
+        rc = launch_kernel<256, 4, 1, kModeStreamK>(st, 5, p, grid, stream);
+    } else if (bn == 128) {
+        rc = launch_kernel<128, 6, 1, kModeStreamK>(st, 6, p, grid, stream);
+    } else {
+        rc = launch_kernel<64, 8, 1, kModeStreamK>(st, 7, p, grid, stream);
+    }
+    if (rc != B200_HGEMM_OK) return rc;
+
+    // Tiles whose k-range was cut across ranges left FP32 partials behind: sum them. Nothing to do
+    // when every range boundary falls on a tile boundary.
+    const uint32_t parts = grid;
+    const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
+    bool any_split = false;
+    for (uint32_t part = 1; part < parts && !any_split; ++part) {
+        any_split = (unit_begin(part, parts, total_units) % p.k_blocks) != 0;
+    }
+    if (!any_split) return B200_HGEMM_OK;
+    ReduceParams rp;
+    rp.partials = p.partials;
+    rp.c = p.c;
+    rp.m = p.m;
+    rp.n = p.n;
+    rp.m_blocks = p.m_blocks;
+    rp.n_blocks = p.n_blocks;
+    rp.k_blocks = p.k_blocks;
+    rp.tiles = p.tiles;
+    rp.group_m = p.group_m;
+    rp.parts = parts;
+    rp.bn = static_cast<uint32_t>(bn);
+    // enough blocks per tile to put every SM to work, at least one per 2048 words
+    const uint32_t words = 128u * static_cast<uint32_t>(bn) / 4u;
+    uint32_t chunks = (2u * static_cast<uint32_t>(st.sm_count > 0 ? st.sm_count : 148) + p.tiles - 1) / p.tiles;
+    const uint32_t max_chunks = (words + kReduceThreads - 1) / kReduceThreads;
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(chunks, p.tiles, 1);
+    cfg.blockDim = dim3(kReduceThreads, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, streamk_reduce_kernel, rp) != cudaSuccess) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_HGEMM_OK;
 }
 
 static int entry(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_plan *fixed,
