@@ -212,19 +212,46 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     }
 
     const uint64_t pairs256 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 256);
-    if (pairs256 * 100 >= 135ull * (sms / 2)) {
+    const uint64_t pair_slots = sms / 2;
+    if (pairs256 >= 2 * pair_slots) {
+        // two or more full waves of CTA pairs: the tensor-bound regime
         pl->variant = B200_VARIANT_CTA2;
         pl->bn = 256;
         return;
     }
-    pl->variant = B200_VARIANT_CTA1;
-    if (tiles256 >= 64) {
-        pl->bn = 256;
-    } else if (tiles128 >= 64) {
-        pl->bn = 128;
-    } else {
-        pl->bn = 64;
+
+    // Fewer tiles than that: pick by estimated time. Microseconds per 64-wide k-block of one
+    // tile (measured on B200 at 1024..3072: these sizes are bound by the rate at which one SM can
+    // pull operand slabs from L2, not by the tensor pipe), plus a fixed cost per kernel; the
+    // stream-k estimates carry the cost of writing and summing the partial tiles (measured at
+    // 2304 and 2560: 660 and 775 TFLOP/s against 850 and 1030 for whole tiles).
+    struct Candidate {
+        int variant, bn;
+        double us;
+    };
+    const double kb = static_cast<double>(k_blocks);
+    const uint64_t tiles64 = m_blocks * ceil_div_u32(N, 64);
+    auto waves = [](uint64_t work, uint64_t slots) { return static_cast<double>((work + slots - 1) / slots); };
+    // every range leaves up to two FP32 partial tiles, each written once and read once through L2
+    // (about 4 TB/s for this pattern): with full-height tiles that costs more than a ragged last
+    // wave does, so stream-k only wins here when the tiles are few and k is long
+    auto partial_us = [&](int bn) { return 2.0 * sms * 2.0 * (128.0 * bn * 4.0) / 4.0e6; };
+    Candidate cands[6] = {
+        {B200_VARIANT_CTA1, 256, waves(tiles256, sms) * kb * 0.35 + 2.0},
+        {B200_VARIANT_CTA1, 128, waves(tiles128, sms) * kb * 0.33 + 1.5},
+        {B200_VARIANT_CTA1, 64, waves(tiles64, sms) * kb * 0.30 + 1.2},
+        {B200_VARIANT_CTA2, 256, waves(pairs256, pair_slots) * kb * 0.37 + 2.0},
+        {B200_VARIANT_STREAMK, 256, static_cast<double>(tiles256) * kb / sms * 0.35 + 4.0 + partial_us(256)},
+        {B200_VARIANT_STREAMK, 128, static_cast<double>(tiles128) * kb / sms * 0.33 + 4.0 + partial_us(128)},
+    };
+    if (M % 256 != 0) cands[3].us *= 1.0 + 128.0 / static_cast<double>(M);  // the pair's second CTA idles on the last rows
+    if (k_blocks < 16) cands[4].us = cands[5].us = 1e30;                    // too little k to split
+    int best = 0;
+    for (int i = 1; i < 6; ++i) {
+        if (cands[i].us < cands[best].us * 0.98) best = i;  // earlier entries win ties: fewer moving parts
     }
+    pl->variant = cands[best].variant;
+    pl->bn = cands[best].bn;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -454,11 +481,10 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     rp.group_m = p.group_m;
     rp.parts = parts;
     rp.bn = static_cast<uint32_t>(bn);
-    // enough blocks per tile to put every SM to work, at least one per 2048 words
+    // One or two 16-byte words per thread: the sum over ranges is a chain of dependent-latency
+    // loads, so the kernel gets its bandwidth from many resident threads, not from long loops.
     const uint32_t words = 128u * static_cast<uint32_t>(bn) / 4u;
-    uint32_t chunks = (2u * static_cast<uint32_t>(st.sm_count > 0 ? st.sm_count : 148) + p.tiles - 1) / p.tiles;
-    const uint32_t max_chunks = (words + kReduceThreads - 1) / kReduceThreads;
-    if (chunks > max_chunks) chunks = max_chunks;
+    uint32_t chunks = (words + 2u * kReduceThreads - 1) / (2u * kReduceThreads);
     if (chunks < 1) chunks = 1;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
