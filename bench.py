@@ -300,6 +300,14 @@ def dist_setup(torch, n_gpus):
     return rank, world, local
 
 
+def dist_teardown(world):
+    if world > 1:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
 def barrier(torch, world):
     if world > 1:
         import torch.distributed as dist
@@ -334,10 +342,19 @@ def run_ours(args):
     C = torch.empty((hi - lo, N), dtype=torch.float16, device=device)
     rows = hi - lo
     plan = api.select_plan(rows, N, K) if rows else None
+    # Operands that fit in the 126 MB L2 (the decode-style shapes: B is 117 MB) would be served from
+    # L2 on every step after the first: cycle through enough copies of B to exceed L2 several times.
+    small = (rows * K + N * K + rows * N) * 2 < (512 << 20)
+    Bs = [B]
+    if small:
+        while len(Bs) * N * K * 2 < (768 << 20) and len(Bs) < 64:
+            Bs.append(B.clone())
+    counter = [0]
 
     def step():
         if rows:
-            api.b200Hgemm(A, B, C)
+            api.b200Hgemm(A, Bs[counter[0] % len(Bs)], C)
+            counter[0] += 1
 
     # ---- device-resident timing: the headline kernel number ----
     preheat(torch, step)
@@ -379,9 +396,29 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(torch, (time.perf_counter() - t0) / e2e_steps, world, device)
     barrier(torch, world)
+    if rows:
+        api.b200Hgemm(A, B, C)
+        torch.cuda.synchronize()
     e2e_ok = bool(torch.equal(hC.to(device), C)) if rows else True
 
+    # ---- optional: all-gather of the C slabs (never part of the multiply; timed on its own) ----
+    gather_ms = None
+    if world > 1 and args.gather:
+        from cuda_hgemm_b200 import multi_gpu
+
+        for _ in range(2):
+            multi_gpu.allgather_c(C, M, N)
+        barrier(torch, world)
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            multi_gpu.allgather_c(C, M, N)
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = max_over_ranks(torch, g0.elapsed_time(g1) / 5, world, device)
+
     if rank != 0:
+        dist_teardown(world)
         return
     peaks = measured_peaks()
     flops_launch = 2.0 * rows * N * K
@@ -400,8 +437,8 @@ def run_ours(args):
         "data": f"synthetic: FP16 {dist_name} from seed {SEED}",
         "config": {"workload": f"{args.workload}: {desc}", "M": M, "N": N, "K": K,
                    "partition": f"{world} row slab(s) of C, B replicated, no collective",
-                   "l2": "operands larger than L2 (A, B, C slabs >= 64 MiB each)" if rows * K * 2 + N * K * 2 > (126 << 20)
-                   else "operands fit in L2; B rotated is not applied (see skinny workloads in profiles/)",
+                   "l2": (f"B cycled through {len(Bs)} distinct copies ({len(Bs) * N * K * 2 >> 20} MiB in total) so that no step "
+                          "finds its operands in L2") if len(Bs) > 1 else "operands larger than L2",
                    "plan": plan.as_dict() if plan else None},
         "gpu_launches": int(launches_timed),
         "pct_fp16_dense_peak": round(100.0 * value / (NOMINAL_FP16_DENSE_TFLOPS * world), 2),
@@ -419,7 +456,13 @@ def run_ours(args):
         Cc = torch.empty_like(C)
         for key, sym in (("cublas_fp16_compute_tflops", "hgemm_compare_cublas_fp16"),
                          ("cublas_fp32_compute_tflops", "hgemm_compare_cublas_fp32")):
-            ms = time_launches(torch, cublas_callable(torch, cmp_lib, sym, A, B, Cc), warmup, steps)
+            calls = [cublas_callable(torch, cmp_lib, sym, A, b, Cc) for b in Bs]  # same rotation of B as ours
+            turn = [0]
+
+            def cublas_step():
+                calls[turn[0] % len(calls)]()
+                turn[0] += 1
+            ms = time_launches(torch, cublas_step, warmup, steps)
             out[key] = round(world * flops_launch / (ms * 1e-3) / 1e12, 2)
         best = max(out["cublas_fp16_compute_tflops"], out["cublas_fp32_compute_tflops"])
         out["vs_cublas_best"] = round(value / best, 4)
@@ -441,7 +484,11 @@ def run_ours(args):
 
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(M, N, K, dist_name)
+    if gather_ms is not None:
+        out["allgather_c"] = {"ms": round(gather_ms, 4), "bytes_received_per_rank": int((M - rows) * N * 2),
+                              "note": "NCCL all-gather of the row slabs into full C on every rank; outside the timed multiply"}
     print(json.dumps(out), flush=True)
+    dist_teardown(world)
 
 
 REF_ENABLED = ("wmmaPadding", "wmmaAsync", "wmmaAsyncPg2s", "wmmaAsyncPg2sPs2r", "wmmaAsyncStage2", "wmmaAsyncStage3",
@@ -534,6 +581,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square16384")
+    ap.add_argument("--gather", action="store_true", help="with N > 1: also time the optional all-gather of C")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra square sizes measured after the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
