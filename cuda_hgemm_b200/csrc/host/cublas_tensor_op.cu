@@ -54,6 +54,30 @@ extern "C" int hgemm_compare_cublas_fp32(const void *A, const void *B, void *C, 
     return static_cast<int>(gemm_fp32_compute(static_cast<cudaStream_t>(stream), static_cast<const half *>(A),
                                               static_cast<const half *>(B), static_cast<half *>(C), M, N, K));
 }
+
+// Times `iters` back-to-back calls of any GEMM entry point of the C-ABI shape after `warmup`
+// calls, between two events on `stream`: the reference driver's protocol
+// (src/common/tester.h:59-64,89-95) without an interpreter in the loop. Returns mean
+// milliseconds per call, or a negative value when a call or a CUDA function failed.
+typedef int (*hgemm_entry_fn)(const void *, const void *, void *, size_t, size_t, size_t, void *);
+
+extern "C" double hgemm_compare_time_loop(hgemm_entry_fn fn, const void *A, const void *B, void *C, size_t M, size_t N,
+                                          size_t K, int warmup, int iters, void *stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return -1.0;
+    double result = -1.0;
+    bool ok = true;
+    for (int i = 0; i < warmup && ok; ++i) ok = fn(A, B, C, M, N, K, stream) == 0;
+    ok = ok && cudaEventRecord(e0, s) == cudaSuccess;
+    for (int i = 0; i < iters && ok; ++i) ok = fn(A, B, C, M, N, K, stream) == 0;
+    ok = ok && cudaEventRecord(e1, s) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+    float ms = 0.f;
+    if (ok && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess && iters > 0) result = static_cast<double>(ms) / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return result;
+}
 #else
 void cublasTensorOp(half *A, half *B, half *C, size_t M, size_t N, size_t K) {
     HGEMM_CHECK_CUBLAS_ERROR(gemm_fp16_compute(nullptr, A, B, C, M, N, K));
