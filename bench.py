@@ -156,6 +156,8 @@ def preheat(torch, fn, seconds=PREHEAT_S):
     """Untimed calls for about `seconds` of GPU time: clocks ramp up from idle and then settle under
     the power cap within the first tens of milliseconds of a dense GEMM, so a short timed region that
     starts cold measures that transient, not the kernel. Applied to every library measured, alike."""
+    fn()  # first call pays one-time set-up (module load, attributes, tensor maps): not representative
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     fn()
