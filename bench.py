@@ -212,7 +212,8 @@ def time_graph(torch, fn, launches=20, replays=5):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
 # captures under profiles/, keyed by workload; scaled captures say so there.
 NCU_TRAFFIC_BYTES = {
-    "square8192": 1.168e9,
+    "square8192": 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
+    "skinny16": 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
 }
 
 

@@ -143,10 +143,7 @@ __device__ __forceinline__ void store_row_chunk32(__half *c, uint32_t row, uint3
     }
 }
 
-// PDL = true compiles in the programmatic-dependent-launch hand-shake (griddepcontrol); the
-// PDL = false twin is the same kernel without those two instructions, for launches made without
-// the attribute (profilers that replay kernels skip the PDL build).
-template <int BN, int STAGES, int CG, int MODE, bool PDL>
+template <int BN, int STAGES, int CG, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     using T = KernelTraits<BN, STAGES, CG>;
     static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
@@ -213,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     }
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = (CG == 1 && warp == 0) ? 0u : *tmem_slot;
-    if (PDL) pdl_launch_dependents();
+    pdl_launch_dependents();
     if (threadIdx.x == 0) B200_STAMP(1);
 
     if (warp == 0) {
@@ -226,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
 #ifdef B200_TIMELINE
             bool stamped_first_load = false;
 #endif
-            if (PDL) pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
+            pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
             while (ok && work.next(seg)) {
                 const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
                 const int32_t row_a = static_cast<int32_t>((tc.m_blk * CG + cta_rank) * kBM);
@@ -327,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         WorkWalker<MODE> work(p, worker, workers);
         Segment seg;
         uint32_t it = 0, store_buf = 0;
-        if (PDL) pdl_wait_prior_grids();  // C and the workspace may still be in use by the previous kernel
+        pdl_wait_prior_grids();  // C and the workspace may still be in use by the previous kernel
         while (work.next(seg)) {
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;
@@ -485,14 +482,13 @@ struct ReduceParams {
 
 constexpr int kReduceThreads = 256;
 
-template <bool PDL>
 __global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const ReduceParams p) {
     const uint32_t tile = blockIdx.y;
     const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
     const uint64_t u0 = static_cast<uint64_t>(tile) * p.k_blocks;
     const uint32_t part_first = part_of_unit(u0, p.parts, total_units);
     const uint32_t part_last = part_of_unit(u0 + p.k_blocks - 1, p.parts, total_units);
-    if (PDL) pdl_wait_prior_grids();  // the partials are written by the GEMM kernel launched just before
+    pdl_wait_prior_grids();  // the partials are written by the GEMM kernel launched just before
     if (part_first == part_last) return;
 
     const TileCoord tc = tile_coord(tile, p.m_blocks, p.n_blocks, p.group_m);

@@ -257,18 +257,17 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
 // ------------------------------------------------------------------------------------------
 // launch
 // ------------------------------------------------------------------------------------------
-// Programmatic dependent launch is on unless B200_HGEMM_NO_PDL is set in the environment
-// (Nsight Compute's kernel replay skips kernels that contain the hand-shake; profiling runs set it
-// and get the twin instantiation without it).
+// Programmatic dependent launch is on unless B200_HGEMM_NO_PDL is set in the environment (for
+// A/B measurements; without the launch attribute the kernels' griddepcontrol instructions do nothing).
 static bool pdl_enabled() {
     static const bool on = (getenv("B200_HGEMM_NO_PDL") == nullptr);
     return on;
 }
 
-template <int BN, int STAGES, int CG, int MODE, bool PDL>
-static int launch_kernel_impl(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
+template <int BN, int STAGES, int CG, int MODE>
+static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
     using T = KernelTraits<BN, STAGES, CG>;
-    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE, PDL>;
+    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -289,7 +288,7 @@ static int launch_kernel_impl(DeviceState &st, int attr_slot, const GemmParams &
     // programmatic dependent launch: the kernel's prologue (barrier set-up, tensor-memory
     // allocation) may overlap the tail of the previous kernel in the stream; every global
     // access inside the kernel comes after griddepcontrol.wait
-    if (PDL) {
+    if (pdl_enabled()) {
         attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
         ++n_attrs;
@@ -326,12 +325,6 @@ static int launch_kernel_impl(DeviceState &st, int attr_slot, const GemmParams &
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return B200_HGEMM_OK;
-}
-
-template <int BN, int STAGES, int CG, int MODE>
-static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
-    if (pdl_enabled()) return launch_kernel_impl<BN, STAGES, CG, MODE, true>(st, attr_slot, p, grid, stream);
-    return launch_kernel_impl<BN, STAGES, CG, MODE, false>(st, attr_slot + 8, p, grid, stream);
 }
 
 static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, size_t K, const b200_hgemm_plan &pl) {
@@ -512,9 +505,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    const cudaError_t reduce_rc = pdl_enabled() ? cudaLaunchKernelEx(&cfg, streamk_reduce_kernel<true>, rp)
-                                                : cudaLaunchKernelEx(&cfg, streamk_reduce_kernel<false>, rp);
-    if (reduce_rc != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, streamk_reduce_kernel, rp) != cudaSuccess) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
     }
