@@ -172,19 +172,22 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     const uint32_t workers = gridDim.x / CG;
 
     if (threadIdx.x == 0) B200_STAMP(0);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar + 8u * s, 1);
-            mbar_init(empty_bar + 8u * s, 1);
-        }
-        for (int a = 0; a < 2; ++a) {
+    if (warp == 0) {
+        // one lane per barrier: the set-up of the producer warp is a serial chain otherwise
+        if (lane < static_cast<uint32_t>(STAGES)) {
+            mbar_init(full_bar + 8u * lane, 1);
+            mbar_init(empty_bar + 8u * lane, 1);
+        } else if (lane < static_cast<uint32_t>(STAGES) + 2u) {
+            const uint32_t a = lane - STAGES;
             mbar_init(tfull_bar + 8u * a, 1);
             mbar_init(tempty_bar + 8u * a, 4 * CG);  // one arrival per epilogue warp of every CTA of the pair
+        } else if (lane == static_cast<uint32_t>(STAGES) + 2u) {
+            *abort_flag = 0;
         }
-        *abort_flag = 0;
         fence_mbar_init();
+        __syncwarp();
     }
-    if (warp == 0 && lane == 0) {
+    if (warp == 2 && lane == 0) {
         tma_prefetch_desc(&p.tm_a);
         tma_prefetch_desc(&p.tm_b);
         if (p.tma_store) tma_prefetch_desc(&p.tm_c);
@@ -347,12 +350,21 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             if (whole_tile) {
                 if (p.tma_store) {
                     const bool warp_rows_live = (m0 + q * 32u) < p.m;
-#pragma unroll 1
-                    for (uint32_t c = 0; c < BN / 64; ++c) {
-                        uint32_t r0[32], r1[32];
-                        tmem_ld_32x32b_x32(taddr + c * 64u, r0);
-                        tmem_ld_32x32b_x32(taddr + c * 64u + 32u, r1);
+                    constexpr uint32_t kChunks = BN / 64;
+                    // Two register sets: the TMEM load of chunk c+1 is in flight while chunk c is
+                    // converted, staged and handed to TMA.
+                    uint32_t ra[64], rb[64];
+                    tmem_ld_32x32b_x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(ra));
+                    tmem_ld_32x32b_x32(taddr + 32u, *reinterpret_cast<uint32_t(*)[32]>(ra + 32));
+#pragma unroll
+                    for (uint32_t c = 0; c < kChunks; ++c) {
+                        uint32_t *cur = (c & 1u) ? rb : ra;
+                        uint32_t *nxt = (c & 1u) ? ra : rb;
                         tmem_ld_wait();
+                        if (c + 1 < kChunks) {
+                            tmem_ld_32x32b_x32(taddr + (c + 1) * 64u, *reinterpret_cast<uint32_t(*)[32]>(nxt));
+                            tmem_ld_32x32b_x32(taddr + (c + 1) * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(nxt + 32));
+                        }
                         const bool live = warp_rows_live && (n0 + c * 64u) < p.n;
                         if (live) {
                             uint8_t *buf = my_staging_ptr + (store_buf & 1u) * 4096u;
@@ -361,22 +373,14 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                             __syncwarp();
                             uint8_t *row_ptr = buf + lane * 128u;
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
+                            for (uint32_t j = 0; j < 8; ++j) {
                                 uint4 v;
-                                v.x = pack_half2_rn(r0[8 * j + 0], r0[8 * j + 1]);
-                                v.y = pack_half2_rn(r0[8 * j + 2], r0[8 * j + 3]);
-                                v.z = pack_half2_rn(r0[8 * j + 4], r0[8 * j + 5]);
-                                v.w = pack_half2_rn(r0[8 * j + 6], r0[8 * j + 7]);
+                                v.x = pack_half2_rn(cur[8 * j + 0], cur[8 * j + 1]);
+                                v.y = pack_half2_rn(cur[8 * j + 2], cur[8 * j + 3]);
+                                v.z = pack_half2_rn(cur[8 * j + 4], cur[8 * j + 5]);
+                                v.w = pack_half2_rn(cur[8 * j + 6], cur[8 * j + 7]);
+                                // 128-byte swizzle: 16-byte word j of row r lives at word j ^ (r % 8)
                                 *reinterpret_cast<uint4 *>(row_ptr + ((j ^ (lane & 7u)) << 4)) = v;
-                            }
-#pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
-                                uint4 v;
-                                v.x = pack_half2_rn(r1[8 * j + 0], r1[8 * j + 1]);
-                                v.y = pack_half2_rn(r1[8 * j + 2], r1[8 * j + 3]);
-                                v.z = pack_half2_rn(r1[8 * j + 4], r1[8 * j + 5]);
-                                v.w = pack_half2_rn(r1[8 * j + 6], r1[8 * j + 7]);
-                                *reinterpret_cast<uint4 *>(row_ptr + (((j + 4u) ^ (lane & 7u)) << 4)) = v;
                             }
                             fence_proxy_async_smem();
                             __syncwarp();
