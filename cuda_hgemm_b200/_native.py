@@ -35,6 +35,7 @@ VARIANT_CTA1 = 0
 VARIANT_CTA2 = 1
 VARIANT_STREAMK = 2
 VARIANT_SIMT = 3
+VARIANT_CTA2_MCAST = 4
 
 
 class Plan(Structure):

@@ -18,6 +18,8 @@ LIB_DIR = PKG / "lib"
 BIN_DIR = PKG / "bin"
 LIB_SO = LIB_DIR / "libb200_hgemm.so"
 COMPARE_SO = LIB_DIR / "libhgemm_compare.so"
+MULTICAST_SO = LIB_DIR / "libb200_hgemm_mc.so"
+MULTICAST_SRC = CSRC / "mc" / "gemm_multicast.cu"
 DRIVER_BIN = BIN_DIR / "hgemm"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -52,6 +54,20 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         cmd.insert(2, "-v")
     subprocess.run(cmd, check=True)
     return LIB_SO
+
+
+def build_multicast(force: bool = False) -> Path | None:
+    """nvcc -> lib/libb200_hgemm_mc.so, the single-GPU companion with the cluster-multicast kernel.
+    Its source is not shipped to multi-GPU runs; without it there is nothing to build."""
+    if not MULTICAST_SRC.exists():
+        return None
+    if not force and _up_to_date(MULTICAST_SO, [MULTICAST_SRC, *_lib_sources()]):
+        return MULTICAST_SO
+    LIB_DIR.mkdir(exist_ok=True)
+    cmd = [nvcc(), *COMMON_FLAGS, "--shared", "-Xcompiler", "-fPIC", "-cudart", "static",
+           "-o", str(MULTICAST_SO), str(MULTICAST_SRC)]
+    subprocess.run(cmd, check=True)
+    return MULTICAST_SO
 
 
 def _host_sources():
@@ -89,6 +105,8 @@ def build_driver(force: bool = False) -> Path:
 def main(argv) -> int:
     force = "--force" in argv
     print("built", build_library(force=force, verbose="-v" in argv))
+    mc = build_multicast(force=force)
+    print("built" if mc else "no multicast source; skipped", mc or "")
     if (CSRC / "host" / "cublas_tensor_op.cu").exists():
         print("built", build_compare(force=force))
     if (CSRC / "host" / "main.cu").exists():

@@ -49,14 +49,17 @@ enum {
     B200_VARIANT_CTA1 = 0,    /* tcgen05.mma cta_group::1, whole tiles, persistent */
     B200_VARIANT_CTA2 = 1,    /* tcgen05.mma cta_group::2 (CTA pair on a 256-row tile) */
     B200_VARIANT_STREAMK = 2, /* cta_group::1, k-ranges split across CTAs, FP32 workspace reduce */
-    B200_VARIANT_SIMT = 3     /* CUDA-core kernel for shapes the tensor path rejects (K % 8 != 0) */
+    B200_VARIANT_SIMT = 3,    /* CUDA-core kernel for shapes the tensor path rejects (K % 8 != 0) */
+    B200_VARIANT_CTA2_MCAST = 4 /* CTA pairs in clusters of four with the A slab delivered by TMA multicast;
+                                   single-GPU builds only: it lives in libb200_hgemm_mc.so, which the library
+                                   loads when present (B200_HGEMM_ERR_UNSUPPORTED otherwise); needs N % 8 == 0 */
 };
 
 /* The dispatch decision for one shape. All fields are filled by b200_hgemm_select(); a
  * caller may edit them and pass the plan to b200_hgemm_ex(). */
 typedef struct b200_hgemm_plan {
     int32_t variant;   /* B200_VARIANT_* */
-    int32_t bn;        /* tile width in N: 64, 128 or 256 (tile height is 128, or 256 per CTA pair) */
+    int32_t bn;        /* tile width in N: 64, 128 or 256 (tile height is 128, or 256 per CTA pair; CTA2_MCAST: 256) */
     int32_t parts;     /* STREAMK: number of equal k-ranges = CTAs launched; 0 = one per SM */
     int32_t group_m;   /* rasterisation band height in row blocks; 0 = library default */
     int32_t tma_store; /* 1: epilogue writes C with TMA stores (needs N % 8 == 0); 0: plain stores */

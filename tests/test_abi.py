@@ -88,7 +88,7 @@ def test_plan_selection_covers_the_benchmark_shapes(native_lib):
     from cuda_hgemm_b200 import api
 
     big = api.select_plan(8192, 8192, 8192)
-    assert big.variant in (_native.VARIANT_CTA1, _native.VARIANT_CTA2) and big.bn == 256
+    assert big.variant in (_native.VARIANT_CTA1, _native.VARIANT_CTA2, _native.VARIANT_CTA2_MCAST) and big.bn == 256
     # decode shapes: 112 whole tiles cover most SMs at N = 14336; at N = 4096 the k-range is split
     assert api.select_plan(16, 14336, 4096).variant == _native.VARIANT_CTA1
     skinny = api.select_plan(16, 4096, 14336)

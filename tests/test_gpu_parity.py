@@ -98,6 +98,23 @@ def test_cta_pair_tiles(cuda_device, shape, bn):
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta2 bn={bn} {shape}")
 
 
+@pytest.mark.parametrize("shape", [(256, 512, 64), (256, 256, 320), (328, 776, 136), (1024, 2048, 1024), (2304, 2560, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_cluster_multicast_pairs(cuda_device, shape):
+    """The single-GPU companion kernel: CTA pairs in clusters of four, A slabs delivered by TMA multicast."""
+    from cuda_hgemm_b200 import build
+
+    if not build.MULTICAST_SO.exists():
+        pytest.skip("libb200_hgemm_mc.so is not part of this run (it is left out on multi-GPU runs)")
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=12)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2_MCAST, 256))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"multicast pairs {shape}")
+    # same products in the same order as the plain pair kernel: bit-identical results
+    C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2, 256))
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
 @pytest.mark.parametrize("parts", [0, 1, 7, 33, 148, 400])
 @pytest.mark.parametrize("bn", [64, 128, 256])
 def test_stream_k_ranges(cuda_device, bn, parts):
