@@ -63,7 +63,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.01):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
