@@ -15,6 +15,7 @@
 #include <atomic>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/b200_hgemm.h"
 #include "gemm_kernel.cuh"
@@ -50,10 +51,17 @@ struct DeviceState {
     bool sm100 = false;
     int sm_count = 0;
     uint32_t *error_word = nullptr;
-    // split-k workspace: [tile counters | FP32 partial slots]
+    // stream-k workspace [64 KiB header | FP32 partial slots]: either one the caller handed over
+    // (ws), or one per stream that the library allocates and grows itself, so that GEMMs running
+    // on different streams at the same time never share partial-tile slots
     void *ws = nullptr;
     size_t ws_bytes = 0;
-    bool ws_owned = false;
+    struct StreamWorkspace {
+        cudaStream_t stream;
+        void *ptr;
+        size_t bytes;
+    };
+    std::vector<StreamWorkspace> owned_ws;
     // staging buffers of the host-pointer entry point
     void *host_a = nullptr, *host_b = nullptr, *host_c = nullptr;
     size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
@@ -364,24 +372,41 @@ static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, si
     return kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * pl.bn * sizeof(float));
 }
 
-static int ensure_workspace(DeviceState &st, size_t need) {
+constexpr size_t kMaxStreamWorkspaces = 64;
+
+// The workspace a stream-k launch on `stream` may use: the caller's when one was handed over,
+// else this stream's own, allocated or grown here (cudaMalloc / cudaFree: never during capture).
+static int workspace_for(DeviceState &st, cudaStream_t stream, size_t need, uint8_t **out) {
     std::lock_guard<std::mutex> lock(st.mu);
-    if (st.ws && st.ws_bytes >= need) return B200_HGEMM_OK;
-    if (st.ws && !st.ws_owned) return B200_HGEMM_ERR_WORKSPACE;  // caller-provided and too small
-    if (need > kMaxOwnedWorkspace) return B200_HGEMM_ERR_WORKSPACE;
     if (st.ws) {
-        if (cudaFree(st.ws) != cudaSuccess) return B200_HGEMM_ERR_CUDA;  // synchronises the device
-        st.ws = nullptr;
-        st.ws_bytes = 0;
+        if (st.ws_bytes < need) return B200_HGEMM_ERR_WORKSPACE;  // caller-provided and too small
+        *out = static_cast<uint8_t *>(st.ws);
+        return B200_HGEMM_OK;
     }
-    size_t bytes = need < (size_t(32) << 20) ? (size_t(32) << 20) : need;
-    if (cudaMalloc(&st.ws, bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return B200_HGEMM_ERR_WORKSPACE;
+    if (need > kMaxOwnedWorkspace) return B200_HGEMM_ERR_WORKSPACE;
+    DeviceState::StreamWorkspace *slot = nullptr;
+    for (auto &w : st.owned_ws) {
+        if (w.stream == stream) slot = &w;
     }
-    if (cudaMemset(st.ws, 0, kCounterBytes) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
-    st.ws_bytes = bytes;
-    st.ws_owned = true;
+    if (!slot) {
+        if (st.owned_ws.size() >= kMaxStreamWorkspaces) return B200_HGEMM_ERR_WORKSPACE;
+        st.owned_ws.push_back({stream, nullptr, 0});
+        slot = &st.owned_ws.back();
+    }
+    if (slot->bytes < need) {
+        if (slot->ptr) {
+            if (cudaFree(slot->ptr) != cudaSuccess) return B200_HGEMM_ERR_CUDA;  // synchronises the device
+            slot->ptr = nullptr;
+            slot->bytes = 0;
+        }
+        const size_t bytes = need < (size_t(32) << 20) ? (size_t(32) << 20) : need;
+        if (cudaMalloc(&slot->ptr, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return B200_HGEMM_ERR_WORKSPACE;
+        }
+        slot->bytes = bytes;
+    }
+    *out = static_cast<uint8_t *>(slot->ptr);
     return B200_HGEMM_OK;
 }
 
@@ -491,9 +516,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
             if (ws_override_bytes < need) return B200_HGEMM_ERR_WORKSPACE;
             ws = static_cast<uint8_t *>(ws_override);
         } else {
-            rc = ensure_workspace(st, need);
+            rc = workspace_for(st, stream, need, &ws);
             if (rc != B200_HGEMM_OK) return rc;
-            ws = static_cast<uint8_t *>(st.ws);
         }
         p.partials = reinterpret_cast<float4 *>(ws + kCounterBytes);
         grid = parts;
@@ -805,12 +829,8 @@ int b200_hgemm_set_workspace(void *workspace, size_t bytes) {
         return B200_HGEMM_ERR_WORKSPACE;
     }
     std::lock_guard<std::mutex> lock(st->mu);
-    if (st->ws && st->ws_owned) {
-        if (cudaFree(st->ws) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
-    }
     st->ws = workspace;
     st->ws_bytes = workspace ? bytes : 0;
-    st->ws_owned = false;
     return B200_HGEMM_OK;
 }
 
@@ -824,12 +844,7 @@ int b200_hgemm_last_device_error(void) {
     if (cudaMemcpy(&word, st->error_word, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess) {
         return B200_HGEMM_ERR_CUDA;
     }
-    if (word != 0) {
-        cudaMemset(st->error_word, 0, sizeof(word));
-        // a kernel that gave up may have left tile counters half-counted
-        std::lock_guard<std::mutex> lock(st->mu);
-        if (st->ws) cudaMemset(st->ws, 0, kCounterBytes);
-    }
+    if (word != 0) cudaMemset(st->error_word, 0, sizeof(word));
     return static_cast<int>(word);
 }
 
@@ -880,6 +895,11 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     if (rc != B200_HGEMM_OK) return rc;
     if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
     const size_t a_bytes = M * K * sizeof(__half), b_bytes = N * K * sizeof(__half), c_bytes = M * N * sizeof(__half);
+    // one host-pointer GEMM per device at a time: the staging buffers and the two streams are shared
+    static std::mutex host_call_mu[kMaxDevices];
+    int host_dev = 0;
+    if (cudaGetDevice(&host_dev) != cudaSuccess || host_dev < 0 || host_dev >= kMaxDevices) return B200_HGEMM_ERR_CUDA;
+    std::lock_guard<std::mutex> host_lock(host_call_mu[host_dev]);
     {
         std::lock_guard<std::mutex> lock(st->mu);
         if ((rc = grow(&st->host_a, &st->host_a_bytes, a_bytes)) != B200_HGEMM_OK) return rc;

@@ -115,9 +115,11 @@ int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan);
 /* Bytes of device workspace `plan` needs for this shape (0 for whole-tile variants). */
 size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan);
 
-/* Hands the library a caller-owned, zero-initialised device workspace for the current device
- * (256-byte aligned). With no workspace set the library allocates and grows its own on
- * first need (cudaMalloc outside any stream capture). Pass (NULL, 0) to go back to that. */
+/* Hands the library a caller-owned device workspace for the current device (256-byte aligned);
+ * every stream-k call on that device then uses it, so such calls must be ordered with respect to
+ * each other. With no workspace set the library keeps one workspace per stream, allocated and
+ * grown on first need (cudaMalloc outside any stream capture), and calls on different streams
+ * may overlap freely. Pass (NULL, 0) to go back to that. */
 int b200_hgemm_set_workspace(void *workspace, size_t bytes);
 
 /* Synchronises the current device and returns the device-side error word (0 = none,

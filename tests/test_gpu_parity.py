@@ -273,3 +273,44 @@ def test_error_codes_on_device(cuda_device):
     assert lib.b200_hgemm_set_workspace(None, 0) == 0
     torch.cuda.synchronize()
     assert api.last_device_error() == 0
+
+
+def test_concurrent_streams_and_threads_do_not_share_scratch(cuda_device):
+    """Stream-k GEMMs issued from several host threads on several streams at once: every stream has
+    its own partial-tile workspace, so the results are those of the same calls made one by one."""
+    import threading
+
+    import torch
+
+    shapes = [(64, 2048, 4096), (128, 1024, 8192), (200, 1032, 1096), (16, 3584, 2048)]
+    jobs = []
+    for i, (M, N, K) in enumerate(shapes):
+        A, B = make_inputs(M, N, K, seed=30 + i, dist="normal")
+        dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+        expect = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+        api.b200HgemmStreamK(dA, dB, expect)
+        jobs.append((dA, dB, expect, torch.cuda.Stream(device=cuda_device)))
+    torch.cuda.synchronize()
+    outs = [torch.full_like(j[2], float("nan")) for j in jobs]
+    errors = []
+
+    def worker(idx):
+        try:
+            dA, dB, _, stream = jobs[idx]
+            with torch.cuda.stream(stream):
+                for _ in range(20):
+                    api.b200HgemmStreamK(dA, dB, outs[idx])
+            stream.synchronize()
+        except Exception as exc:  # surfaced below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(jobs))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    assert not errors, errors
+    assert api.last_device_error() == 0
+    for (dA, dB, expect, _), out in zip(jobs, outs):
+        assert torch.equal(out, expect)
