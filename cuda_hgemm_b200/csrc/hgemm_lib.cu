@@ -80,6 +80,16 @@ extern "C" void b200_debug_set_timeline(unsigned long long *buf) { g_timeline = 
 #endif
 static std::atomic<uint64_t> g_launches{0};
 
+// With B200_HGEMM_DEBUG set in the environment, every failing CUDA call is named on stderr
+// (the C ABI itself only returns B200_HGEMM_ERR_CUDA).
+static bool cuda_ok(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return true;
+    static const bool verbose = (getenv("B200_HGEMM_DEBUG") != nullptr);
+    if (verbose) fprintf(stderr, "[b200_hgemm] %s failed: %s\n", what, cudaGetErrorString(e));
+    cudaGetLastError();
+    return false;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -99,8 +109,17 @@ static EncodeTiledFn encode_tiled_fn() {
 
 static int current_state(DeviceState **out) {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return B200_HGEMM_ERR_CUDA;
     if (dev < 0 || dev >= kMaxDevices) return B200_HGEMM_ERR_CUDA;
+    // The tensor-map encoder is a driver call and wants a context current on the calling thread; a
+    // thread that has made no runtime call yet has none. Binding the device's primary context
+    // once per thread (and again when the thread switches device) costs nothing afterwards.
+    static thread_local int bound_dev = -1;
+    if (bound_dev != dev) {
+        if (!cuda_ok(cudaSetDevice(dev), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaFree(nullptr), "cudaFree(nullptr)")) return B200_HGEMM_ERR_CUDA;
+        bound_dev = dev;
+    }
     DeviceState &st = g_dev[dev];
     std::lock_guard<std::mutex> lock(st.mu);
     if (!st.probed) {
@@ -112,8 +131,8 @@ static int current_state(DeviceState **out) {
         st.sm100 = (major == 10);
         st.sm_count = sms;
         if (st.sm100) {
-            if (cudaMalloc(&st.error_word, 256) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
-            if (cudaMemset(st.error_word, 0, 256) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+            if (!cuda_ok(cudaMalloc(&st.error_word, 256), "cudaMalloc")) return B200_HGEMM_ERR_CUDA;
+            if (!cuda_ok(cudaMemset(st.error_word, 0, 256), "cudaMemset")) return B200_HGEMM_ERR_CUDA;
         }
         st.probed = true;
     }
@@ -147,6 +166,7 @@ static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint6
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         slot.used = false;
+        if (getenv("B200_HGEMM_DEBUG")) fprintf(stderr, "[b200_hgemm] cuTensorMapEncodeTiled failed: CUresult %d\n", static_cast<int>(r));
         return B200_HGEMM_ERR_CUDA;
     }
     slot.used = true;
@@ -309,7 +329,7 @@ static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, ui
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) != cudaSuccess) {
+            if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes), "cudaFuncSetAttribute")) {
                 return B200_HGEMM_ERR_CUDA;
             }
             st.attr_set[attr_slot] = true;
@@ -357,7 +377,7 @@ static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, ui
             cfg.gridDim = dim3(grid, 1, 1);
         }
     }
-    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
+    if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, p), "cudaLaunchKernelEx")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
     }
@@ -395,12 +415,12 @@ static int workspace_for(DeviceState &st, cudaStream_t stream, size_t need, uint
     }
     if (slot->bytes < need) {
         if (slot->ptr) {
-            if (cudaFree(slot->ptr) != cudaSuccess) return B200_HGEMM_ERR_CUDA;  // synchronises the device
+            if (!cuda_ok(cudaFree(slot->ptr), "cudaFree")) return B200_HGEMM_ERR_CUDA;  // synchronises the device
             slot->ptr = nullptr;
             slot->bytes = 0;
         }
         const size_t bytes = need < (size_t(32) << 20) ? (size_t(32) << 20) : need;
-        if (cudaMalloc(&slot->ptr, bytes) != cudaSuccess) {
+        if (!cuda_ok(cudaMalloc(&slot->ptr, bytes), "cudaMalloc")) {
             cudaGetLastError();
             return B200_HGEMM_ERR_WORKSPACE;
         }
@@ -429,7 +449,7 @@ static int run_simt(const void *A, const void *B, void *C, size_t M, size_t N, s
     if (grid.y > 65535u) return B200_HGEMM_ERR_UNSUPPORTED;
     hgemm_simt_kernel<<<grid, block, 0, stream>>>(static_cast<const __half *>(A), static_cast<const __half *>(B),
                                                   static_cast<__half *>(C), M, N, K);
-    if (cudaGetLastError() != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaGetLastError(), "cudaGetLastError")) return B200_HGEMM_ERR_CUDA;
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return B200_HGEMM_OK;
 }
@@ -583,7 +603,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, streamk_reduce_kernel, rp) != cudaSuccess) {
+    if (!cuda_ok(cudaLaunchKernelEx(&cfg, streamk_reduce_kernel, rp), "cudaLaunchKernelEx")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
     }
@@ -766,7 +786,7 @@ int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, s
 
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     // the error word and the tile counters have to start at zero
-    if (cudaMemsetAsync(sd.scratch, 0, kStaticHeaderBytes + kCounterBytes, s) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaMemsetAsync(sd.scratch, 0, kStaticHeaderBytes + kCounterBytes, s), "cudaMemsetAsync")) return B200_HGEMM_ERR_CUDA;
 
     b200_hgemm_plan pl;
     memset(&pl, 0, sizeof(pl));
@@ -839,9 +859,9 @@ int b200_hgemm_last_device_error(void) {
     int rc = current_state(&st);
     if (rc != B200_HGEMM_OK) return rc;
     if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
-    if (cudaDeviceSynchronize() != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return B200_HGEMM_ERR_CUDA;
     uint32_t word = 0;
-    if (cudaMemcpy(&word, st->error_word, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    if (!cuda_ok(cudaMemcpy(&word, st->error_word, sizeof(word), cudaMemcpyDeviceToHost), "cudaMemcpy")) {
         return B200_HGEMM_ERR_CUDA;
     }
     if (word != 0) cudaMemset(st->error_word, 0, sizeof(word));
@@ -875,11 +895,11 @@ uint64_t b200_hgemm_launch_count(void) {
 static int grow(void **ptr, size_t *have, size_t need) {
     if (*have >= need) return B200_HGEMM_OK;
     if (*ptr) {
-        if (cudaFree(*ptr) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaFree(*ptr), "cudaFree")) return B200_HGEMM_ERR_CUDA;
         *ptr = nullptr;
         *have = 0;
     }
-    if (cudaMalloc(ptr, need) != cudaSuccess) {
+    if (!cuda_ok(cudaMalloc(ptr, need), "cudaMalloc")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
     }
@@ -915,7 +935,7 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     // B first (every row slab needs all of it), then A and C move in row slabs so that the
     // upload of slab i+1 and the download of slab i-1 overlap the GEMM of slab i.
     cudaStream_t s_up = st->host_stream[0], s_run = st->host_stream[1];
-    if (cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
     size_t slabs = 1;
     if (M >= 2048 && M % 128 == 0) {
         slabs = M >= 8192 ? 8 : 4;
@@ -927,17 +947,17 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
         char *a_dst = static_cast<char *>(st->host_a) + s * rows * K * sizeof(__half);
         char *c_dev = static_cast<char *>(st->host_c) + s * rows * N * sizeof(__half);
         char *c_dst = static_cast<char *>(C_host) + s * rows * N * sizeof(__half);
-        if (cudaMemcpyAsync(a_dst, a_src, rows * K * sizeof(__half), cudaMemcpyHostToDevice, s_up) != cudaSuccess)
+        if (!cuda_ok(cudaMemcpyAsync(a_dst, a_src, rows * K * sizeof(__half), cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync"))
             return B200_HGEMM_ERR_CUDA;
-        if (cudaEventRecord(st->host_event[0], s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
-        if (cudaStreamWaitEvent(s_run, st->host_event[0], 0) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaEventRecord(st->host_event[0], s_up), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaStreamWaitEvent(s_run, st->host_event[0], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
         rc = entry(a_dst, st->host_b, c_dev, rows, N, K, nullptr, -1, s_run);
         if (rc != B200_HGEMM_OK) return rc;
-        if (cudaMemcpyAsync(c_dst, c_dev, rows * N * sizeof(__half), cudaMemcpyDeviceToHost, s_run) != cudaSuccess)
+        if (!cuda_ok(cudaMemcpyAsync(c_dst, c_dev, rows * N * sizeof(__half), cudaMemcpyDeviceToHost, s_run), "cudaMemcpyAsync"))
             return B200_HGEMM_ERR_CUDA;
     }
-    if (cudaStreamSynchronize(s_run) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
-    if (cudaStreamSynchronize(s_up) != cudaSuccess) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaStreamSynchronize(s_run), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaStreamSynchronize(s_up), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     return B200_HGEMM_OK;
 }
 
