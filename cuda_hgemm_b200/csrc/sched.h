@@ -22,18 +22,33 @@ struct TileCoord {
     uint32_t n_blk;
 };
 
-// Linear tile id -> (m_blk, n_blk). Tiles are walked in bands of `group_m` row blocks; inside
-// a band the row block moves fastest, and odd bands walk the columns backwards so the column
-// tiles at a band boundary are still in L2.
+// Linear tile id -> (m_blk, n_blk). Tiles are walked in bands of about `group_m` row blocks;
+// inside a band the row block moves fastest, and odd bands walk the columns backwards so the
+// column tiles at a band boundary are still in L2. The row blocks are spread evenly over the
+// bands (59 row blocks at group_m = 8 give bands of 8,8,8,7,7,7,7,7, not seven of 8 and one of
+// 3): a thin last band would make its waves long and narrow and lose the reuse of A.
 B200_HD TileCoord tile_coord(uint32_t t, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m) {
-    const uint32_t per_band = group_m * n_blocks;
-    const uint32_t band = t / per_band;
-    const uint32_t first_m = band * group_m;
-    const uint32_t rows_here = (m_blocks - first_m < group_m) ? (m_blocks - first_m) : group_m;
-    const uint32_t r = t - band * per_band;
+    const uint32_t bands = (m_blocks + group_m - 1) / group_m;
+    const uint32_t base = m_blocks / bands;   // rows of the shorter bands
+    const uint32_t extra = m_blocks % bands;  // the first `extra` bands have one row more
+    const uint32_t tall_tiles = extra * (base + 1) * n_blocks;
+    uint32_t band, first_m, rows_here, r;
+    if (t < tall_tiles) {
+        rows_here = base + 1;
+        band = t / (rows_here * n_blocks);
+        first_m = band * rows_here;
+        r = t - band * rows_here * n_blocks;
+    } else {
+        rows_here = base;
+        const uint32_t u = t - tall_tiles;
+        const uint32_t b = u / (rows_here * n_blocks);
+        band = extra + b;
+        first_m = extra * (base + 1) + b * rows_here;
+        r = u - b * rows_here * n_blocks;
+    }
     TileCoord c;
     c.m_blk = first_m + r % rows_here;
-    uint32_t n = r / rows_here;
+    const uint32_t n = r / rows_here;
     c.n_blk = (band & 1u) ? (n_blocks - 1u - n) : n;
     return c;
 }
