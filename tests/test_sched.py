@@ -49,3 +49,48 @@ def test_bands_are_even(native_lib):
         sizes.append(h)
         idx += h * n_blocks
     assert sizes == [8, 8, 8, 7, 7, 7, 7, 7]
+
+
+def segments(lib, part, parts, tiles, k_blocks):
+    buf = (ctypes.c_uint32 * (3 * 64))()
+    n = lib.b200_sched_segments(part, parts, tiles, k_blocks, buf, 64)
+    assert n <= 64
+    return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
+
+
+@pytest.mark.parametrize("tiles,k_blocks,parts", [
+    (1, 1, 1), (1, 64, 148), (8, 4, 148), (32, 4, 32), (112, 64, 148), (112, 64, 448), (2, 3, 5), (7, 5, 3),
+    (224, 224, 148), (56, 64, 147), (3, 1000, 148), (4096, 2, 148),
+])
+def test_stream_k_ranges_cover_every_unit_once(native_lib, tiles, k_blocks, parts):
+    parts = min(parts, tiles * k_blocks)
+    covered = {}
+    for part in range(parts):
+        segs = segments(native_lib, part, parts, tiles, k_blocks)
+        partial = [s for s in segs if not (s[1] == 0 and s[2] == k_blocks)]
+        # only the first and the last segment of a range can be partial tiles
+        for s in partial:
+            assert s is segs[0] or s is segs[-1]
+        for tile, kb0, kb1 in segs:
+            assert 0 <= kb0 < kb1 <= k_blocks and tile < tiles
+            for kb in range(kb0, kb1):
+                assert (tile, kb) not in covered
+                covered[(tile, kb)] = part
+    assert len(covered) == tiles * k_blocks
+    sizes = [sum(kb1 - kb0 for _, kb0, kb1 in segments(native_lib, p, parts, tiles, k_blocks)) for p in range(parts)]
+    assert max(sizes) - min(sizes) <= 1  # equal shares
+
+    # contributors and workspace slots
+    first, last = ctypes.c_uint32(), ctypes.c_uint32()
+    for tile in range(min(tiles, 300)):
+        native_lib.b200_sched_contributors(tile, parts, tiles, k_blocks, ctypes.byref(first), ctypes.byref(last))
+        owners = sorted({covered[(tile, kb)] for kb in range(k_blocks)})
+        assert owners == list(range(first.value, last.value + 1))
+    used = set()
+    for part in range(parts):
+        for tile, kb0, kb1 in segments(native_lib, part, parts, tiles, k_blocks):
+            if kb0 == 0 and kb1 == k_blocks:
+                continue
+            slot = native_lib.b200_sched_partial_slot(part, parts, tiles, k_blocks, tile)
+            assert slot // 2 == part and slot not in used
+            used.add(slot)
