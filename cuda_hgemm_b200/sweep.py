@@ -8,7 +8,7 @@ and format (so that tool still works on the output directory) and sweeps every m
 kernel) and ``sweep.md`` (one row per size: cuBLAS in both compute modes, the best reference
 kernel, the new kernels).
 
-    python -m cuda_hgemm_b200.sweep --out gpurun_out/sweep [--ref-lib oracle/_ref/libcuda_hgemm_ref.so]
+    python -m cuda_hgemm_b200.sweep --out sweep_out [--ref-lib oracle/_ref/libcuda_hgemm_ref.so]
 """
 from __future__ import annotations
 
@@ -63,7 +63,7 @@ def summarise(n: int, rows):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--out", default="gpurun_out/sweep")
+    ap.add_argument("--out", default="sweep_out")
     ap.add_argument("--first", type=int, default=256)
     ap.add_argument("--last", type=int, default=16384)
     ap.add_argument("--step", type=int, default=256)
