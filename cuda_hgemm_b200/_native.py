@@ -19,6 +19,7 @@ EXPORTED_SYMBOLS = (
     "b200_hgemm_set_workspace", "b200_hgemm_last_device_error", "b200_hgemm_status_string",
     "b200_hgemm_version", "b200_hgemm_launch_count", "b200_sched_tile_coord", "b200_sched_segments",
     "b200_sched_contributors", "b200_sched_partial_slot", "b200_debug_idesc", "b200_debug_smem_desc",
+    "b200_debug_wait_expiry",
 )
 
 OK = 0
@@ -98,6 +99,8 @@ def load() -> ctypes.CDLL:
     lib.b200_sched_contributors.restype = None
     lib.b200_sched_partial_slot.argtypes = [c_uint32, c_uint32, c_uint32, c_uint32, c_uint32]
     lib.b200_sched_partial_slot.restype = c_uint32
+    lib.b200_debug_wait_expiry.argtypes = [c_uint32, c_void_p]
+    lib.b200_debug_wait_expiry.restype = c_int
     lib.b200_debug_idesc.argtypes = [c_uint32, c_uint32]
     lib.b200_debug_idesc.restype = c_uint32
     lib.b200_debug_smem_desc.argtypes = [c_uint32]

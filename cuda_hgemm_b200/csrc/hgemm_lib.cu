@@ -430,6 +430,23 @@ static int workspace_for(DeviceState &st, cudaStream_t stream, size_t need, uint
     return B200_HGEMM_OK;
 }
 
+// One CTA waits on an mbarrier that nothing ever arrives on, with a short limit: the expiry
+// path of the kernels' bounded waits (abort flag, error word), exercised without hanging anything.
+__global__ void wait_expiry_probe_kernel(uint32_t *error_word, uint64_t limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    // parity 0 of a fresh barrier completes only after an arrival, and none is ever made
+    const bool done = mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && !done && abort_flag != 0) atomicExch(error_word, static_cast<uint32_t>(kDevWaitTimeout));
+}
+
 // Any-shape CUDA-core kernel: one thread per C element, FP32 accumulate.
 __global__ void hgemm_simt_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ c,
                                   size_t m, size_t n, size_t k) {
@@ -995,6 +1012,18 @@ void b200_sched_contributors(uint32_t tile, uint32_t parts, uint32_t tiles, uint
 
 uint32_t b200_sched_partial_slot(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t tile) {
     return partial_slot(part, parts, tiles, k_blocks, tile);
+}
+
+int b200_debug_wait_expiry(uint32_t limit_ms, b200_stream_t stream) {
+    if (limit_ms == 0 || limit_ms > 1000) return B200_HGEMM_ERR_INVALID_ARG;  // a second at most
+    DeviceState *st = nullptr;
+    int rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    wait_expiry_probe_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(st->error_word,
+                                                                                   static_cast<uint64_t>(limit_ms) * 1000000ull);
+    if (!cuda_ok(cudaGetLastError(), "wait_expiry_probe_kernel")) return B200_HGEMM_ERR_CUDA;
+    return B200_HGEMM_OK;
 }
 
 uint32_t b200_debug_idesc(uint32_t m, uint32_t n) {

@@ -117,21 +117,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Same, with cluster-scope acquire: used when the arrival came from the peer CTA.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
 // Longest time one wait may take before the kernel gives up (nanoseconds).
 // A healthy wait is microseconds; the bound only exists so that a protocol
 // bug ends as an error status instead of a hung GPU.
@@ -142,24 +127,28 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // Bounded wait. `abort_flag` is a CTA-shared word: once any role of the CTA has
 // given up, every later wait returns false at once so the CTA drains quickly.
 // Returns true when the barrier phase completed.
-template <bool kClusterScope = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
-    if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
-        if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag != 0) return false;
             uint64_t now = global_timer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > B200_WAIT_LIMIT_NS) {
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, B200_WAIT_LIMIT_NS);
 }
 
 // ---------------------------------------------------------------------------

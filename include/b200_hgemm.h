@@ -144,6 +144,10 @@ uint32_t b200_sched_segments(uint32_t part, uint32_t parts, uint32_t tiles, uint
 void b200_sched_contributors(uint32_t tile, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *first,
                              uint32_t *last);
 uint32_t b200_sched_partial_slot(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t tile);
+/* Needs a GPU: launches one CTA that waits, for at most `limit_ms` (1..1000), on a barrier nothing
+ * arrives on -- the way a kernel of this library would notice a protocol failure -- and raises the
+ * device error word. b200_hgemm_last_device_error() then returns 1 and the device stays usable. */
+int b200_debug_wait_expiry(uint32_t limit_ms, b200_stream_t stream);
 /* tcgen05 descriptor encoders (instruction descriptor; shared-memory matrix descriptor). */
 uint32_t b200_debug_idesc(uint32_t m, uint32_t n);
 uint64_t b200_debug_smem_desc(uint32_t smem_addr);

@@ -314,3 +314,26 @@ def test_concurrent_streams_and_threads_do_not_share_scratch(cuda_device):
     assert api.last_device_error() == 0
     for (dA, dB, expect, _), out in zip(jobs, outs):
         assert torch.equal(out, expect)
+
+
+def test_an_expired_wait_is_reported_and_the_device_stays_usable(cuda_device):
+    """Failure detection without a fault: a wait that cannot complete runs into its time limit, the
+    kernel returns, the host reads the error word, and the next GEMM on the same context is correct."""
+    import time
+
+    import torch
+
+    lib = _native.load()
+    assert api.last_device_error() == 0
+    t0 = time.perf_counter()
+    assert lib.b200_debug_wait_expiry(50, None) == _native.OK  # 50 ms limit
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.04 < waited < 2.0, waited
+    assert api.last_device_error() == 1   # reported once ...
+    assert api.last_device_error() == 0   # ... and cleared
+    assert lib.b200_debug_wait_expiry(0, None) == _native.ERR_INVALID_ARG
+    assert lib.b200_debug_wait_expiry(5000, None) == _native.ERR_INVALID_ARG
+    A, B = make_inputs(256, 256, 256, seed=40)
+    C = run(api.b200Hgemm, A, B, cuda_device)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), "after an expired wait")
