@@ -337,3 +337,27 @@ def test_an_expired_wait_is_reported_and_the_device_stays_usable(cuda_device):
     A, B = make_inputs(256, 256, 256, seed=40)
     C = run(api.b200Hgemm, A, B, cuda_device)
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), "after an expired wait")
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 8, 8), (1, 8, 4096), (4096, 8, 64), (8, 4096, 64), (128, 256, 8), (129, 257 * 8, 72), (16, 16, 65536),
+    (40000, 16, 64), (24, 40000, 64), (2304, 2304, 2304), (3000, 1000, 520),
+], ids=lambda s: "x".join(map(str, s)))
+def test_extreme_aspect_ratios(cuda_device, shape):
+    """Degenerate and lopsided shapes through the auto dispatch: one row, eight columns, one k-block of
+    eight, very deep k, hundreds of row or column blocks."""
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=50, dist="normal")
+    C = run(api.b200Hgemm, A, B, cuda_device)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"auto {shape}")
+
+
+def test_static_scratch_and_every_variant_on_a_lopsided_shape(cuda_device):
+    M, N, K = 72, 1544, 2056
+    A, B = make_inputs(M, N, K, seed=51)
+    ref = oracle.gemm_f32(A, B)
+    for variant, bn in ((_native.VARIANT_CTA1, 64), (_native.VARIANT_CTA1, 256), (_native.VARIANT_CTA2, 128),
+                        (_native.VARIANT_CTA2, 256), (_native.VARIANT_STREAMK, 64), (_native.VARIANT_STREAMK, 256),
+                        (_native.VARIANT_SIMT, 0)):
+        C = run(None, A, B, cuda_device, plan_of(variant, bn))
+        assert_close_to_oracle(C, ref, f"variant {variant} bn {bn}")
