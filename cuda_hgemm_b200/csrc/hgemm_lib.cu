@@ -497,6 +497,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         mp.m_blocks = ceil_div_u32(M, 256);  // super-tiles of 256 x 512: two pairs side by side
         mp.n_blocks = ceil_div_u32(N, 512);
         mp.k_blocks = ceil_div_u32(K, 64);
+        if (static_cast<uint64_t>(mp.m_blocks) * mp.n_blocks > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
         mp.tiles = mp.m_blocks * mp.n_blocks;
         mp.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : 8u;
         if (mp.group_m > mp.m_blocks) mp.group_m = mp.m_blocks;
