@@ -27,8 +27,8 @@ namespace b200 {
 // ------------------------------------------------------------------------------------------
 constexpr int kMaxDevices = 64;
 constexpr size_t kMaxOwnedWorkspace = size_t(1) << 30;  // the library never grows its own workspace past 1 GiB
-constexpr size_t kCounterBytes = 64 * 1024;             // tile counters at the front of the workspace
-constexpr uint32_t kMaxCountedTiles = kCounterBytes / 4;
+constexpr size_t kCounterBytes = 64 * 1024;             // reserved header at the front of the workspace (no kernel uses it now)
+constexpr uint32_t kMaxCountedTiles = kCounterBytes / 4;  // most tiles a stream-k launch accepts (the reduce kernel's grid.y)
 
 struct TensorMapKey {
     const void *ptr;
@@ -668,7 +668,7 @@ static int entry(const void *A, const void *B, void *C, size_t M, size_t N, size
 // ------------------------------------------------------------------------------------------
 // allocation-free stream-k: scratch in a static device array
 // ------------------------------------------------------------------------------------------
-// Layout: [256 B error word | 64 KiB tile counters | 16 MiB FP32 partial-tile slots].
+// Layout: [256 B error word | 64 KiB reserved | 16 MiB FP32 partial-tile slots].
 // 16 MiB holds 2 slots of 128 x 128 floats for each of 128 k-ranges, which is the most the
 // entry point launches. Every GPU on which this library is loaded keeps these 16.06 MiB
 // reserved until the process exits, whether or not the entry point is ever called.
@@ -783,7 +783,7 @@ int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N,
 //    sets the kernel's shared-memory attribute and encodes tensor maps. Make that first call
 //    outside any stream capture.
 //  * All calls on a device share the one array, which keeps whatever the last call left in it.
-//    Each call clears the error word and the tile counters, stream-ordered, before its kernel;
+//    Each call clears the error word and the reserved header, stream-ordered, before its kernel;
 //    partial tiles are always written before they are read. Two calls whose kernels overlap on
 //    the GPU (different streams with no dependency between them) race on the array: serialise them.
 //  * A bounded wait that expires inside this variant is recorded in the first word of the
@@ -803,7 +803,7 @@ int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, s
     if (!sd.sm100) return B200_HGEMM_ERR_NO_SM100;
 
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    // the error word and the tile counters have to start at zero
+    // the error word has to start at zero (the reserved header is cleared with it)
     if (!cuda_ok(cudaMemsetAsync(sd.scratch, 0, kStaticHeaderBytes + kCounterBytes, s), "cudaMemsetAsync")) return B200_HGEMM_ERR_CUDA;
 
     b200_hgemm_plan pl;

@@ -81,7 +81,7 @@ int b200_hgemm_cta2(const void *A, const void *B, void *C, size_t M, size_t N, s
 int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
 int b200_hgemm_streamk(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
 
-/* Stream-k GEMM that never allocates: its scratch (tile counters and FP32 partial tiles) is a
+/* Stream-k GEMM that never allocates: its scratch (the FP32 partial tiles of split k-ranges) is a
  * static 16.06 MiB device array inside the library, held by every GPU the library is loaded on.
  * It has no counterpart in the reference, whose kernels need no scratch memory; it exists for
  * callers that may not call cudaMalloc where they need the GEMM (all device memory owned by a

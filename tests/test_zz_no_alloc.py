@@ -3,7 +3,7 @@
 Some users of this library cannot allocate device memory where they need a GEMM: all memory
 belongs to a pool, an allocation's implicit synchronisation would stall a serving loop, or the
 host application forbids allocations after start-up. For them the library offers one entry
-point whose scratch (tile counters and FP32 partial tiles) is a static 16 MiB device array.
+point whose scratch (the FP32 partial tiles of split k-ranges) is a static 16 MiB device array.
 This test calls it through the C ABI twice in a row -- the second call finds the array as the
 first one left it -- and compares each result with the ordinary stream-k entry point and with
 the CPU oracle, on the tolerance the other parity tests use. It also checks that the call
