@@ -1,0 +1,98 @@
+"""Interleaved A/B timing of kernel plans against cuBLAS on one shape.
+
+The dispatch rules in ``csrc/hgemm_lib.cu`` (``select_plan``) were derived with this tool: every
+candidate is pre-heated and timed in turn, the whole list is repeated ``--rounds`` times, and the
+median / min / max TFLOP/s per candidate are printed, so that the order of measurement and the
+power state of the GPU do not decide the comparison.
+
+    python -m cuda_hgemm_b200.abtest --shape 8192x8192x8192 \
+        --plans auto,cta2:256,cta1:256:g16,cta1:128,streamk:128,mcast:256
+
+A plan is ``variant:bn[:gN][:pN][:nt]`` with variant one of cta1, cta2, streamk, mcast, simt;
+``gN`` sets the rasterisation band height, ``pN`` the number of stream-k ranges, ``nt`` turns the
+TMA-store epilogue off. ``auto`` is the library's own choice.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+from . import _native, api
+from .timing import cublas_callable, load_compare, time_graph, time_launches
+
+VARIANTS = {"cta1": _native.VARIANT_CTA1, "cta2": _native.VARIANT_CTA2, "streamk": _native.VARIANT_STREAMK,
+            "simt": _native.VARIANT_SIMT, "mcast": _native.VARIANT_CTA2_MCAST}
+
+
+def parse_plan(text: str) -> _native.Plan:
+    parts = text.split(":")
+    plan = _native.Plan()
+    plan.variant = VARIANTS[parts[0]]
+    plan.bn = int(parts[1]) if len(parts) > 1 else 256
+    plan.tma_store = 1
+    for extra in parts[2:]:
+        if extra.startswith("g"):
+            plan.group_m = int(extra[1:])
+        elif extra.startswith("p"):
+            plan.parts = int(extra[1:])
+        elif extra == "nt":
+            plan.tma_store = 0
+        else:
+            raise ValueError(f"unknown plan field {extra!r}")
+    return plan
+
+
+def main(argv=None) -> int:
+    import torch
+
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--shape", default="8192x8192x8192", help="MxNxK")
+    ap.add_argument("--plans", default="auto,cta2:256,cta1:256")
+    ap.add_argument("--rounds", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--graph", action="store_true", help="time 20 launches per CUDA graph instead of stream launches")
+    ap.add_argument("--dist", choices=("uniform", "normal"), default="uniform")
+    args = ap.parse_args(argv)
+
+    M, N, K = (int(x) for x in args.shape.lower().split("x"))
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(2023)
+    if args.dist == "uniform":
+        A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).half()
+        B = (torch.rand((N, K), generator=g, device=dev) * 2 - 1).half()
+    else:
+        A = torch.randn((M, K), generator=g, device=dev).half()
+        B = (torch.randn((N, K), generator=g, device=dev) / K ** 0.5).half()
+    C = torch.empty((M, N), dtype=torch.float16, device=dev)
+
+    candidates = {}
+    cmp_lib = load_compare()
+    if cmp_lib is not None:
+        candidates["cublas_fp32_compute"] = cublas_callable(torch, cmp_lib, "hgemm_compare_cublas_fp32", A, B, C)
+        candidates["cublas_fp16_compute"] = cublas_callable(torch, cmp_lib, "hgemm_compare_cublas_fp16", A, B, C)
+    for text in args.plans.split(","):
+        if text == "auto":
+            candidates["auto"] = lambda: api.b200Hgemm(A, B, C)
+        else:
+            plan = parse_plan(text)
+            candidates[text] = (lambda plan=plan: api.hgemm_ex(A, B, C, plan))
+
+    gflop = 2.0 * M * N * K / 1e9
+    results = {name: [] for name in candidates}
+    for _ in range(args.rounds):
+        for name, fn in candidates.items():
+            ms = time_graph(torch, fn) if args.graph else time_launches(torch, fn, 3, args.steps)
+            results[name].append(gflop / ms)
+    if api.last_device_error() != 0:
+        print("device-side wait expired", file=sys.stderr)
+        return 1
+    print(json.dumps({"shape": [M, N, K], "tflops_median_min_max": {
+        name: [round(statistics.median(v), 1), round(min(v), 1), round(max(v), 1)] for name, v in results.items()}}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
