@@ -1,11 +1,19 @@
 // CTA-pair kernel with cluster multicast of the A operand, for single-GPU runs only.
 //
-// A cluster of four CTAs (two CTA pairs side by side along N) computes a 256 x 512 super-tile.
+// Four consecutive CTAs (two CTA pairs side by side along N) compute a 256 x 512 super-tile.
 // Both pairs multiply the same 256 rows of A, so each 128-row slab of A that a CTA needs is
-// also needed by the CTA at the same position of the other pair: each of the two loads one
-// 64-row half of that slab with a TMA load that delivers it to both CTAs at once. Per CTA and
-// k-block that is 24 KB read from L2 for the same 32 KB of operands landing in shared memory,
-// where the plain pair kernel reads 32 KB (hgemm_tcgen05_kernel<256, 6, 2, kModeTiles>).
+// also needed by the CTA at the same position of the other pair. When the four CTAs were
+// launched as one cluster, each of the two loads one 64-row half of that slab with a TMA load
+// that delivers it to both CTAs at once: per CTA and k-block 24 KB are read from L2 for the same
+// 32 KB of operands landing in shared memory, where the plain pair kernel reads 32 KB
+// (hgemm_tcgen05_kernel<256, 6, 2, kModeTiles>).
+//
+// Only 33 clusters of four fit the 148 SMs of a B200 (GPCs of 18 SMs hold four such clusters and
+// leave two SMs over), so the kernel is launched with a regular cluster of 2 and a PREFERRED
+// cluster of 4 (cudaLaunchAttributePreferredClusterDimension): the hardware forms clusters of
+// four where it can and clusters of two from the rest. The kernel reads its actual cluster size
+// at run time; pairs that ended up in a cluster of two load their whole A slab themselves and
+// otherwise behave like the plain pair kernel. The tile assignment is the same either way.
 //
 // This translation unit is the only place in the repository that names a multicast TMA load.
 // It is built into a library of its own (libb200_hgemm_mc.so) that the main library loads when
@@ -72,9 +80,10 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t rank = cluster_cta_rank();  // 0..3
-    const uint32_t pair = rank >> 1;           // which 256-column half of the super-tile
-    const uint32_t half = rank & 1u;           // which 128 rows of the pair's 256
+    const uint32_t rank = cluster_cta_rank();   // 0..3 in a cluster of four, 0..1 in a cluster of two
+    const bool quad = cluster_num_ctas() == 4u;  // all four CTAs of the super-tile share one cluster
+    const uint32_t pair = (blockIdx.x >> 1) & 1u;  // which 256-column half of the super-tile
+    const uint32_t half = blockIdx.x & 1u;         // which 128 rows of the pair's 256 (= rank & 1)
     const uint32_t worker = blockIdx.x / kMcClusterCtas;
     const uint32_t workers = gridDim.x / kMcClusterCtas;
     const uint32_t k_blocks = p.k_blocks;
@@ -83,7 +92,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
     if (warp == 0) {
         if (lane < static_cast<uint32_t>(STAGES)) {
             mbar_init(full_bar + 8u * lane, 1);
-            mbar_init(empty_bar + 8u * lane, 2);  // the MMA issuers of both pairs release a stage
+            mbar_init(empty_bar + 8u * lane, quad ? 2 : 1);  // in a cluster of four both pairs' MMA issuers release a stage
         } else if (lane < static_cast<uint32_t>(STAGES) + 2u) {
             const uint32_t a = lane - STAGES;
             mbar_init(tfull_bar + 8u * a, 1);
@@ -115,13 +124,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const uint16_t a_mask = static_cast<uint16_t>((1u << rank) | (1u << (rank ^ 2u)));
+            const uint16_t a_mask = static_cast<uint16_t>((1u << rank) | (1u << (rank ^ 2u)));  // cluster of four only
             pdl_wait_prior_grids();
             for (uint32_t ti = 0; ok && ti < my_tiles; ++ti) {
                 const TileCoord tc = tile_coord(worker + ti * workers, p.m_blocks, p.n_blocks, p.group_m);
                 // this CTA's 128 rows of A; it fetches the 64-row part `pair` of them for itself and
                 // for the CTA at the same position of the other pair, which fetches the other part
-                const int32_t row_a = static_cast<int32_t>(tc.m_blk * 256u + half * 128u + pair * 64u);
+                const int32_t row_a0 = static_cast<int32_t>(tc.m_blk * 256u + half * 128u);
                 const int32_t row_b = static_cast<int32_t>(tc.n_blk * 512u + pair * BN + half * 128u);
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar + 8u * stage, phase ^ 1u, abort_flag)) {
@@ -133,7 +142,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
                     const int32_t kx = static_cast<int32_t>(kb * kBK);
                     if (half == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * kMcStageBytes);
                     const uint32_t leader = pair_leader_bar(full_bar + 8u * stage);
-                    tma_load_2d_pair_multicast(sa + pair * (kMcABytes / 2), &p.tm_a, kx, row_a, leader, a_mask);
+                    if (quad) {
+                        tma_load_2d_pair_multicast(sa + pair * (kMcABytes / 2), &p.tm_a, kx, row_a0 + static_cast<int32_t>(pair * 64u),
+                                                   leader, a_mask);
+                    } else {
+                        tma_load_2d_pair(sa, &p.tm_a, kx, row_a0, leader);
+                        tma_load_2d_pair(sa + kMcABytes / 2, &p.tm_a, kx, row_a0 + 64, leader);
+                    }
                     tma_load_2d_pair(sb, &p.tm_b, kx, row_b, leader);
                     if (++stage == STAGES) {
                         stage = 0;
@@ -147,7 +162,8 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
         // ------------------------------------------------------------------ MMA issuer (pair leaders)
         if (lane == 0 && half == 0) {
             constexpr uint32_t idesc = umma_idesc_f16_f32(256, BN);
-            const uint16_t pair_mask = static_cast<uint16_t>(0x3u << (2u * pair));
+            const uint16_t pair_mask = static_cast<uint16_t>(quad ? (0x3u << (2u * pair)) : 0x3u);
+            const uint16_t all_mask = static_cast<uint16_t>(quad ? 0xFu : 0x3u);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t ti = 0; ok && ti < my_tiles; ++ti) {
@@ -169,9 +185,9 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
                     for (uint32_t k = 0; k < kBK / 16; ++k) {
                         umma_f16<2>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
-                    // all four CTAs write into each other's A slabs: every one of them has to learn
-                    // that this pair is done with the stage
-                    umma_commit_pair(empty_bar + 8u * stage, 0xF);
+                    // in a cluster of four the CTAs write into each other's A slabs: every one of them
+                    // has to learn that this pair is done with the stage
+                    umma_commit_pair(empty_bar + 8u * stage, all_mask);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -218,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
                     // the accumulator is in registers: hand it back to the pair's MMA issuer
                     tcgen05_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar + 8u * acc, pair * 2u));
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar + 8u * acc, quad ? pair * 2u : 0u));
                 }
                 const bool live = warp_rows_live && (n0 + c * 64u) < p.n;
                 if (live) {
@@ -297,12 +313,17 @@ extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = kMcSmemBytes;
     cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[3];
     int n_attrs = 0;
-    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
-    attrs[n_attrs].val.clusterDim.x = kMcClusterCtas;
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;  // what the hardware may fall back to
+    attrs[n_attrs].val.clusterDim.x = 2;
     attrs[n_attrs].val.clusterDim.y = 1;
     attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+    attrs[n_attrs].id = cudaLaunchAttributePreferredClusterDimension;  // what it forms where four SMs are free
+    attrs[n_attrs].val.preferredClusterDim.x = kMcClusterCtas;
+    attrs[n_attrs].val.preferredClusterDim.y = 1;
+    attrs[n_attrs].val.preferredClusterDim.z = 1;
     ++n_attrs;
     if (use_pdl) {
         attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -311,22 +332,17 @@ extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n_attrs;
-    cfg.gridDim = dim3(kMcClusterCtas, 1, 1);
     {
         std::lock_guard<std::mutex> lock(g_mu);
         if (g_max_clusters[dev] == 0) {
-            int n = 0;
-            cfg.gridDim = dim3(kMcClusterCtas * 64, 1, 1);
-            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
-                cudaGetLastError();
-                return -5;
-            }
-            g_max_clusters[dev] = n;
+            int sms = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < kMcClusterCtas) return -5;
+            g_max_clusters[dev] = sms / kMcClusterCtas;  // groups of four CTAs, one CTA per SM
         }
     }
-    uint32_t clusters = static_cast<uint32_t>(g_max_clusters[dev]);
-    if (clusters > p.tiles) clusters = p.tiles;
-    cfg.gridDim = dim3(clusters * kMcClusterCtas, 1, 1);
+    uint32_t groups = static_cast<uint32_t>(g_max_clusters[dev]);
+    if (groups > p.tiles) groups = p.tiles;
+    cfg.gridDim = dim3(groups * kMcClusterCtas, 1, 1);
     if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
         cudaGetLastError();
         return -5;
@@ -334,7 +350,7 @@ extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
     return 0;
 }
 
-// How many four-CTA clusters the device keeps resident (0 before the first launch on it).
+// How many groups of four CTAs a launch uses on this device (0 before the first launch on it).
 extern "C" int b200_mc_resident_clusters(void) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;

@@ -38,6 +38,13 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
     return r;
 }
 
+// Number of CTAs in the cluster this CTA was launched in.
+__device__ __forceinline__ uint32_t cluster_num_ctas() {
+    uint32_t n;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+    return n;
+}
+
 // Address of the same shared-memory offset inside CTA `rank` of this cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
     uint32_t r;
