@@ -156,6 +156,7 @@ from cuda_hgemm_b200.timing import (cublas_callable, load_compare, preheat, time
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
 # captures under profiles/, keyed by workload; scaled captures say so there.
 NCU_TRAFFIC_BYTES = {
+    "square16384": 16.5e9,   # profiles/hgemm_tcgen05_cta2_vs_cublas_square16384.md
     "square8192": 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
     "skinny16": 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
 }
