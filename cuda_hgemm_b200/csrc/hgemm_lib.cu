@@ -19,6 +19,7 @@
 
 #include "../../include/b200_hgemm.h"
 #include "gemm_kernel.cuh"
+#include "gemm_kernel_big.cuh"
 
 namespace b200 {
 
@@ -183,19 +184,31 @@ static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint6
 // several GPUs do not carry it, and everything here works without it.
 typedef int (*McLaunchFn)(const void *params, void *stream, int use_pdl);
 
-static McLaunchFn mc_launch_fn() {
-    static McLaunchFn fn = []() -> McLaunchFn {
-        if (getenv("B200_HGEMM_NO_MULTICAST")) return nullptr;
+struct McEntryPoints {
+    McLaunchFn launch256 = nullptr;  // 256 x 512 super-tiles, 128 x 256 per CTA
+    McLaunchFn launch512 = nullptr;  // 512 x 512 super-tiles, 256 x 256 per CTA
+};
+
+static const McEntryPoints &mc_entry_points() {
+    static McEntryPoints ep = []() -> McEntryPoints {
+        McEntryPoints e;
+        if (getenv("B200_HGEMM_NO_MULTICAST")) return e;
         Dl_info info;
-        if (!dladdr(reinterpret_cast<const void *>(&g_launches), &info) || !info.dli_fname) return nullptr;
+        if (!dladdr(reinterpret_cast<const void *>(&g_launches), &info) || !info.dli_fname) return e;
         std::string path(info.dli_fname);
         const size_t slash = path.rfind('/');
         path = (slash == std::string::npos ? std::string(".") : path.substr(0, slash)) + "/libb200_hgemm_mc.so";
         void *h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
-        if (!h) return nullptr;
-        return reinterpret_cast<McLaunchFn>(dlsym(h, "b200_mc_launch"));
+        if (!h) return e;
+        e.launch256 = reinterpret_cast<McLaunchFn>(dlsym(h, "b200_mc_launch"));
+        e.launch512 = reinterpret_cast<McLaunchFn>(dlsym(h, "b200_mc512_launch"));
+        return e;
     }();
-    return fn;
+    return ep;
+}
+
+static McLaunchFn mc_launch_fn(int bn = 256) {
+    return bn == 512 ? mc_entry_points().launch512 : mc_entry_points().launch256;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -213,9 +226,16 @@ static bool plan_is_tensor(const b200_hgemm_plan &pl) {
 static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     if (pl.variant == B200_VARIANT_SIMT) return B200_HGEMM_OK;
     if (!plan_is_tensor(pl)) return B200_HGEMM_ERR_UNSUPPORTED;
-    if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (pl.variant == B200_VARIANT_CTA2_MCAST) {
+        // bn names the CTA arrangement here: 256 = 128 x 256 per CTA, 512 = 256 x 256 per CTA
+        if ((pl.bn != 256 && pl.bn != 512) || N % 8 != 0 || !mc_launch_fn(pl.bn)) return B200_HGEMM_ERR_UNSUPPORTED;
+    } else if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 512) {
+        // 256 x 256 outputs per CTA, 512 x 256 per pair; its epilogue is TMA stores only
+        if (N % 8 != 0 || !pl.tma_store) return B200_HGEMM_ERR_UNSUPPORTED;
+    } else if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) {
+        return B200_HGEMM_ERR_UNSUPPORTED;
+    }
     if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 64) return B200_HGEMM_ERR_UNSUPPORTED;
-    if (pl.variant == B200_VARIANT_CTA2_MCAST && (pl.bn != 256 || N % 8 != 0 || !mc_launch_fn())) return B200_HGEMM_ERR_UNSUPPORTED;
     if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
     if (pl.tma_store && N % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;
     if (pl.parts < 0 || pl.group_m < 0 || pl.grid < 0) return B200_HGEMM_ERR_INVALID_ARG;
@@ -385,6 +405,65 @@ static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, ui
     return B200_HGEMM_OK;
 }
 
+// The pair kernel with 256 x 256 outputs per CTA (gemm_kernel_big.cuh), 512 x 256 per pair.
+__global__ void __launch_bounds__(kBigThreads, 1) hgemm_tcgen05_big_kernel(const __grid_constant__ GemmParams p) {
+    hgemm_big_body<2, NoMulticastLoad>(p);
+}
+
+constexpr int kBigAttrSlot = 8;
+
+static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
+    auto kern = hgemm_tcgen05_big_kernel;
+    if (!st.attr_set[kBigAttrSlot]) {
+        std::lock_guard<std::mutex> lock(st.mu);
+        if (!st.attr_set[kBigAttrSlot]) {
+            if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBigSmemBytes), "cudaFuncSetAttribute")) {
+                return B200_HGEMM_ERR_CUDA;
+            }
+            st.attr_set[kBigAttrSlot] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kBigThreads, 1, 1);
+    cfg.dynamicSmemBytes = kBigSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int n_attrs = 0;
+    if (pdl_enabled()) {
+        attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attrs;
+    }
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 2;
+    attrs[n_attrs].val.clusterDim.y = 1;
+    attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+    cfg.attrs = attrs;
+    cfg.numAttrs = n_attrs;
+    if (st.max_clusters[kBigAttrSlot] == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            return B200_HGEMM_ERR_CUDA;
+        }
+        std::lock_guard<std::mutex> lock(st.mu);
+        st.max_clusters[kBigAttrSlot] = n;
+    }
+    if (grid / 2 > static_cast<uint32_t>(st.max_clusters[kBigAttrSlot])) {
+        grid = 2u * static_cast<uint32_t>(st.max_clusters[kBigAttrSlot]);
+        cfg.gridDim = dim3(grid, 1, 1);
+    }
+    if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, p), "cudaLaunchKernelEx")) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_HGEMM_OK;
+}
+
 static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, size_t K, const b200_hgemm_plan &pl) {
     if (pl.variant != B200_VARIANT_STREAMK) return 0;
     const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, pl.bn);
@@ -494,25 +573,27 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         mp.m = static_cast<uint32_t>(M);
         mp.n = static_cast<uint32_t>(N);
         mp.k = static_cast<uint32_t>(K);
-        mp.m_blocks = ceil_div_u32(M, 256);  // super-tiles of 256 x 512: two pairs side by side
+        const bool big = pl.bn == 512;           // 256 rows per CTA instead of 128
+        mp.m_blocks = ceil_div_u32(M, big ? 512 : 256);  // super-tiles of 256 x 512 or 512 x 512: two pairs side by side
         mp.n_blocks = ceil_div_u32(N, 512);
         mp.k_blocks = ceil_div_u32(K, 64);
         if (static_cast<uint64_t>(mp.m_blocks) * mp.n_blocks > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
         mp.tiles = mp.m_blocks * mp.n_blocks;
-        mp.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : 8u;
+        mp.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : (big ? 6u : 8u);
         if (mp.group_m > mp.m_blocks) mp.group_m = mp.m_blocks;
         mp.tma_store = 1;
         mp.c_vec_ok = 1;
-        if ((rc = get_tensor_map(st, A, M, K, 64, 64, &mp.tm_a)) != B200_HGEMM_OK) return rc;
+        if ((rc = get_tensor_map(st, A, M, K, big ? 128 : 64, 64, &mp.tm_a)) != B200_HGEMM_OK) return rc;
         if ((rc = get_tensor_map(st, B, N, K, 128, 64, &mp.tm_b)) != B200_HGEMM_OK) return rc;
         if ((rc = get_tensor_map(st, C, M, N, 32, 64, &mp.tm_c)) != B200_HGEMM_OK) return rc;
-        rc = mc_launch_fn()(&mp, stream, pdl_enabled() ? 1 : 0);
+        rc = mc_launch_fn(pl.bn)(&mp, stream, pdl_enabled() ? 1 : 0);
         if (rc != 0) return B200_HGEMM_ERR_CUDA;
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return B200_HGEMM_OK;
     }
     const int cg = (pl.variant == B200_VARIANT_CTA2) ? 2 : 1;
-    const int bn = pl.bn;
+    const bool big = pl.variant == B200_VARIANT_CTA2 && pl.bn == 512;  // 512 x 256 per pair
+    const int bn = big ? 256 : pl.bn;
 
     GemmParams p;
     memset(&p, 0, sizeof(p));
@@ -521,13 +602,13 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     p.m = static_cast<uint32_t>(M);
     p.n = static_cast<uint32_t>(N);
     p.k = static_cast<uint32_t>(K);
-    p.m_blocks = ceil_div_u32(M, 128u * cg);
+    p.m_blocks = ceil_div_u32(M, big ? 512u : 128u * cg);
     p.n_blocks = ceil_div_u32(N, bn);
     p.k_blocks = ceil_div_u32(K, 64);
     const uint64_t tiles64 = static_cast<uint64_t>(p.m_blocks) * p.n_blocks;
     if (tiles64 > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
     p.tiles = static_cast<uint32_t>(tiles64);
-    p.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : (cg == 2 ? 8u : 16u);
+    p.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : (big ? 6u : cg == 2 ? 8u : 16u);
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
     p.tma_store = pl.tma_store ? 1u : 0u;
     p.c_vec_ok = (N % 8 == 0) ? 1u : 0u;
@@ -572,6 +653,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 128) return launch_kernel<128, 6, 1, kModeTiles>(st, 1, p, grid, stream);
         return launch_kernel<64, 8, 1, kModeTiles>(st, 2, p, grid, stream);
     }
+    if (big) return launch_big_kernel(st, p, grid, stream);
     if (pl.variant == B200_VARIANT_CTA2) {
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
         return launch_kernel<128, 8, 2, kModeTiles>(st, 4, p, grid, stream);

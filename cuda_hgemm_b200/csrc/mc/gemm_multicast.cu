@@ -29,6 +29,7 @@
 #include <mutex>
 
 #include "../gemm_kernel.cuh"
+#include "../gemm_kernel_big.cuh"
 
 namespace b200 {
 
@@ -39,13 +40,6 @@ constexpr uint32_t kMcBBytes = 128 * kBK * 2;
 constexpr uint32_t kMcStageBytes = kMcABytes + kMcBBytes;
 constexpr uint32_t kMcTmemCols = 512;
 constexpr uint32_t kMcSmemBytes = 1024 + kMcStages * kMcStageBytes + kStagingBytes + 256;
-
-// The barrier of the pair's leader CTA, as seen from either CTA of the pair: shared-window
-// addresses carry the CTA's rank in the cluster from bit 24 up, and the two CTAs of a pair differ
-// in bit 24 only.
-__device__ __forceinline__ uint32_t pair_leader_bar(uint32_t local_bar) {
-    return local_bar & 0xFEFFFFFFu;
-}
 
 // TMA tile load delivered to every CTA of `cta_mask` at the same shared-memory offset; the
 // transaction bytes are counted on the barrier of each destination pair's leader.
@@ -283,35 +277,54 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
     }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// 512 x 512 super-tiles: 256 x 256 outputs per CTA
+// ------------------------------------------------------------------------------------------
+// The kernel body is hgemm_big_body (../gemm_kernel_big.cuh) for groups of four CTAs; this file
+// adds the one thing that header may not contain, the multicast load of the A slab halves.
+struct PairMulticastLoad {
+    static __device__ __forceinline__ void load(uint32_t smem_dst, const CUtensorMap *tm, int32_t x, int32_t y, uint32_t leader_bar,
+                                                uint16_t cta_mask) {
+        tma_load_2d_pair_multicast(smem_dst, tm, x, y, leader_bar, cta_mask);
+    }
+};
+
+__global__ void __launch_bounds__(kBigThreads, 1) hgemm_tcgen05_mc512_kernel(const __grid_constant__ GemmParams p) {
+    hgemm_big_body<4, PairMulticastLoad>(p);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 namespace {
 std::mutex g_mu;
-bool g_attr_set[64] = {};
+bool g_attr_set[2][64] = {};
 int g_max_clusters[64] = {};
-}  // namespace
 
-// Launches the multicast kernel on `stream`. `params` is a b200::GemmParams whose tensor maps use
-// boxes of 64 rows (A), 128 rows (B) and 32 rows (C), with m_blocks / n_blocks / tiles counted in
-// 256 x 512 super-tiles. Returns 0, or -5 when a CUDA call fails.
-extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
-    const GemmParams &p = *static_cast<const GemmParams *>(params);
+// Launches one of the two kernels: groups of four CTAs, a regular cluster of 2 and a preferred
+// cluster of 4, at most one group per four SMs.
+int launch_groups(void (*kern)(const GemmParams), int which, uint32_t smem_bytes, uint32_t threads, const GemmParams &p,
+                  void *stream, int use_pdl) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -5;
-    auto kern = hgemm_tcgen05_mc_kernel;
     {
         std::lock_guard<std::mutex> lock(g_mu);
-        if (!g_attr_set[dev]) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMcSmemBytes) != cudaSuccess) return -5;
-            g_attr_set[dev] = true;
+        if (!g_attr_set[which][dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -5;
+            g_attr_set[which][dev] = true;
+        }
+        if (g_max_clusters[dev] == 0) {
+            int sms = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < kMcClusterCtas) return -5;
+            g_max_clusters[dev] = sms / kMcClusterCtas;  // groups of four CTAs, one CTA per SM
         }
     }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = kMcSmemBytes;
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attrs[3];
     int n_attrs = 0;
@@ -332,14 +345,6 @@ extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n_attrs;
-    {
-        std::lock_guard<std::mutex> lock(g_mu);
-        if (g_max_clusters[dev] == 0) {
-            int sms = 0;
-            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < kMcClusterCtas) return -5;
-            g_max_clusters[dev] = sms / kMcClusterCtas;  // groups of four CTAs, one CTA per SM
-        }
-    }
     uint32_t groups = static_cast<uint32_t>(g_max_clusters[dev]);
     if (groups > p.tiles) groups = p.tiles;
     cfg.gridDim = dim3(groups * kMcClusterCtas, 1, 1);
@@ -348,6 +353,22 @@ extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
         return -5;
     }
     return 0;
+}
+}  // namespace
+
+// Launches the 256 x 512 multicast kernel on `stream`. `params` is a b200::GemmParams whose tensor
+// maps use boxes of 64 rows (A), 128 rows (B) and 32 rows (C), with m_blocks / n_blocks / tiles
+// counted in 256 x 512 super-tiles. Returns 0, or -5 when a CUDA call fails.
+extern "C" int b200_mc_launch(const void *params, void *stream, int use_pdl) {
+    return launch_groups(hgemm_tcgen05_mc_kernel, 0, kMcSmemBytes, kThreads, *static_cast<const GemmParams *>(params), stream,
+                         use_pdl);
+}
+
+// Launches the 512 x 512 multicast kernel: boxes of 128 rows (A), 128 rows (B) and 32 rows (C);
+// m_blocks / n_blocks / tiles counted in 512 x 512 super-tiles.
+extern "C" int b200_mc512_launch(const void *params, void *stream, int use_pdl) {
+    return launch_groups(hgemm_tcgen05_mc512_kernel, 1, kBigSmemBytes, kBigThreads, *static_cast<const GemmParams *>(params),
+                         stream, use_pdl);
 }
 
 // How many groups of four CTAs a launch uses on this device (0 before the first launch on it).
