@@ -288,13 +288,34 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
 
     const uint64_t pairs256 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 256);
     const uint64_t pair_slots = sms / 2;
+    const double kb = static_cast<double>(k_blocks);
+    auto waves = [](uint64_t work, uint64_t slots) { return static_cast<double>((work + slots - 1) / slots); };
+
+    // The arrangements with 256 x 256 outputs per CTA: 512 x 256 tiles on pairs, or 512 x 512 tiles on
+    // groups of four CTAs when the single-GPU companion library with the multicast kernel is there.
+    // A tile costs twice the k-blocks of a 256 x 256 pair tile, less what the smaller operand traffic
+    // buys under the power cap (5-7 %), plus about a microsecond in which the tensor pipe waits for the
+    // epilogue to drain tensor memory. Their epilogue is TMA stores only (N % 8 == 0).
+    const bool big_ok = (N % 8 == 0) && k_blocks >= 24;
+    const bool mc_ok = big_ok && mc_launch_fn(512) != nullptr;
+    const uint64_t tiles_big = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 256);
+    const uint64_t tiles_mc = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 512);
+
     if (pairs256 >= 2 * pair_slots) {
-        // two or more full waves of CTA pairs: the tensor-bound regime
-        // (the cluster-multicast variant measured 4-6 % slower than plain pairs at 8192^3 and 16384^3;
-        // it is chosen only on request)
-        static const bool prefer_mc = (getenv("B200_HGEMM_PREFER_MULTICAST") != nullptr);
-        pl->variant = (prefer_mc && mc_launch_fn() && N % 8 == 0) ? B200_VARIANT_CTA2_MCAST : B200_VARIANT_CTA2;
+        // two or more full waves of CTA pairs: the tensor-bound regime. Measured against each other
+        // at 3072..16384 (K from 1024 to 16384): the larger tiles win from K = 2048 up wherever their
+        // last wave is no emptier, by 2 % at 4096^3 and 10 % at 16384^3.
+        const double t256 = waves(pairs256, pair_slots) * kb * 0.37;
+        const double tbig = big_ok ? waves(tiles_big, pair_slots) * (kb * 0.70 + 1.0) : 1e30;
+        const double tmc = mc_ok ? waves(tiles_mc, sms / 4) * (kb * 0.685 + 1.0) : 1e30;
+        pl->variant = B200_VARIANT_CTA2;
         pl->bn = 256;
+        if (tbig < t256 && tbig <= tmc) {
+            pl->bn = 512;
+        } else if (tmc < t256) {
+            pl->variant = B200_VARIANT_CTA2_MCAST;
+            pl->bn = 512;
+        }
         return;
     }
 
@@ -307,25 +328,30 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         int variant, bn;
         double us;
     };
-    const double kb = static_cast<double>(k_blocks);
     const uint64_t tiles64 = m_blocks * ceil_div_u32(N, 64);
-    auto waves = [](uint64_t work, uint64_t slots) { return static_cast<double>((work + slots - 1) / slots); };
     // every range leaves up to two FP32 partial tiles, each written once and read once through L2
     // (about 4 TB/s for this pattern): with full-height tiles that costs more than a ragged last
     // wave does, so stream-k only wins here when the tiles are few and k is long
     auto partial_us = [&](int bn) { return 2.0 * sms * 2.0 * (128.0 * bn * 4.0) / 4.0e6; };
-    Candidate cands[6] = {
+    constexpr int kCands = 8;
+    Candidate cands[kCands] = {
         {B200_VARIANT_CTA1, 256, waves(tiles256, sms) * kb * 0.35 + 2.0},
         {B200_VARIANT_CTA1, 128, waves(tiles128, sms) * kb * 0.33 + 1.5},
         {B200_VARIANT_CTA1, 64, waves(tiles64, sms) * kb * 0.30 + 1.2},
-        {B200_VARIANT_CTA2, 256, waves(pairs256, pair_slots) * kb * 0.37 + 2.0},
+        // pairs: less L2 traffic per k-block than single CTAs, a costlier launch (measured: single
+        // CTAs ahead at 1792 and 2048, pairs from 2304 up)
+        {B200_VARIANT_CTA2, 256, waves(pairs256, pair_slots) * kb * 0.335 + 2.5},
         {B200_VARIANT_STREAMK, 256, static_cast<double>(tiles256) * kb / sms * 0.35 + 4.0 + partial_us(256)},
         {B200_VARIANT_STREAMK, 128, static_cast<double>(tiles128) * kb / sms * 0.33 + 4.0 + partial_us(128)},
+        // the large tiles only where they fill nine tenths of a wave (measured: behind at 2304 and
+        // 2560 with 45 and 50 tiles for 74 pairs, ahead at 3072 with 72)
+        {B200_VARIANT_CTA2, 512, big_ok && tiles_big * 10 >= pair_slots * 9 ? waves(tiles_big, pair_slots) * (kb * 0.64 + 1.0) + 2.5 : 1e30},
+        {B200_VARIANT_CTA2_MCAST, 512, mc_ok && tiles_mc * 10 >= (sms / 4) * 9 ? waves(tiles_mc, sms / 4) * (kb * 0.625 + 1.0) + 2.5 : 1e30},
     };
     if (M % 256 != 0) cands[3].us *= 1.0 + 128.0 / static_cast<double>(M);  // the pair's second CTA idles on the last rows
     if (k_blocks < 16) cands[4].us = cands[5].us = 1e30;                    // too little k to split
     int best = 0;
-    for (int i = 1; i < 6; ++i) {
+    for (int i = 1; i < kCands; ++i) {
         if (cands[i].us < cands[best].us * 0.98) best = i;  // earlier entries win ties: fewer moving parts
     }
     pl->variant = cands[best].variant;

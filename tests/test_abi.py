@@ -87,8 +87,14 @@ def test_descriptor_encoders(native_lib):
 def test_plan_selection_covers_the_benchmark_shapes(native_lib):
     from cuda_hgemm_b200 import api
 
+    # long k, many tiles: 256 x 256 outputs per CTA (pairs, or groups of four with the multicast companion)
     big = api.select_plan(8192, 8192, 8192)
-    assert big.variant in (_native.VARIANT_CTA1, _native.VARIANT_CTA2, _native.VARIANT_CTA2_MCAST) and big.bn == 256
+    assert big.variant in (_native.VARIANT_CTA2, _native.VARIANT_CTA2_MCAST) and big.bn == 512
+    # short k: the drain of a full tensor memory would show; 128 x 256 per CTA with two accumulator sets
+    short_k = api.select_plan(4096, 4096, 1024)
+    assert short_k.variant == _native.VARIANT_CTA2 and short_k.bn == 256
+    # a last wave that the larger tiles would leave emptier
+    assert api.select_plan(3584, 3584, 3584).bn == 256
     # decode shapes: 112 whole tiles cover most SMs at N = 14336; at N = 4096 the k-range is split
     assert api.select_plan(16, 14336, 4096).variant == _native.VARIANT_CTA1
     skinny = api.select_plan(16, 4096, 14336)

@@ -115,6 +115,64 @@ def test_cluster_multicast_pairs(cuda_device, shape):
     assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
 
 
+BIG_TILE_SHAPES = [
+    (512, 256, 64),      # one pair tile, one k-block
+    (512, 512, 256),     # one tile for a group of four, the ring of 4 stages exactly once
+    (256, 256, 320),     # smaller than the tile: the second CTA of the pair works on padding
+    (600, 776, 136),     # tails in M, N and K
+    (1024, 2048, 1024),
+    (2560, 2304, 512),   # several tiles per worker: tensor memory handed back and forth
+    (6144, 5120, 576),   # more tiles than workers on every arrangement
+    (520, 264, 8200),    # long k, 129 k-blocks
+]
+
+
+@pytest.mark.parametrize("shape", BIG_TILE_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_pair_tiles_of_256_rows_per_cta(cuda_device, shape):
+    """512 x 256 pair tiles: two accumulators per CTA fill tensor memory, drain-first epilogue."""
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=21)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2, 512))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta2 512x256 {shape}")
+    # same products in the same order as the 256 x 256 pair kernel: bit-identical results
+    C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2, 256))
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
+@pytest.mark.parametrize("shape", BIG_TILE_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_cluster_multicast_groups_of_256_rows_per_cta(cuda_device, shape):
+    """512 x 512 tiles on groups of four CTAs, A slab halves delivered by TMA multicast."""
+    from cuda_hgemm_b200 import build
+
+    if not build.MULTICAST_SO.exists():
+        pytest.skip("libb200_hgemm_mc.so is not part of this run (it is left out on multi-GPU runs)")
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=22)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2_MCAST, 512))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"multicast 512x512 {shape}")
+    C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2, 512))
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
+def test_large_tiles_refuse_what_their_epilogue_cannot_store(cuda_device):
+    """Their epilogue is TMA stores only: N must be a multiple of 8 halves and the plan must say TMA."""
+    import torch
+
+    A, B = make_inputs(512, 1001, 512, seed=23)
+    dA, dB = (torch.from_numpy(x).to(cuda_device) for x in (A, B))
+    C = torch.empty((512, 1001), dtype=torch.float16, device=cuda_device)
+    for variant in (_native.VARIANT_CTA2, _native.VARIANT_CTA2_MCAST):
+        with pytest.raises(_native.HgemmError) as e:
+            api.hgemm_ex(dA, dB, C, plan_of(variant, 512))
+        assert e.value.status == _native.ERR_UNSUPPORTED
+    A2, B2 = make_inputs(512, 1024, 512, seed=23)
+    dA2, dB2 = (torch.from_numpy(x).to(cuda_device) for x in (A2, B2))
+    C2 = torch.empty((512, 1024), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_native.HgemmError) as e:
+        api.hgemm_ex(dA2, dB2, C2, plan_of(_native.VARIANT_CTA2, 512, tma_store=0))
+    assert e.value.status == _native.ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("parts", [0, 1, 7, 33, 148, 400])
 @pytest.mark.parametrize("bn", [64, 128, 256])
 def test_stream_k_ranges(cuda_device, bn, parts):
