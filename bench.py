@@ -149,20 +149,29 @@ def make_inputs(torch, M, N, K, dist, device, row_lo, row_hi):
     return A[row_lo:row_hi].contiguous(), B
 
 
+from cuda_hgemm_b200 import _native  # noqa: E402
 from cuda_hgemm_b200.timing import (cublas_callable, load_compare, preheat, time_graph,  # noqa: E402
                                     time_launches, time_native_loop)
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
-# captures under profiles/, keyed by workload; scaled captures say so there.
+# captures under profiles/, keyed by workload and by the kernel the dispatch picks for it
+# (variant, bn); scaled captures say so there.
 NCU_TRAFFIC_BYTES = {
-    "square16384": 16.5e9,   # profiles/hgemm_tcgen05_cta2_vs_cublas_square16384.md
-    "square8192": 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
-    "skinny16": 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
+    # profiles/hgemm_tcgen05_big_vs_cublas_square16384.md
+    ("square16384", _native.VARIANT_CTA2_MCAST, 512): 9.43e9,
+    ("square16384", _native.VARIANT_CTA2, 512): 8.46e9,
+    ("square16384", _native.VARIANT_CTA2, 256): 16.5e9,
+    ("square8192", _native.VARIANT_CTA2, 256): 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
+    ("skinny16", _native.VARIANT_CTA1, 128): 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
 }
 
 
-def roofline(workload, rows, N, K, ms_per_step, peaks):
+def ncu_traffic(workload, plan):
+    return NCU_TRAFFIC_BYTES.get((workload, plan.variant, plan.bn)) if plan is not None else None
+
+
+def roofline(workload, plan, rows, N, K, ms_per_step, peaks):
     """Roofline entry of the dominant kernel for one launch of this rank's slab."""
     skinny = rows <= 128
     if skinny:
@@ -170,7 +179,7 @@ def roofline(workload, rows, N, K, ms_per_step, peaks):
         achieved = algo / (ms_per_step * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": f"{peaks['source']} copy bandwidth",
-                "traffic": NCU_TRAFFIC_BYTES.get(workload)}
+                "traffic": ncu_traffic(workload, plan)}
     achieved = 2.0 * rows * N * K / (ms_per_step * 1e-3) / 1e12
     # the timed region follows a pre-heat and runs back to back under the power cap: the sustained
     # cuBLAS figure is the matching denominator; the burst figure is printed beside it
@@ -179,7 +188,7 @@ def roofline(workload, rows, N, K, ms_per_step, peaks):
             "frac": round(achieved / peak, 4),
             "peak_source": f"{peaks['source']} cuBLAS bf16, sustained (kernel timed in a back-to-back loop after a pre-heat)",
             "frac_of_burst_peak": round(achieved / peaks["tflops"], 4), "burst_peak": peaks["tflops"],
-            "traffic": NCU_TRAFFIC_BYTES.get(workload)}
+            "traffic": ncu_traffic(workload, plan)}
 
 
 def cpu_baseline(M, N, K, dist):
@@ -369,7 +378,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": int((rows * K + N * K) * 2), "d2h_bytes_per_step": int(rows * N * 2),
                 "steps": e2e_steps, "matches_device_result": e2e_ok,
                 "api": "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
-        "roofline": roofline(args.workload, rows, N, K, ms_per_step, peaks),
+        "roofline": roofline(args.workload, plan, rows, N, K, ms_per_step, peaks),
     }
 
     # ---- comparisons on the same operands (outside the timed region) ----
