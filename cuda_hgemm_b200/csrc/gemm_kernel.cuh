@@ -78,14 +78,14 @@ struct alignas(64) GemmParams {
 
 template <int BN, int STAGES, int CG>
 struct KernelTraits {
-    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+    static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN must be a multiple of 64 up to 256");
     static_assert(CG == 1 || CG == 2, "CG is the CTA-pair size");
     static constexpr uint32_t kARows = kBM;
     static constexpr uint32_t kBRows = BN / CG;
     static constexpr uint32_t kABytes = kARows * kBK * 2;
     static constexpr uint32_t kBBytes = kBRows * kBK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two
+    static constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;  // two accumulators; power of two
     static constexpr uint32_t kBarrierBytes = 256;
     static constexpr uint32_t kSmemBytes = 1024 + STAGES * kStageBytes + kStagingBytes + kBarrierBytes;
     static_assert((kStageBytes % 1024) == 0, "stages must keep 1024-byte alignment");

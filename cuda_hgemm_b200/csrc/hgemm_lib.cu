@@ -66,7 +66,7 @@ struct DeviceState {
     // staging buffers of the host-pointer entry point
     void *host_a = nullptr, *host_b = nullptr, *host_c = nullptr;
     size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
-    cudaStream_t host_stream[2] = {nullptr, nullptr};
+    cudaStream_t host_stream[3] = {nullptr, nullptr, nullptr};  // upload, GEMMs, download
     cudaEvent_t host_event[2] = {nullptr, nullptr};
     bool attr_set[16] = {};
     int max_clusters[16] = {};  // CTA pairs the device can keep resident at once, per pair kernel
@@ -232,6 +232,9 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     } else if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 512) {
         // 256 x 256 outputs per CTA, 512 x 256 per pair; its epilogue is TMA stores only
         if (N % 8 != 0 || !pl.tma_store) return B200_HGEMM_ERR_UNSUPPORTED;
+    } else if (pl.bn == 192) {
+        // whole tiles only: between 128 and 256 for shapes whose tile count would leave a wave ragged
+        if (pl.variant == B200_VARIANT_STREAMK) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) {
         return B200_HGEMM_ERR_UNSUPPORTED;
     }
@@ -676,12 +679,14 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
 
     if (pl.variant == B200_VARIANT_CTA1) {
         if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles>(st, 0, p, grid, stream);
+        if (bn == 192) return launch_kernel<192, 4, 1, kModeTiles>(st, 9, p, grid, stream);
         if (bn == 128) return launch_kernel<128, 6, 1, kModeTiles>(st, 1, p, grid, stream);
         return launch_kernel<64, 8, 1, kModeTiles>(st, 2, p, grid, stream);
     }
     if (big) return launch_big_kernel(st, p, grid, stream);
     if (pl.variant == B200_VARIANT_CTA2) {
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
+        if (bn == 192) return launch_kernel<192, 6, 2, kModeTiles>(st, 10, p, grid, stream);
         return launch_kernel<128, 8, 2, kModeTiles>(st, 4, p, grid, stream);
     }
     if (bn == 256) {
@@ -1051,20 +1056,26 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
         if ((rc = grow(&st->host_a, &st->host_a_bytes, a_bytes)) != B200_HGEMM_OK) return rc;
         if ((rc = grow(&st->host_b, &st->host_b_bytes, b_bytes)) != B200_HGEMM_OK) return rc;
         if ((rc = grow(&st->host_c, &st->host_c_bytes, c_bytes)) != B200_HGEMM_OK) return rc;
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 3; ++i) {
             if (!st->host_stream[i] && cudaStreamCreateWithFlags(&st->host_stream[i], cudaStreamNonBlocking) != cudaSuccess)
                 return B200_HGEMM_ERR_CUDA;
+        }
+        for (int i = 0; i < 2; ++i) {
             if (!st->host_event[i] && cudaEventCreateWithFlags(&st->host_event[i], cudaEventDisableTiming) != cudaSuccess)
                 return B200_HGEMM_ERR_CUDA;
         }
     }
-    // B first (every row slab needs all of it), then A and C move in row slabs so that the
-    // upload of slab i+1 and the download of slab i-1 overlap the GEMM of slab i.
-    cudaStream_t s_up = st->host_stream[0], s_run = st->host_stream[1];
+    // B first (every row slab needs all of it), then A and C move in row slabs on three streams:
+    // the upload of slab i+1, the GEMM of slab i and the download of slab i-1 run at the same
+    // time. The link carries both directions at once (measured: 1 GiB up and 0.5 GiB down together
+    // take 20.5 ms, 19.3 ms the upload alone), so what the call adds to the upload of A and B is the
+    // GEMM and the download of the last slab: slabs of about 1024 rows keep that under a millisecond
+    // at N = K = 16384.
+    cudaStream_t s_up = st->host_stream[0], s_run = st->host_stream[1], s_down = st->host_stream[2];
     if (!cuda_ok(cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
     size_t slabs = 1;
     if (M >= 2048 && M % 128 == 0) {
-        slabs = M >= 8192 ? 8 : 4;
+        slabs = M >= 16384 ? 16 : M >= 8192 ? 8 : 4;
         while (slabs > 1 && (M / 128) % slabs != 0) --slabs;
     }
     const size_t rows = M / slabs;
@@ -1079,9 +1090,12 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
         if (!cuda_ok(cudaStreamWaitEvent(s_run, st->host_event[0], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
         rc = entry(a_dst, st->host_b, c_dev, rows, N, K, nullptr, -1, s_run);
         if (rc != B200_HGEMM_OK) return rc;
-        if (!cuda_ok(cudaMemcpyAsync(c_dst, c_dev, rows * N * sizeof(__half), cudaMemcpyDeviceToHost, s_run), "cudaMemcpyAsync"))
+        if (!cuda_ok(cudaEventRecord(st->host_event[1], s_run), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaStreamWaitEvent(s_down, st->host_event[1], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaMemcpyAsync(c_dst, c_dev, rows * N * sizeof(__half), cudaMemcpyDeviceToHost, s_down), "cudaMemcpyAsync"))
             return B200_HGEMM_ERR_CUDA;
     }
+    if (!cuda_ok(cudaStreamSynchronize(s_down), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     if (!cuda_ok(cudaStreamSynchronize(s_run), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     if (!cuda_ok(cudaStreamSynchronize(s_up), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     return B200_HGEMM_OK;
