@@ -3,7 +3,8 @@
 The dispatch rules in ``csrc/hgemm_lib.cu`` (``select_plan``) were derived with this tool: every
 candidate is pre-heated and timed in turn, the whole list is repeated ``--rounds`` times, and the
 median / min / max TFLOP/s per candidate are printed, so that the order of measurement and the
-power state of the GPU do not decide the comparison.
+power state of the GPU do not decide the comparison. ``--burst`` times the way the reference driver
+does instead (a short run after an idle pause, before the power cap bites).
 
     python -m cuda_hgemm_b200.abtest --shape 8192x8192x8192 \
         --plans auto,cta2:256,cta1:256:g16,cta1:128,streamk:128,mcast:256
@@ -20,7 +21,7 @@ import statistics
 import sys
 
 from . import _native, api
-from .timing import cublas_callable, load_compare, time_graph, time_launches
+from .timing import cublas_callable, load_compare, time_burst, time_graph, time_launches
 
 VARIANTS = {"cta1": _native.VARIANT_CTA1, "cta2": _native.VARIANT_CTA2, "streamk": _native.VARIANT_STREAMK,
             "simt": _native.VARIANT_SIMT, "mcast": _native.VARIANT_CTA2_MCAST}
@@ -53,6 +54,8 @@ def main(argv=None) -> int:
     ap.add_argument("--rounds", type=int, default=3)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--graph", action="store_true", help="time 20 launches per CUDA graph instead of stream launches")
+    ap.add_argument("--burst", action="store_true",
+                    help="the reference driver's protocol: idle pause, 3 warm-up and --steps timed launches, no pre-heat")
     ap.add_argument("--dist", choices=("uniform", "normal"), default="uniform")
     args = ap.parse_args(argv)
 
@@ -84,7 +87,12 @@ def main(argv=None) -> int:
     results = {name: [] for name in candidates}
     for _ in range(args.rounds):
         for name, fn in candidates.items():
-            ms = time_graph(torch, fn) if args.graph else time_launches(torch, fn, 3, args.steps)
+            if args.graph:
+                ms = time_graph(torch, fn)
+            elif args.burst:
+                ms = time_burst(torch, fn, 3, args.steps)
+            else:
+                ms = time_launches(torch, fn, 3, args.steps)
             results[name].append(gflop / ms)
     if api.last_device_error() != 0:
         print("device-side wait expired", file=sys.stderr)

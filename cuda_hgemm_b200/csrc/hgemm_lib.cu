@@ -10,6 +10,7 @@
 #include <dlfcn.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <math.h>
 #include <string.h>
 
 #include <atomic>
@@ -294,30 +295,40 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     const double kb = static_cast<double>(k_blocks);
     auto waves = [](uint64_t work, uint64_t slots) { return static_cast<double>((work + slots - 1) / slots); };
 
-    // The arrangements with 256 x 256 outputs per CTA: 512 x 256 tiles on pairs, or 512 x 512 tiles on
-    // groups of four CTAs when the single-GPU companion library with the multicast kernel is there.
-    // A tile costs twice the k-blocks of a 256 x 256 pair tile, less what the smaller operand traffic
-    // buys under the power cap (5-7 %), plus about a microsecond in which the tensor pipe waits for the
-    // epilogue to drain tensor memory. Their epilogue is TMA stores only (N % 8 == 0).
-    const bool big_ok = (N % 8 == 0) && k_blocks >= 24;
-    const bool mc_ok = big_ok && mc_launch_fn(512) != nullptr;
-    const uint64_t tiles_big = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 256);
-    const uint64_t tiles_mc = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 512);
-
     if (pairs256 >= 2 * pair_slots) {
-        // two or more full waves of CTA pairs: the tensor-bound regime. Measured against each other
-        // at 3072..16384 (K from 1024 to 16384): the larger tiles win from K = 2048 up wherever their
-        // last wave is no emptier, by 2 % at 4096^3 and 10 % at 16384^3.
-        const double t256 = waves(pairs256, pair_slots) * kb * 0.37;
-        const double tbig = big_ok ? waves(tiles_big, pair_slots) * (kb * 0.70 + 1.0) : 1e30;
-        const double tmc = mc_ok ? waves(tiles_mc, sms / 4) * (kb * 0.685 + 1.0) : 1e30;
+        // Two or more full waves of CTA pairs: the tensor-bound regime. 256 x 256 tiles on pairs, unless
+        // the arrangements with 256 x 256 outputs per CTA apply: 512 x 256 tiles on pairs, or 512 x 512
+        // tiles on groups of four CTAs when the single-GPU companion library with the multicast kernel
+        // is there. Those move fewer bytes per flop, which under the power cap means a higher clock:
+        // +10 % at 16384^3, +4 % at 8192 x 8192 x 2048, level at 4096^3, and behind below that (the run
+        // is over before the cap bites), at K < 1536 (the tensor pipe waits about a microsecond per tile
+        // for the epilogue to drain tensor memory) and wherever their last wave is emptier (3840^3,
+        // 7168^3). Their epilogue is TMA stores only (N % 8 == 0). Measured with abtest.py, both protocols.
         pl->variant = B200_VARIANT_CTA2;
         pl->bn = 256;
-        if (tbig < t256 && tbig <= tmc) {
-            pl->bn = 512;
-        } else if (tmc < t256) {
-            pl->variant = B200_VARIANT_CTA2_MCAST;
-            pl->bn = 512;
+        const double flops = 2.0 * static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
+        if (N % 8 == 0 && k_blocks >= 24 && flops >= 2.0 * 4096.0 * 4096.0 * 4096.0) {
+            // share of the launched tile area that is output, last wave included
+            auto fill = [&](uint64_t tiles, uint64_t slots, double tile_area) {
+                return static_cast<double>(M) * static_cast<double>(N) / (waves(tiles, slots) * static_cast<double>(slots) * tile_area);
+            };
+            const uint64_t tiles_big = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 256);
+            const uint64_t tiles_mc = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 512);
+            const double f256 = fill(pairs256, pair_slots, 256.0 * 256.0);
+            const double fbig = fill(tiles_big, pair_slots, 512.0 * 256.0);
+            const double fmc = mc_launch_fn(512) ? fill(tiles_mc, sms / 4, 512.0 * 512.0) : 0.0;
+            // what the larger tiles gain at equal fill grows with the length of the run (measured:
+            // pairs +0.5 % at 4096^3, +4 % at 8192^3, +7 % at 16384^3; groups of four 2 % more)
+            const double doublings = log2(flops / (2.0 * 4096.0 * 4096.0 * 4096.0));
+            const double gain_big = 0.005 + 0.012 * doublings;
+            const double gain_mc = gain_big + 0.02;
+            const double s256 = f256, sbig = fbig * (1.0 + gain_big), smc = fmc * (1.0 + gain_mc);
+            if (smc > s256 && smc >= sbig) {
+                pl->variant = B200_VARIANT_CTA2_MCAST;
+                pl->bn = 512;
+            } else if (sbig > s256) {
+                pl->bn = 512;
+            }
         }
         return;
     }
@@ -336,7 +347,7 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     // (about 4 TB/s for this pattern): with full-height tiles that costs more than a ragged last
     // wave does, so stream-k only wins here when the tiles are few and k is long
     auto partial_us = [&](int bn) { return 2.0 * sms * 2.0 * (128.0 * bn * 4.0) / 4.0e6; };
-    constexpr int kCands = 8;
+    constexpr int kCands = 6;
     Candidate cands[kCands] = {
         {B200_VARIANT_CTA1, 256, waves(tiles256, sms) * kb * 0.35 + 2.0},
         {B200_VARIANT_CTA1, 128, waves(tiles128, sms) * kb * 0.33 + 1.5},
@@ -346,10 +357,6 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         {B200_VARIANT_CTA2, 256, waves(pairs256, pair_slots) * kb * 0.335 + 2.5},
         {B200_VARIANT_STREAMK, 256, static_cast<double>(tiles256) * kb / sms * 0.35 + 4.0 + partial_us(256)},
         {B200_VARIANT_STREAMK, 128, static_cast<double>(tiles128) * kb / sms * 0.33 + 4.0 + partial_us(128)},
-        // the large tiles only where they fill nine tenths of a wave (measured: behind at 2304 and
-        // 2560 with 45 and 50 tiles for 74 pairs, ahead at 3072 with 72)
-        {B200_VARIANT_CTA2, 512, big_ok && tiles_big * 10 >= pair_slots * 9 ? waves(tiles_big, pair_slots) * (kb * 0.64 + 1.0) + 2.5 : 1e30},
-        {B200_VARIANT_CTA2_MCAST, 512, mc_ok && tiles_mc * 10 >= (sms / 4) * 9 ? waves(tiles_mc, sms / 4) * (kb * 0.625 + 1.0) + 2.5 : 1e30},
     };
     if (M % 256 != 0) cands[3].us *= 1.0 + 128.0 / static_cast<double>(M);  // the pair's second CTA idles on the last rows
     if (k_blocks < 16) cands[4].us = cands[5].us = 1e30;                    // too little k to split

@@ -44,6 +44,25 @@ def time_launches(torch, fn, warmup, steps):
     return e0.elapsed_time(e1) / steps
 
 
+def time_burst(torch, fn, warmup=3, steps=10, idle_s=0.25):
+    """Mean milliseconds of `steps` back-to-back calls issued after an idle pause and `warmup` calls:
+    the reference driver's protocol (a short run on a GPU that is not yet under its power cap)."""
+    import time
+
+    torch.cuda.synchronize()
+    time.sleep(idle_s)
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
 def time_graph(torch, fn, launches=20, replays=5):
     """Mean milliseconds per call when `launches` calls are captured into one CUDA graph: removes the
     interpreter's per-call cost, which dominates kernels of a few microseconds."""
