@@ -37,6 +37,7 @@ VARIANT_CTA2 = 1
 VARIANT_STREAMK = 2
 VARIANT_SIMT = 3
 VARIANT_CTA2_MCAST = 4
+VARIANT_SKINNY = 5
 
 
 class Plan(Structure):

@@ -76,19 +76,21 @@ struct alignas(64) GemmParams {
     } while (0)
 #endif
 
-template <int BN, int STAGES, int CG>
+template <int BN, int STAGES, int CG, int KPS = 1>
 struct KernelTraits {
+    static_assert(KPS == 1 || KPS == 2, "a stage holds one or two 64-wide k-blocks");
     static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN must be a multiple of 64 up to 256");
     static_assert(CG == 1 || CG == 2, "CG is the CTA-pair size");
     static constexpr uint32_t kARows = kBM;
     static constexpr uint32_t kBRows = BN / CG;
     static constexpr uint32_t kABytes = kARows * kBK * 2;
     static constexpr uint32_t kBBytes = kBRows * kBK * 2;
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kBlockBytes = kABytes + kBBytes;   // one k-block of A and B
+    static constexpr uint32_t kStageBytes = KPS * kBlockBytes;  // [A0][B0] or [A0][B0][A1][B1]
     static constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;  // two accumulators; power of two
     static constexpr uint32_t kBarrierBytes = 256;
     static constexpr uint32_t kSmemBytes = 1024 + STAGES * kStageBytes + kStagingBytes + kBarrierBytes;
-    static_assert((kStageBytes % 1024) == 0, "stages must keep 1024-byte alignment");
+    static_assert((kBlockBytes % 1024) == 0, "operand slabs must keep 1024-byte alignment");
     static_assert(kSmemBytes <= 232448, "exceeds 227 KB of shared memory");
     static_assert((2 * STAGES + 4) * 8 + 16 <= kBarrierBytes, "barrier area too small");
 };
@@ -143,9 +145,11 @@ __device__ __forceinline__ void store_row_chunk32(__half *c, uint32_t row, uint3
     }
 }
 
-template <int BN, int STAGES, int CG, int MODE>
+// KPS = k-blocks per stage. With KPS = 2, GemmParams::k_blocks and every k index of the work
+// decomposition count pairs of k-blocks (one stage each); a pair that reaches past K reads zeros there.
+template <int BN, int STAGES, int CG, int MODE, int KPS = 1>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
-    using T = KernelTraits<BN, STAGES, CG>;
+    using T = KernelTraits<BN, STAGES, CG, KPS>;
     static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
 
     extern __shared__ uint8_t smem_raw[];
@@ -236,20 +240,28 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         ok = false;
                         break;
                     }
-                    const uint32_t sa = base + stage * T::kStageBytes;
-                    const uint32_t sb = sa + T::kABytes;
-                    const int32_t kx = static_cast<int32_t>(kb * kBK);
+                    const uint32_t slot = base + stage * T::kStageBytes;
                     if (CG == 1) {
                         mbar_arrive_expect_tx(full_bar + 8u * stage, T::kStageBytes);
-                        tma_load_2d(sa, &p.tm_a, kx, row_a, full_bar + 8u * stage);
-                        tma_load_2d(sb, &p.tm_b, kx, row_b, full_bar + 8u * stage);
+#pragma unroll
+                        for (uint32_t j = 0; j < KPS; ++j) {
+                            const uint32_t sa = slot + j * T::kBlockBytes;
+                            const int32_t kx = static_cast<int32_t>((kb * KPS + j) * kBK);  // past K: zero fill
+                            tma_load_2d(sa, &p.tm_a, kx, row_a, full_bar + 8u * stage);
+                            tma_load_2d(sa + T::kABytes, &p.tm_b, kx, row_b, full_bar + 8u * stage);
+                        }
                     } else {
                         // Both CTAs' copies complete on the leader's barrier; the leader alone
                         // posts the expected byte count for the pair.
                         if (cta_rank == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * T::kStageBytes);
                         const uint32_t leader_bar = map_to_cta(full_bar + 8u * stage, 0);
-                        tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
-                        tma_load_2d_pair(sb, &p.tm_b, kx, row_b, leader_bar);
+#pragma unroll
+                        for (uint32_t j = 0; j < KPS; ++j) {
+                            const uint32_t sa = slot + j * T::kBlockBytes;
+                            const int32_t kx = static_cast<int32_t>((kb * KPS + j) * kBK);
+                            tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
+                            tma_load_2d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, leader_bar);
+                        }
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -289,13 +301,16 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
 #ifdef B200_TIMELINE
                     if (it == 0 && kb == seg.kb0) B200_STAMP(4);
 #endif
-                    const uint32_t sa = base + stage * T::kStageBytes;
-                    const uint64_t da = umma_smem_desc_sw128(sa);
-                    const uint64_t db = umma_smem_desc_sw128(sa + T::kABytes);
+                    const uint32_t slot = base + stage * T::kStageBytes;
 #pragma unroll
-                    for (uint32_t k = 0; k < kBK / 16; ++k) {
-                        // 16 halves = 32 bytes along K inside the swizzle atom -> +2 in the address field
-                        umma_f16<CG>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > seg.kb0 || k > 0) ? 1u : 0u);
+                    for (uint32_t j = 0; j < KPS; ++j) {
+                        const uint64_t da = umma_smem_desc_sw128(slot + j * T::kBlockBytes);
+                        const uint64_t db = umma_smem_desc_sw128(slot + j * T::kBlockBytes + T::kABytes);
+#pragma unroll
+                        for (uint32_t k = 0; k < kBK / 16; ++k) {
+                            // 16 halves = 32 bytes along K inside the swizzle atom -> +2 in the address field
+                            umma_f16<CG>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > seg.kb0 || j > 0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     if (CG == 1) {
                         umma_commit(empty_bar + 8u * stage);

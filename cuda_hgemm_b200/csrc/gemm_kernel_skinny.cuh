@@ -1,0 +1,232 @@
+// Kernel for a short A (M <= 64 rows): the weight matrix B streams through the MMA's row operand.
+//
+// C[M x N] = A[M x K] * B^T with M of a decode batch (16 ... 64 rows) is bound by reading B once from
+// HBM. hgemm_tcgen05_kernel puts A on the 128 rows of the MMA, so every k-block stages a 16 KB slab of
+// A that is mostly padding next to 16 KB of B, six stages deep, and the thread that issues the MMAs
+// needs about 0.28 us per k-block for its own instructions (a barrier test, four MMAs, a commit):
+// 112 CTAs x 16 KB / 0.28 us is 6.4 TB/s, the HBM rate itself.
+//
+// Here the operands are swapped: 128 rows of B are the MMA's row operand, the MT >= M rows of A its
+// column operand (UMMA 128 x MT x 16), and the accumulator holds C transposed: tensor-memory lane = column
+// of C, tensor-memory column = row of C. A stage is two k-blocks (32 KB of B and 2 x MT x 128 B of A)
+// under one barrier round trip, six stages deep for MT = 16: twice the bytes of B in flight per SM and
+// 0.20 us of issue time per k-block. One CTA computes one (128-column tile, k-range) pair; when the tiles
+// are too few to fill the GPU (N = 4096: 32) the k-range is cut into equal slices whose FP32 partial
+// results go to a workspace and are summed by skinny_reduce_kernel, which follows in the stream.
+//
+// Operand layouts, swizzle, bounded waits and the error word are those of hgemm_tcgen05_kernel
+// (gemm_kernel.cuh); the reference has no counterpart (its kernels tile every shape alike,
+// src/mma/mma_async_stage4.cu:54-70).
+#pragma once
+
+#include "gemm_kernel.cuh"
+
+namespace b200 {
+
+struct alignas(64) SkinnyParams {
+    CUtensorMap tm_w;  // B as {K, N}, box {64, 128}
+    CUtensorMap tm_x;  // A as {K, M}, box {64, MT}
+    __half *c;
+    float *partials;  // slices x MT x n_pad FP32, used when slices > 1
+    uint32_t *error_word;
+    uint32_t m, n, k;
+    uint32_t k_blocks;
+    uint32_t n_tiles;        // 128-column tiles of C
+    uint32_t slices;         // k-ranges per tile
+    uint32_t kb_per_slice;   // k-blocks per k-range (the last one may be shorter, never empty)
+    uint32_t n_pad;          // row pitch of the partial results, in floats
+};
+
+template <int MT, int STAGES, int KPS>
+struct SkinnyTraits {
+    static_assert(MT == 16 || MT == 32 || MT == 64, "rows of A per tile");
+    static_assert(KPS == 1 || KPS == 2, "k-blocks per stage");
+    static constexpr uint32_t kWBytes = 128 * kBK * 2;
+    static constexpr uint32_t kXBytes = MT * kBK * 2;
+    static constexpr uint32_t kBlockBytes = kWBytes + kXBytes;
+    static constexpr uint32_t kStageBytes = KPS * kBlockBytes;
+    static constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
+    static constexpr uint32_t kSmemBytes = 1024 + STAGES * kStageBytes + 256;
+    static_assert((kBlockBytes % 1024) == 0, "operand slabs must keep 1024-byte alignment");
+    static_assert(kSmemBytes <= 232448, "exceeds 227 KB of shared memory");
+    static_assert((2 * STAGES + 1) * 8 + 16 <= 256, "barrier area too small");
+};
+
+template <int MT, int STAGES, int KPS>
+__global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_constant__ SkinnyParams p) {
+    using T = SkinnyTraits<MT, STAGES, KPS>;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - raw_addr);
+    const uint32_t bars = base + STAGES * T::kStageBytes;
+    uint8_t *bars_ptr = base_ptr + STAGES * T::kStageBytes;
+    const uint32_t full_bar = bars;
+    const uint32_t empty_bar = bars + 8u * STAGES;
+    const uint32_t tfull_bar = bars + 16u * STAGES;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_ptr + 16u * STAGES + 8u);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t tile = blockIdx.x % p.n_tiles;
+    const uint32_t slice = blockIdx.x / p.n_tiles;
+    const uint32_t kb0 = slice * p.kb_per_slice;
+    const uint32_t kb1 = min(p.k_blocks, kb0 + p.kb_per_slice);
+    const uint32_t n0 = tile * 128u;
+
+    if (warp == 0) {
+        if (lane < static_cast<uint32_t>(STAGES)) {
+            mbar_init(full_bar + 8u * lane, 1);
+            mbar_init(empty_bar + 8u * lane, 1);
+        } else if (lane == static_cast<uint32_t>(STAGES)) {
+            mbar_init(tfull_bar, 1);
+        } else if (lane == static_cast<uint32_t>(STAGES) + 1u) {
+            *abort_flag = 0;
+        }
+        fence_mbar_init();
+        __syncwarp();
+    }
+    if (warp == 2 && lane == 0) {
+        tma_prefetch_desc(&p.tm_w);
+        tma_prefetch_desc(&p.tm_x);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t *>(tmem_slot)), T::kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
+            for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
+                if (!mbar_wait(empty_bar + 8u * stage, phase ^ 1u, abort_flag)) break;
+                const uint32_t slot = base + stage * T::kStageBytes;
+                // a k-block past the end of this k-range is not loaded; its share of the stage is not waited for
+                const uint32_t blocks = min(static_cast<uint32_t>(KPS), kb1 - kb);
+                mbar_arrive_expect_tx(full_bar + 8u * stage, blocks * T::kBlockBytes);
+                for (uint32_t j = 0; j < blocks; ++j) {
+                    const uint32_t sw = slot + j * T::kBlockBytes;
+                    const int32_t kx = static_cast<int32_t>((kb + j) * kBK);
+                    tma_load_2d(sw, &p.tm_w, kx, static_cast<int32_t>(n0), full_bar + 8u * stage);
+                    tma_load_2d(sw + T::kWBytes, &p.tm_x, kx, 0, full_bar + 8u * stage);
+                }
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16_f32(128, MT);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
+                if (!mbar_wait(full_bar + 8u * stage, phase, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after_sync();
+                const uint32_t slot = base + stage * T::kStageBytes;
+                const uint32_t blocks = min(static_cast<uint32_t>(KPS), kb1 - kb);
+                for (uint32_t j = 0; j < blocks; ++j) {
+                    const uint64_t dw = umma_smem_desc_sw128(slot + j * T::kBlockBytes);
+                    const uint64_t dx = umma_smem_desc_sw128(slot + j * T::kBlockBytes + T::kWBytes);
+#pragma unroll
+                    for (uint32_t k = 0; k < kBK / 16; ++k) {
+                        umma_f16<1>(tmem_base, dw + 2u * k, dx + 2u * k, idesc, (kb > kb0 || j > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(empty_bar + 8u * stage);
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (ok) umma_commit(tfull_bar);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        // lane of tensor memory = column of C (n), column of tensor memory = row of C (m)
+        const uint32_t q = warp & 3u;
+        const uint32_t n = n0 + q * 32u + lane;
+        pdl_wait_prior_grids();  // C (or the workspace) may still be read by the previous kernel
+        uint32_t ready = 1;
+        if (lane == 0) ready = mbar_wait(tfull_bar, 0, abort_flag) ? 1u : 0u;
+        ready = __shfl_sync(0xffffffffu, ready, 0);
+        if (ready) {
+            tcgen05_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16);
+#pragma unroll
+            for (uint32_t c = 0; c < MT / 16; ++c) {
+                uint32_t r[16];
+                tmem_ld_32x32b_x16(taddr + c * 16u, r);
+                tmem_ld_wait();
+                if (n < p.n) {
+                    if (p.slices == 1) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; ++j) {
+                            const uint32_t m = c * 16u + j;
+                            // 32 lanes write 32 consecutive halves of one row of C
+                            if (m < p.m) p.c[static_cast<size_t>(m) * p.n + n] = __float2half_rn(__uint_as_float(r[j]));
+                        }
+                    } else {
+                        float *ws = p.partials + static_cast<size_t>(slice) * MT * p.n_pad;
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; ++j) {
+                            const uint32_t m = c * 16u + j;
+                            if (m < p.m) ws[static_cast<size_t>(m) * p.n_pad + n] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        // give copies still in flight time to land before shared memory is released
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+        if (threadIdx.x == 0) atomicExch(p.error_word, static_cast<uint32_t>(kDevWaitTimeout));
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, T::kTmemCols);
+    }
+}
+
+constexpr int kSkinnyReduceThreads = 256;
+
+// C[m][n] = sum over the k-ranges of their FP32 partial results, in range order, rounded to FP16 once.
+__global__ void __launch_bounds__(kSkinnyReduceThreads) skinny_reduce_kernel(const float *partials, __half *c, uint32_t m,
+                                                                            uint32_t n, uint32_t n_pad, uint32_t mt,
+                                                                            uint32_t slices) {
+    pdl_wait_prior_grids();
+    const uint32_t col = blockIdx.x * kSkinnyReduceThreads + threadIdx.x;
+    const uint32_t row = blockIdx.y;
+    if (row >= m || col >= n) return;
+    float acc = 0.f;
+    for (uint32_t s = 0; s < slices; ++s) {
+        acc += partials[(static_cast<size_t>(s) * mt + row) * n_pad + col];
+    }
+    c[static_cast<size_t>(row) * n + col] = __float2half_rn(acc);
+}
+
+}  // namespace b200

@@ -21,6 +21,7 @@
 #include "../../include/b200_hgemm.h"
 #include "gemm_kernel.cuh"
 #include "gemm_kernel_big.cuh"
+#include "gemm_kernel_skinny.cuh"
 
 namespace b200 {
 
@@ -221,13 +222,16 @@ static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) {
 
 static bool plan_is_tensor(const b200_hgemm_plan &pl) {
     return pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_CTA2 || pl.variant == B200_VARIANT_STREAMK ||
-           pl.variant == B200_VARIANT_CTA2_MCAST;
+           pl.variant == B200_VARIANT_CTA2_MCAST || pl.variant == B200_VARIANT_SKINNY;
 }
 
 static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     if (pl.variant == B200_VARIANT_SIMT) return B200_HGEMM_OK;
     if (!plan_is_tensor(pl)) return B200_HGEMM_ERR_UNSUPPORTED;
-    if (pl.variant == B200_VARIANT_CTA2_MCAST) {
+    if (pl.variant == B200_VARIANT_SKINNY) {
+        // bn is the number of rows of A a tile holds (M may not exceed it; checked where M is known)
+        if (pl.bn != 16 && pl.bn != 32 && pl.bn != 64) return B200_HGEMM_ERR_UNSUPPORTED;
+    } else if (pl.variant == B200_VARIANT_CTA2_MCAST) {
         // bn names the CTA arrangement here: 256 = 128 x 256 per CTA, 512 = 256 x 256 per CTA
         if ((pl.bn != 256 && pl.bn != 512) || N % 8 != 0 || !mc_launch_fn(pl.bn)) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 512) {
@@ -241,9 +245,26 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     }
     if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 64) return B200_HGEMM_ERR_UNSUPPORTED;
     if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
-    if (pl.tma_store && N % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (pl.tma_store && N % 8 != 0 && pl.variant != B200_VARIANT_SKINNY) return B200_HGEMM_ERR_UNSUPPORTED;  // (that kernel stores by element)
     if (pl.parts < 0 || pl.group_m < 0 || pl.grid < 0) return B200_HGEMM_ERR_INVALID_ARG;
     return B200_HGEMM_OK;
+}
+
+// k-blocks per pipeline stage of the kernel a plan runs. Tiles narrower than 256 columns take two:
+// the thread that issues the MMAs spends about 0.28 us per stage on its own instructions (a
+// barrier wait, four MMAs, a commit; measured with one CTA alone on the GPU, the same for every
+// tile width), which the four MMAs of a 256-column slab cover and those of a narrower slab do not;
+// one wait and one commit per two k-blocks brought 128 x 64 tiles from 0.28 to 0.20 us per k-block
+// and the M = 128 decode shape from 3.8 to 4.2 TB/s. The kernels count k in stages, so everything
+// that cuts k-ranges (stream-k ranges, workspace sizes) counts the same units.
+static uint32_t plan_kps(const b200_hgemm_plan &pl) {
+    if (pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_STREAMK) return (pl.bn == 128 || pl.bn == 64) ? 2u : 1u;
+    if (pl.variant == B200_VARIANT_CTA2) return pl.bn == 128 ? 2u : 1u;
+    return 1u;
+}
+
+static uint32_t plan_k_units(const b200_hgemm_plan &pl, size_t K) {
+    return ceil_div_u32(K, 64u * plan_kps(pl));
 }
 
 static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, uint32_t tiles, uint32_t k_blocks) {
@@ -276,6 +297,14 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     const uint64_t tiles256 = m_blocks * ceil_div_u32(N, 256);
     const uint64_t tiles128 = m_blocks * ceil_div_u32(N, 128);
 
+    if (M <= 64) {
+        // decode batches: B through the MMA's row operand, deeper ring, k cut only when the column tiles
+        // are few (measured against the 128-row tiles below at N = 14336, K = 4096 and the transpose:
+        // +18 % at M = 16, +10 % at M = 64)
+        pl->variant = B200_VARIANT_SKINNY;
+        pl->bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        return;
+    }
     if (M <= 128) {
         if (tiles128 * 4 >= 3ull * sms) {  // e.g. N = 14336: 112 tiles on 148 SMs
             pl->variant = B200_VARIANT_CTA1;
@@ -378,10 +407,10 @@ static bool pdl_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, int CG, int MODE>
+template <int BN, int STAGES, int CG, int MODE, int KPS = 1>
 static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
-    using T = KernelTraits<BN, STAGES, CG>;
-    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE>;
+    using T = KernelTraits<BN, STAGES, CG, KPS>;
+    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE, KPS>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -503,7 +532,7 @@ static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid
 static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, size_t K, const b200_hgemm_plan &pl) {
     if (pl.variant != B200_VARIANT_STREAMK) return 0;
     const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, pl.bn);
-    const uint32_t parts = streamk_parts(pl, st, tiles, ceil_div_u32(K, 64));
+    const uint32_t parts = streamk_parts(pl, st, tiles, plan_k_units(pl, K));
     return kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * pl.bn * sizeof(float));
 }
 
@@ -586,6 +615,124 @@ static int run_simt(const void *A, const void *B, void *C, size_t M, size_t N, s
     return B200_HGEMM_OK;
 }
 
+// ---- short A (M <= 64): B streams through the MMA's row operand (gemm_kernel_skinny.cuh) ----
+static uint32_t skinny_slices(const b200_hgemm_plan &pl, const DeviceState &st, size_t N, size_t K) {
+    const uint32_t tiles = ceil_div_u32(N, 128);
+    const uint32_t k_blocks = ceil_div_u32(K, 64);
+    const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
+    uint32_t slices = pl.parts > 0 ? static_cast<uint32_t>(pl.parts) : 0u;
+    if (slices == 0) {
+        // cut k only when the column tiles leave most of the GPU idle, and keep 8 k-blocks per slice
+        slices = (tiles * 5 >= sms * 3) ? 1u : sms / tiles;
+        const uint32_t most = k_blocks / 8 > 0 ? k_blocks / 8 : 1u;
+        if (slices > most) slices = most;
+    }
+    if (slices > k_blocks) slices = k_blocks;
+    if (slices < 1) slices = 1;
+    const uint32_t per = ceil_div_u32(k_blocks, slices);
+    return ceil_div_u32(k_blocks, per);  // no empty slice
+}
+
+static size_t skinny_workspace_bytes(const b200_hgemm_plan &pl, const DeviceState &st, size_t N, size_t K) {
+    const uint32_t slices = skinny_slices(pl, st, N, K);
+    if (slices <= 1) return 0;
+    const size_t n_pad = (N + 31) / 32 * 32;
+    return static_cast<size_t>(slices) * pl.bn * n_pad * sizeof(float);
+}
+
+template <int MT, int STAGES, int KPS>
+static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream) {
+    using T = SkinnyTraits<MT, STAGES, KPS>;
+    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS>;
+    if (!st.attr_set[attr_slot]) {
+        std::lock_guard<std::mutex> lock(st.mu);
+        if (!st.attr_set[attr_slot]) {
+            if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes), "cudaFuncSetAttribute")) {
+                return B200_HGEMM_ERR_CUDA;
+            }
+            st.attr_set[attr_slot] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(p.n_tiles * p.slices, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = T::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, p), "cudaLaunchKernelEx")) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_HGEMM_OK;
+}
+
+static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+                      const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes,
+                      uint32_t *error_word) {
+    if (M > static_cast<size_t>(pl.bn)) return B200_HGEMM_ERR_UNSUPPORTED;
+    SkinnyParams p;
+    memset(&p, 0, sizeof(p));
+    p.c = static_cast<__half *>(C);
+    p.error_word = error_word;
+    p.m = static_cast<uint32_t>(M);
+    p.n = static_cast<uint32_t>(N);
+    p.k = static_cast<uint32_t>(K);
+    p.k_blocks = ceil_div_u32(K, 64);
+    p.n_tiles = ceil_div_u32(N, 128);
+    p.slices = skinny_slices(pl, st, N, K);
+    p.kb_per_slice = ceil_div_u32(p.k_blocks, p.slices);
+    p.n_pad = static_cast<uint32_t>((N + 31) / 32 * 32);
+    if (static_cast<uint64_t>(p.n_tiles) * p.slices > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
+    int rc = get_tensor_map(st, B, N, K, 128, 64, &p.tm_w);
+    if (rc != B200_HGEMM_OK) return rc;
+    rc = get_tensor_map(st, A, M, K, static_cast<uint32_t>(pl.bn), 64, &p.tm_x);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (p.slices > 1) {
+        const size_t need = skinny_workspace_bytes(pl, st, N, K);
+        uint8_t *ws = nullptr;
+        if (ws_override) {
+            if (ws_override_bytes < need) return B200_HGEMM_ERR_WORKSPACE;
+            ws = static_cast<uint8_t *>(ws_override);
+        } else {
+            rc = workspace_for(st, stream, need, &ws);
+            if (rc != B200_HGEMM_OK) return rc;
+        }
+        p.partials = reinterpret_cast<float *>(ws);
+    }
+    if (pl.bn == 16) {
+        rc = launch_skinny<16, 6, 2>(st, 11, p, stream);
+    } else if (pl.bn == 32) {
+        rc = launch_skinny<32, 5, 2>(st, 12, p, stream);
+    } else {
+        rc = launch_skinny<64, 4, 2>(st, 13, p, stream);
+    }
+    if (rc != B200_HGEMM_OK || p.slices == 1) return rc;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(ceil_div_u32(N, kSkinnyReduceThreads), static_cast<unsigned>(M), 1);
+    cfg.blockDim = dim3(kSkinnyReduceThreads, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    if (!cuda_ok(cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, static_cast<const float *>(p.partials), p.c, p.m, p.n, p.n_pad,
+                                    static_cast<uint32_t>(pl.bn), p.slices),
+                 "cudaLaunchKernelEx")) {
+        cudaGetLastError();
+        return B200_HGEMM_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_HGEMM_OK;
+}
+
 static int check_args(const void *A, const void *B, const void *C, size_t M, size_t N, size_t K) {
     if (!A || !B || !C || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
     if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return B200_HGEMM_ERR_UNSUPPORTED;
@@ -600,6 +747,10 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (pl.variant == B200_VARIANT_SIMT) return run_simt(A, B, C, M, N, K, stream);
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u) {
         return B200_HGEMM_ERR_MISALIGNED;
+    }
+    if (pl.variant == B200_VARIANT_SKINNY) {
+        return run_skinny(st, A, B, C, M, N, K, pl, stream, ws_override, ws_override_bytes,
+                          error_word_override ? error_word_override : st.error_word);
     }
     if (pl.variant == B200_VARIANT_CTA2_MCAST) {
         GemmParams mp;
@@ -640,7 +791,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     p.k = static_cast<uint32_t>(K);
     p.m_blocks = ceil_div_u32(M, big ? 512u : 128u * cg);
     p.n_blocks = ceil_div_u32(N, bn);
-    p.k_blocks = ceil_div_u32(K, 64);
+    p.k_blocks = plan_k_units(pl, K);  // pipeline stages per tile: k-blocks, or pairs of them
     const uint64_t tiles64 = static_cast<uint64_t>(p.m_blocks) * p.n_blocks;
     if (tiles64 > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
     p.tiles = static_cast<uint32_t>(tiles64);
@@ -687,21 +838,21 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (pl.variant == B200_VARIANT_CTA1) {
         if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles>(st, 0, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 4, 1, kModeTiles>(st, 9, p, grid, stream);
-        if (bn == 128) return launch_kernel<128, 6, 1, kModeTiles>(st, 1, p, grid, stream);
-        return launch_kernel<64, 8, 1, kModeTiles>(st, 2, p, grid, stream);
+        if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2>(st, 1, p, grid, stream);
+        return launch_kernel<64, 4, 1, kModeTiles, 2>(st, 2, p, grid, stream);
     }
     if (big) return launch_big_kernel(st, p, grid, stream);
     if (pl.variant == B200_VARIANT_CTA2) {
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 6, 2, kModeTiles>(st, 10, p, grid, stream);
-        return launch_kernel<128, 8, 2, kModeTiles>(st, 4, p, grid, stream);
+        return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);
     }
     if (bn == 256) {
         rc = launch_kernel<256, 4, 1, kModeStreamK>(st, 5, p, grid, stream);
     } else if (bn == 128) {
-        rc = launch_kernel<128, 6, 1, kModeStreamK>(st, 6, p, grid, stream);
+        rc = launch_kernel<128, 3, 1, kModeStreamK, 2>(st, 6, p, grid, stream);
     } else {
-        rc = launch_kernel<64, 8, 1, kModeStreamK>(st, 7, p, grid, stream);
+        rc = launch_kernel<64, 4, 1, kModeStreamK, 2>(st, 7, p, grid, stream);
     }
     if (rc != B200_HGEMM_OK) return rc;
 
@@ -877,7 +1028,7 @@ int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N,
         pl.variant = B200_VARIANT_STREAMK;
         pl.bn = 128;
         const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, 128);
-        const uint32_t k_blocks = ceil_div_u32(K, 64);
+        const uint32_t k_blocks = plan_k_units(pl, K);  // the kernel's own unit of k: one pipeline stage
         uint32_t slices = (static_cast<uint32_t>(st->sm_count) + tiles - 1) / tiles;
         if (slices < 2) slices = 2;
         while (slices > 1 && k_blocks % slices != 0) --slices;  // equal slices only
@@ -967,6 +1118,17 @@ int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {
 
 size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan) {
     if (!plan || M == 0 || N == 0 || K == 0) return 0;
+    if (plan->variant == B200_VARIANT_SKINNY) {
+        if (plan->bn != 16 && plan->bn != 32 && plan->bn != 64) return 0;
+        DeviceState *st = nullptr;
+        if (current_state(&st) != B200_HGEMM_OK) {
+            cudaGetLastError();
+            DeviceState nominal;
+            nominal.sm_count = 148;
+            return skinny_workspace_bytes(*plan, nominal, N, K);
+        }
+        return skinny_workspace_bytes(*plan, *st, N, K);
+    }
     if (plan->variant != B200_VARIANT_STREAMK) return 0;
     if (plan->bn != 64 && plan->bn != 128 && plan->bn != 256) return 0;
     DeviceState *st = nullptr;

@@ -95,11 +95,17 @@ def test_plan_selection_covers_the_benchmark_shapes(native_lib):
     assert short_k.variant == _native.VARIANT_CTA2 and short_k.bn == 256
     # a last wave that the larger tiles would leave emptier
     assert api.select_plan(3584, 3584, 3584).bn == 256
-    # decode shapes: 112 whole tiles cover most SMs at N = 14336; at N = 4096 the k-range is split
-    assert api.select_plan(16, 14336, 4096).variant == _native.VARIANT_CTA1
-    skinny = api.select_plan(16, 4096, 14336)
-    assert skinny.variant == _native.VARIANT_STREAMK
-    assert api.workspace_bytes(16, 4096, 14336, skinny) > 0
+    # decode shapes: the kernel for a short A; whole k-ranges at N = 14336 (112 column tiles), cut at N = 4096
+    wide = api.select_plan(16, 14336, 4096)
+    assert wide.variant == _native.VARIANT_SKINNY and wide.bn == 16
+    assert api.workspace_bytes(16, 14336, 4096, wide) == 0
+    skinny = api.select_plan(48, 4096, 14336)
+    assert skinny.variant == _native.VARIANT_SKINNY and skinny.bn == 64
+    assert api.workspace_bytes(48, 4096, 14336, skinny) > 0
+    # 65 ... 128 rows keep the 128-row tiles
+    assert api.select_plan(128, 14336, 4096).variant == _native.VARIANT_CTA1
+    mid = api.select_plan(96, 4096, 14336)
+    assert mid.variant == _native.VARIANT_STREAMK and api.workspace_bytes(96, 4096, 14336, mid) > 0
     assert api.workspace_bytes(8192, 8192, 8192, big) == 0
     odd = api.select_plan(48, 40, 100)
     assert odd.variant == _native.VARIANT_SIMT  # K % 8 != 0: no TMA row pitch

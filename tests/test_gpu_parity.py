@@ -78,7 +78,7 @@ def test_auto_dispatch_matches_oracle(cuda_device, shape):
 
 
 @pytest.mark.parametrize("tma_store", [0, 1])
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 128, 192, 256])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (384, 512, 320), (200, 264, 136), (1024, 1536, 512)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_single_cta_tiles(cuda_device, shape, bn, tma_store):
@@ -88,7 +88,7 @@ def test_single_cta_tiles(cuda_device, shape, bn, tma_store):
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta1 bn={bn} tma_store={tma_store} {shape}")
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 192, 256])
 @pytest.mark.parametrize("shape", [(256, 256, 64), (256, 512, 320), (512, 2048, 1024), (328, 264, 136), (2048, 2048, 512)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_cta_pair_tiles(cuda_device, shape, bn):
@@ -180,6 +180,48 @@ def test_stream_k_ranges(cuda_device, bn, parts):
     A, B = make_inputs(M, N, K, seed=3)
     C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_STREAMK, bn, parts=parts))
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"stream-k bn={bn} parts={parts}")
+
+
+SHORT_A_CASES = [
+    # M, N, K, rows of A per tile, k-ranges per column tile (0 = the library's choice)
+    (16, 128, 64, 16, 0),      # one tile, one k-block: half a stage
+    (16, 256, 128, 16, 0),     # exactly one stage of two k-blocks
+    (1, 128, 192, 16, 0),      # a single row; three k-blocks
+    (9, 520, 200, 16, 0),      # tails in M, N (not a multiple of 8) and K
+    (16, 1024, 4096, 16, 0),
+    (16, 4096, 3584, 16, 3),   # three k-ranges of 19, 19 and 18 k-blocks
+    (17, 264, 136, 32, 2),
+    (32, 1000, 1096, 32, 0),
+    (33, 1024, 3584, 64, 0),
+    (64, 777, 320, 64, 5),     # as many k-ranges as k-blocks
+    (64, 3584, 1024, 64, 0),
+]
+
+
+@pytest.mark.parametrize("case", SHORT_A_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-mt{c[3]}-p{c[4]}")
+def test_short_a_kernel(cuda_device, case):
+    """M <= 64: B on the MMA's row operand, C accumulated transposed, k-ranges summed from FP32 partials."""
+    M, N, K, mt, parts = case
+    A, B = make_inputs(M, N, K, seed=31, dist="normal")
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_SKINNY, mt, parts=parts))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"short-A mt={mt} parts={parts} {(M, N, K)}")
+    # the same plan twice gives the same bits (the k-ranges are summed in a fixed order)
+    C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_SKINNY, mt, parts=parts))
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
+def test_short_a_kernel_refuses_more_rows_than_its_tile(cuda_device):
+    import torch
+
+    A, B = make_inputs(40, 256, 256, seed=32)
+    dA, dB = (torch.from_numpy(x).to(cuda_device) for x in (A, B))
+    C = torch.empty((40, 256), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_native.HgemmError) as e:
+        api.hgemm_ex(dA, dB, C, plan_of(_native.VARIANT_SKINNY, 32))
+    assert e.value.status == _native.ERR_UNSUPPORTED
+    with pytest.raises(_native.HgemmError) as e:
+        api.hgemm_ex(dA, dB, C, plan_of(_native.VARIANT_SKINNY, 48))
+    assert e.value.status == _native.ERR_UNSUPPORTED
 
 
 @pytest.mark.parametrize("M", [16, 32, 64, 128])
