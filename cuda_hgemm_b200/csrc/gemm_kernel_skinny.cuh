@@ -97,9 +97,16 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
         tmem_relinquish<1>();
     }
     tcgen05_fence_before_sync();
-    __syncthreads();
+    // The producer warp initialised the barriers itself and needs no tensor memory: it only
+    // announces its arrival and starts loading while the allocation completes.
+    if (warp == 0) {
+        __threadfence_block();
+        named_bar_arrive(2, kThreads);
+    } else {
+        named_bar_sync(2, kThreads);
+    }
     tcgen05_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
     pdl_launch_dependents();
 
     if (warp == 0) {
