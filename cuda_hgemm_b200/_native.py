@@ -38,6 +38,7 @@ VARIANT_STREAMK = 2
 VARIANT_SIMT = 3
 VARIANT_CTA2_MCAST = 4
 VARIANT_SKINNY = 5
+VARIANT_HYBRID = 6
 
 
 class Plan(Structure):

@@ -9,7 +9,7 @@ does instead (a short run after an idle pause, before the power cap bites).
     python -m cuda_hgemm_b200.abtest --shape 8192x8192x8192 \
         --plans auto,cta2:256,cta1:256:g16,cta1:128,streamk:128,mcast:256
 
-A plan is ``variant:bn[:gN][:pN][:nt]`` with variant one of cta1, cta2, streamk, mcast, skinny, simt;
+A plan is ``variant:bn[:gN][:pN][:nt]`` with variant one of cta1, cta2, streamk, hybrid, mcast, skinny, simt;
 ``gN`` sets the rasterisation band height, ``pN`` the number of stream-k ranges, ``nt`` turns the
 TMA-store epilogue off. ``auto`` is the library's own choice.
 """
@@ -24,7 +24,7 @@ from . import _native, api
 from .timing import cublas_callable, load_compare, time_burst, time_graph, time_launches
 
 VARIANTS = {"cta1": _native.VARIANT_CTA1, "cta2": _native.VARIANT_CTA2, "streamk": _native.VARIANT_STREAMK,
-            "simt": _native.VARIANT_SIMT, "mcast": _native.VARIANT_CTA2_MCAST, "skinny": _native.VARIANT_SKINNY}
+            "simt": _native.VARIANT_SIMT, "mcast": _native.VARIANT_CTA2_MCAST, "skinny": _native.VARIANT_SKINNY, "hybrid": _native.VARIANT_HYBRID}
 
 
 def parse_plan(text: str) -> _native.Plan:

@@ -58,6 +58,8 @@ struct alignas(64) GemmParams {
     uint32_t k_blocks;
     uint32_t tiles;
     uint32_t group_m;
+    uint32_t dp_tiles;   // stream-k: the first dp_tiles tiles are walked whole, strided by the grid; the rest is cut into k-ranges
+    uint32_t sk_parts;   // stream-k: workers that own a k-range (the first sk_parts; never more than there are units)
     uint32_t tma_store;  // 1: epilogue uses TMA stores (needs N % 8 == 0)
     uint32_t c_vec_ok;   // 1: 16-byte vector stores to C are aligned (N % 8 == 0)
 #ifdef B200_TIMELINE
@@ -114,12 +116,29 @@ struct WorkWalker<kModeTiles> {
     }
 };
 
+// Stream-k, optionally behind whole tiles: a worker first takes every workers-th of the first
+// dp_tiles tiles whole, then its contiguous range of the (tile, k) units of the remaining tiles.
+// With dp_tiles = a whole number of waves, only the ragged last wave pays for partial tiles.
 template <>
 struct WorkWalker<kModeStreamK> {
+    uint32_t t, step, dp_tiles, k_blocks;
+    bool has_range;  // only the first sk_parts workers own a k-range (there are never more ranges than units)
     SegmentWalker w;
     __device__ WorkWalker(const GemmParams &p, uint32_t worker, uint32_t workers)
-        : w(worker, workers, p.tiles, p.k_blocks) {}
-    __device__ bool next(Segment &s) { return w.next(s); }
+        : t(worker), step(workers), dp_tiles(p.dp_tiles), k_blocks(p.k_blocks), has_range(worker < p.sk_parts),
+          w(has_range ? worker : 0u, p.sk_parts > 0 ? p.sk_parts : 1u, p.tiles - p.dp_tiles, p.k_blocks) {}
+    __device__ bool next(Segment &s) {
+        if (t < dp_tiles) {
+            s.tile = t;
+            s.kb0 = 0;
+            s.kb1 = k_blocks;
+            t += step;
+            return true;
+        }
+        if (!has_range || !w.next(s)) return false;
+        s.tile += dp_tiles;
+        return true;
+    }
 };
 
 // 32 FP32 accumulator columns of one row -> FP16 -> global memory.
@@ -428,7 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 }
             } else {
                 // ---- this tile's k-range is shared with other workers: publish an FP32 partial
-                const uint32_t slot = partial_slot(worker, workers, p.tiles, p.k_blocks, seg.tile);
+                const uint32_t slot = partial_slot(worker, p.sk_parts, p.tiles - p.dp_tiles, p.k_blocks, seg.tile - p.dp_tiles);
                 float4 *ws = p.partials + static_cast<size_t>(slot) * (kBM * BN / 4);
                 const bool row_live = (m0 + row_in_tile) < p.m;
 #pragma unroll 1
@@ -495,6 +514,7 @@ struct ReduceParams {
     __half *c;
     uint32_t m, n;
     uint32_t m_blocks, n_blocks, k_blocks, tiles, group_m;
+    uint32_t dp_tiles;  // tiles the GEMM kernel walked whole; the k-ranges cover tiles [dp_tiles, tiles)
     uint32_t parts;
     uint32_t bn;
 };
@@ -502,9 +522,11 @@ struct ReduceParams {
 constexpr int kReduceThreads = 256;
 
 __global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const ReduceParams p) {
-    const uint32_t tile = blockIdx.y;
-    const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
-    const uint64_t u0 = static_cast<uint64_t>(tile) * p.k_blocks;
+    const uint32_t cut_tile = blockIdx.y;  // index among the tiles that are cut into k-ranges
+    const uint32_t cut_tiles = p.tiles - p.dp_tiles;
+    const uint32_t tile = p.dp_tiles + cut_tile;
+    const uint64_t total_units = static_cast<uint64_t>(cut_tiles) * p.k_blocks;
+    const uint64_t u0 = static_cast<uint64_t>(cut_tile) * p.k_blocks;
     const uint32_t part_first = part_of_unit(u0, p.parts, total_units);
     const uint32_t part_last = part_of_unit(u0 + p.k_blocks - 1, p.parts, total_units);
     pdl_wait_prior_grids();  // the partials are written by the GEMM kernel launched just before
@@ -520,7 +542,7 @@ __global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const Re
     const size_t slot_words = static_cast<size_t>(kBM) * p.bn / 4;
     // the first contributor may have entered this tile from an earlier one (its second slot);
     // every later contributor starts inside this tile (its first slot)
-    const uint32_t slot_first = partial_slot(part_first, p.parts, p.tiles, p.k_blocks, tile);
+    const uint32_t slot_first = partial_slot(part_first, p.parts, cut_tiles, p.k_blocks, cut_tile);
     const bool vec4_ok = (p.n % 4u) == 0;
 
     for (uint32_t i = blockIdx.x * kReduceThreads + threadIdx.x; i < total_words; i += gridDim.x * kReduceThreads) {

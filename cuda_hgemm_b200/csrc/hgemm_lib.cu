@@ -220,8 +220,13 @@ static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) {
     return static_cast<uint32_t>((a + b - 1) / b);
 }
 
+// STREAMK and HYBRID run the same kernel; HYBRID walks the full waves of tiles whole first.
+static bool plan_cuts_k(const b200_hgemm_plan &pl) {
+    return pl.variant == B200_VARIANT_STREAMK || pl.variant == B200_VARIANT_HYBRID;
+}
+
 static bool plan_is_tensor(const b200_hgemm_plan &pl) {
-    return pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_CTA2 || pl.variant == B200_VARIANT_STREAMK ||
+    return pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_CTA2 || plan_cuts_k(pl) ||
            pl.variant == B200_VARIANT_CTA2_MCAST || pl.variant == B200_VARIANT_SKINNY;
 }
 
@@ -239,7 +244,7 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
         if (N % 8 != 0 || !pl.tma_store) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.bn == 192) {
         // whole tiles only: between 128 and 256 for shapes whose tile count would leave a wave ragged
-        if (pl.variant == B200_VARIANT_STREAMK) return B200_HGEMM_ERR_UNSUPPORTED;
+        if (plan_cuts_k(pl)) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) {
         return B200_HGEMM_ERR_UNSUPPORTED;
     }
@@ -258,7 +263,7 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
 // and the M = 128 decode shape from 3.8 to 4.2 TB/s. The kernels count k in stages, so everything
 // that cuts k-ranges (stream-k ranges, workspace sizes) counts the same units.
 static uint32_t plan_kps(const b200_hgemm_plan &pl) {
-    if (pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_STREAMK) return (pl.bn == 128 || pl.bn == 64) ? 2u : 1u;
+    if (pl.variant == B200_VARIANT_CTA1 || plan_cuts_k(pl)) return (pl.bn == 128 || pl.bn == 64) ? 2u : 1u;
     if (pl.variant == B200_VARIANT_CTA2) return pl.bn == 128 ? 2u : 1u;
     return 1u;
 }
@@ -530,7 +535,7 @@ static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid
 }
 
 static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, size_t K, const b200_hgemm_plan &pl) {
-    if (pl.variant != B200_VARIANT_STREAMK) return 0;
+    if (!plan_cuts_k(pl)) return 0;
     const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, pl.bn);
     const uint32_t parts = streamk_parts(pl, st, tiles, plan_k_units(pl, K));
     return kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * pl.bn * sizeof(float));
@@ -813,9 +818,13 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     }
 
     uint32_t grid = 0;
-    if (pl.variant == B200_VARIANT_STREAMK) {
+    if (plan_cuts_k(pl)) {
         if (p.tiles > kMaxCountedTiles) return B200_HGEMM_ERR_UNSUPPORTED;
         const uint32_t parts = streamk_parts(pl, st, p.tiles, p.k_blocks);
+        // HYBRID: every full wave of tiles is walked whole; only the rest is cut into k-ranges
+        if (pl.variant == B200_VARIANT_HYBRID) p.dp_tiles = (p.tiles / parts) * parts;
+        const uint64_t cut_units = static_cast<uint64_t>(p.tiles - p.dp_tiles) * p.k_blocks;
+        p.sk_parts = cut_units < parts ? static_cast<uint32_t>(cut_units) : parts;  // no empty k-range
         const size_t need = kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * bn * sizeof(float));
         uint8_t *ws = nullptr;
         if (ws_override) {
@@ -858,8 +867,10 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
 
     // Tiles whose k-range was cut across ranges left FP32 partials behind: sum them. Nothing to do
     // when every range boundary falls on a tile boundary.
-    const uint32_t parts = grid;
-    const uint64_t total_units = static_cast<uint64_t>(p.tiles) * p.k_blocks;
+    const uint32_t parts = p.sk_parts;
+    const uint32_t cut_tiles = p.tiles - p.dp_tiles;
+    if (cut_tiles == 0) return B200_HGEMM_OK;
+    const uint64_t total_units = static_cast<uint64_t>(cut_tiles) * p.k_blocks;
     bool any_split = false;
     for (uint32_t part = 1; part < parts && !any_split; ++part) {
         any_split = (unit_begin(part, parts, total_units) % p.k_blocks) != 0;
@@ -874,6 +885,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     rp.n_blocks = p.n_blocks;
     rp.k_blocks = p.k_blocks;
     rp.tiles = p.tiles;
+    rp.dp_tiles = p.dp_tiles;
     rp.group_m = p.group_m;
     rp.parts = parts;
     rp.bn = static_cast<uint32_t>(bn);
@@ -884,7 +896,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (chunks < 1) chunks = 1;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(chunks, p.tiles, 1);
+    cfg.gridDim = dim3(chunks, cut_tiles, 1);
     cfg.blockDim = dim3(kReduceThreads, 1, 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr;
@@ -1129,7 +1141,7 @@ size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm
         }
         return skinny_workspace_bytes(*plan, *st, N, K);
     }
-    if (plan->variant != B200_VARIANT_STREAMK) return 0;
+    if (!plan_cuts_k(*plan)) return 0;
     if (plan->bn != 64 && plan->bn != 128 && plan->bn != 256) return 0;
     DeviceState *st = nullptr;
     if (current_state(&st) != B200_HGEMM_OK) {

@@ -53,10 +53,12 @@ enum {
     B200_VARIANT_CTA2_MCAST = 4, /* CTA pairs in clusters of four with the A slab delivered by TMA multicast;
                                    single-GPU builds only: it lives in libb200_hgemm_mc.so, which the library
                                    loads when present (B200_HGEMM_ERR_UNSUPPORTED otherwise); needs N % 8 == 0 */
-    B200_VARIANT_SKINNY = 5      /* M <= 64 (decode batches): B streams through the MMA's row operand and C is
+    B200_VARIANT_SKINNY = 5,     /* M <= 64 (decode batches): B streams through the MMA's row operand and C is
                                    accumulated transposed; plan.bn = rows of A per tile (16, 32 or 64, >= M),
                                    plan.parts = equal k-ranges per column tile (0 = library's choice), summed
                                    from an FP32 workspace when there is more than one */
+    B200_VARIANT_HYBRID = 6      /* as STREAMK, but every full wave of tiles (parts tiles each) is computed whole
+                                   and only the tiles of the ragged last wave are cut into k-ranges */
 };
 
 /* The dispatch decision for one shape. All fields are filled by b200_hgemm_select(); a

@@ -224,6 +224,30 @@ def test_short_a_kernel_refuses_more_rows_than_its_tile(cuda_device):
     assert e.value.status == _native.ERR_UNSUPPORTED
 
 
+HYBRID_CASES = [
+    # M, N, K, bn, parts (0 = one per SM)
+    (2304, 2304, 512, 256, 0),    # 162 tiles: one full wave whole, 14 tiles cut into k-ranges
+    (2304, 2304, 512, 128, 0),    # 324 tiles, two whole per worker, 28 cut; two k-blocks per stage
+    (1000, 1032, 1096, 256, 7),   # tails everywhere; 40 tiles on 7 workers: 35 whole, 5 cut
+    (1000, 1032, 1096, 64, 7),
+    (200, 1032, 1096, 128, 33),   # fewer tiles than workers: nothing whole, plain stream-k
+    (1280, 2560, 320, 256, 10),   # 100 tiles on 10 workers: nothing left to cut
+    (3840, 3840, 256, 256, 148),  # 6 cut tiles of 4 k-blocks: fewer units than workers
+]
+
+
+@pytest.mark.parametrize("case", HYBRID_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-bn{c[3]}-p{c[4]}")
+def test_whole_tiles_then_k_ranges(cuda_device, case):
+    """HYBRID: full waves of tiles computed whole, the ragged rest cut into k-ranges and summed."""
+    M, N, K, bn, parts = case
+    A, B = make_inputs(M, N, K, seed=41)
+    C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_HYBRID, bn, parts=parts, tma_store=1 if N % 8 == 0 else 0))
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"hybrid bn={bn} parts={parts} {(M, N, K)}")
+    # poison the workspace's idea of "clean": a second run must not depend on what the first left behind
+    C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_HYBRID, bn, parts=parts, tma_store=1 if N % 8 == 0 else 0))
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
 @pytest.mark.parametrize("M", [16, 32, 64, 128])
 def test_skinny_decode_shapes(cuda_device, M):
     # decode-like: activations ~ N(0,1), weights ~ N(0, 1/K); N and K scaled down 4x from 14336 x 4096
