@@ -264,7 +264,7 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
 // that cuts k-ranges (stream-k ranges, workspace sizes) counts the same units.
 static uint32_t plan_kps(const b200_hgemm_plan &pl) {
     if (pl.variant == B200_VARIANT_CTA1 || plan_cuts_k(pl)) return (pl.bn == 128 || pl.bn == 64) ? 2u : 1u;
-    if (pl.variant == B200_VARIANT_CTA2) return pl.bn == 128 ? 2u : 1u;
+    if (pl.variant == B200_VARIANT_CTA2) return (pl.bn == 128 || pl.bn == 192) ? 2u : 1u;
     return 1u;
 }
 
@@ -381,7 +381,8 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     // (about 4 TB/s for this pattern): with full-height tiles that costs more than a ragged last
     // wave does, so stream-k only wins here when the tiles are few and k is long
     auto partial_us = [&](int bn) { return 2.0 * sms * 2.0 * (128.0 * bn * 4.0) / 4.0e6; };
-    constexpr int kCands = 6;
+    constexpr int kCands = 7;
+    const uint64_t pairs192 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 192);
     Candidate cands[kCands] = {
         {B200_VARIANT_CTA1, 256, waves(tiles256, sms) * kb * 0.35 + 2.0},
         {B200_VARIANT_CTA1, 128, waves(tiles128, sms) * kb * 0.33 + 1.5},
@@ -391,7 +392,12 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         {B200_VARIANT_CTA2, 256, waves(pairs256, pair_slots) * kb * 0.335 + 2.5},
         {B200_VARIANT_STREAMK, 256, static_cast<double>(tiles256) * kb / sms * 0.35 + 4.0 + partial_us(256)},
         {B200_VARIANT_STREAMK, 128, static_cast<double>(tiles128) * kb / sms * 0.33 + 4.0 + partial_us(128)},
+        // pairs on 256 x 192 tiles (two k-blocks per stage): three quarters of the time of a 256-wide tile,
+        // so two ragged waves of them beat two ragged waves of those (measured: 2304^3 950 against 810
+        // TFLOP/s, 2560^3 1160 against 990; no gain where 256-wide tiles fit one wave, as at 1792^3)
+        {B200_VARIANT_CTA2, 192, pairs256 > pair_slots ? waves(pairs192, pair_slots) * kb * 0.27 + 2.5 : 1e30},
     };
+    if (M % 256 != 0) cands[6].us *= 1.0 + 128.0 / static_cast<double>(M);
     if (M % 256 != 0) cands[3].us *= 1.0 + 128.0 / static_cast<double>(M);  // the pair's second CTA idles on the last rows
     if (k_blocks < 16) cands[4].us = cands[5].us = 1e30;                    // too little k to split
     int best = 0;
@@ -853,7 +859,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (big) return launch_big_kernel(st, p, grid, stream);
     if (pl.variant == B200_VARIANT_CTA2) {
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
-        if (bn == 192) return launch_kernel<192, 6, 2, kModeTiles>(st, 10, p, grid, stream);
+        if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);
     }
     if (bn == 256) {
