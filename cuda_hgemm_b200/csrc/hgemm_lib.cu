@@ -1266,21 +1266,28 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
         while (slabs > 1 && (M / 128) % slabs != 0) --slabs;
     }
     const size_t rows = M / slabs;
-    for (size_t s = 0; s < slabs; ++s) {
-        const char *a_src = static_cast<const char *>(A_host) + s * rows * K * sizeof(__half);
-        char *a_dst = static_cast<char *>(st->host_a) + s * rows * K * sizeof(__half);
-        char *c_dev = static_cast<char *>(st->host_c) + s * rows * N * sizeof(__half);
-        char *c_dst = static_cast<char *>(C_host) + s * rows * N * sizeof(__half);
-        if (!cuda_ok(cudaMemcpyAsync(a_dst, a_src, rows * K * sizeof(__half), cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync"))
+    // What the call adds to the uploads is the GEMM and the download of the last slab: the last slab is
+    // cut into four once more (when its quarters are still whole 128-row blocks).
+    const size_t tail_parts = (slabs > 1 && rows % 512 == 0) ? 4 : 1;
+    const size_t pieces = slabs - 1 + tail_parts;
+    size_t row0 = 0;
+    for (size_t s = 0; s < pieces; ++s) {
+        const size_t rows_here = (s < slabs - 1) ? rows : rows / tail_parts;
+        const char *a_src = static_cast<const char *>(A_host) + row0 * K * sizeof(__half);
+        char *a_dst = static_cast<char *>(st->host_a) + row0 * K * sizeof(__half);
+        char *c_dev = static_cast<char *>(st->host_c) + row0 * N * sizeof(__half);
+        char *c_dst = static_cast<char *>(C_host) + row0 * N * sizeof(__half);
+        if (!cuda_ok(cudaMemcpyAsync(a_dst, a_src, rows_here * K * sizeof(__half), cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync"))
             return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaEventRecord(st->host_event[0], s_up), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaStreamWaitEvent(s_run, st->host_event[0], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
-        rc = entry(a_dst, st->host_b, c_dev, rows, N, K, nullptr, -1, s_run);
+        rc = entry(a_dst, st->host_b, c_dev, rows_here, N, K, nullptr, -1, s_run);
         if (rc != B200_HGEMM_OK) return rc;
         if (!cuda_ok(cudaEventRecord(st->host_event[1], s_run), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaStreamWaitEvent(s_down, st->host_event[1], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
-        if (!cuda_ok(cudaMemcpyAsync(c_dst, c_dev, rows * N * sizeof(__half), cudaMemcpyDeviceToHost, s_down), "cudaMemcpyAsync"))
+        if (!cuda_ok(cudaMemcpyAsync(c_dst, c_dev, rows_here * N * sizeof(__half), cudaMemcpyDeviceToHost, s_down), "cudaMemcpyAsync"))
             return B200_HGEMM_ERR_CUDA;
+        row0 += rows_here;
     }
     if (!cuda_ok(cudaStreamSynchronize(s_down), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     if (!cuda_ok(cudaStreamSynchronize(s_run), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;

@@ -173,10 +173,11 @@ def test_large_tiles_refuse_what_their_epilogue_cannot_store(cuda_device):
     assert e.value.status == _native.ERR_UNSUPPORTED
 
 
+@pytest.mark.parametrize("K", [1096, 1160])  # 18 k-blocks; 19, so that the last pair of k-blocks is half past K
 @pytest.mark.parametrize("parts", [0, 1, 7, 33, 148, 400])
 @pytest.mark.parametrize("bn", [64, 128, 256])
-def test_stream_k_ranges(cuda_device, bn, parts):
-    M, N, K = 200, 1032, 1096  # tails everywhere; 18 k-blocks
+def test_stream_k_ranges(cuda_device, bn, parts, K):
+    M, N = 200, 1032  # tails everywhere
     A, B = make_inputs(M, N, K, seed=3)
     C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_STREAMK, bn, parts=parts))
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"stream-k bn={bn} parts={parts}")
