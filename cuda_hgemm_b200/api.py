@@ -97,7 +97,9 @@ def b200HgemmSimt(A, B, C):
 
 
 def hgemm_ex(A, B, C, plan: Plan):
-    """Run an explicit plan (C ABI ``b200_hgemm_ex``)."""
+    """Run an explicit plan (C ABI ``b200_hgemm_ex``): ``plan.variant`` one of the ``_native.VARIANT_*``
+    kernel families, ``plan.bn`` the tile width (or, for the large-tile and short-A kernels, the
+    arrangement: see ``include/b200_hgemm.h``), ``plan.parts`` the number of k-ranges where k is cut."""
     import torch
 
     M, N, K = _shape_of(A, B, C)
@@ -123,6 +125,7 @@ def hgemm_host(A_host, B_host, C_host):
 
 
 def select_plan(M: int, N: int, K: int) -> Plan:
+    """The plan ``b200Hgemm`` would run for this shape on the current device (C ABI ``b200_hgemm_select``)."""
     plan = Plan()
     check(_native.load().b200_hgemm_select(M, N, K, ctypes.byref(plan)))
     return plan

@@ -280,14 +280,16 @@ static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, 
     return static_cast<uint32_t>(parts);
 }
 
-// Shape -> plan, from sweeps on B200 (square sizes 256..16384 and the skinny decode shapes):
-//  * CTA pairs on 256x256 tiles once there are enough of them to fill the 74 pairs about 1.35
-//    times over; this is the configuration whose operand traffic (64 B per SM clock at full
-//    tensor rate) the SM's L2 port sustains, so it is the one that runs tensor-bound;
-//  * below that, single-CTA tiles, as wide as still leaves 64 or more tiles: narrow tiles move
-//    more bytes per flop, but with few tiles the per-SM load rate is what limits;
-//  * M <= 128 (decode-like, HBM-bound): whole 128-wide tiles when they cover most SMs, else
-//    equal k-ranges over all SMs with the FP32 workspace reduce.
+// Shape -> plan, from measurements on B200 (square sizes 256..16384 in both timing protocols of
+// abtest.py, the decode shapes, the prefill shape):
+//  * M <= 64: the short-A kernel (B on the MMA's row operand);
+//  * 65 <= M <= 128 (decode-like, HBM-bound): whole 128-wide tiles when they cover most SMs, else equal
+//    k-ranges over all SMs with the FP32 workspace reduce;
+//  * two or more full waves of CTA pairs on 256 x 256 tiles: those pairs, or - for long runs with long
+//    k - 256 x 256 outputs per CTA (pairs on 512 x 256, groups of four on 512 x 512 with A multicast),
+//    whichever fills its waves best after what the larger tiles gain under the power cap;
+//  * in between: the candidate with the smallest estimated time among single-CTA tiles of three
+//    widths, pairs on 256 x 256 and 256 x 192, and stream-k.
 static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
     memset(pl, 0, sizeof(*pl));
     if (K % 8 != 0) {
