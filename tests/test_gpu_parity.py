@@ -77,6 +77,35 @@ def test_auto_dispatch_matches_oracle(cuda_device, shape):
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"auto {shape}")
 
 
+def _seeded_shapes(count, seed):
+    """Shapes drawn so that every branch of the dispatch is hit: decode batches, one to a few waves of
+    tiles, ragged waves, K with and without a multiple of 8, N with and without."""
+    rng = np.random.default_rng(seed)
+    shapes = []
+    for i in range(count):
+        kind = i % 5
+        if kind == 0:    # short A
+            M = int(rng.integers(1, 65)); N = int(rng.integers(1, 40)) * 64 + int(rng.integers(0, 3)) * 4; K = int(rng.integers(1, 60)) * 64
+        elif kind == 1:  # 65..128 rows
+            M = int(rng.integers(65, 129)); N = int(rng.integers(2, 30)) * 128; K = int(rng.integers(2, 40)) * 64 + 8 * int(rng.integers(0, 8))
+        elif kind == 2:  # a few tiles, tails everywhere
+            M = int(rng.integers(129, 1500)); N = int(rng.integers(1, 190)) * 8; K = int(rng.integers(1, 190)) * 8
+        elif kind == 3:  # around one to three waves of 128 x 256 tiles
+            M = int(rng.integers(8, 24)) * 128; N = int(rng.integers(4, 12)) * 256; K = int(rng.integers(1, 9)) * 64
+        else:            # anything, K not a multiple of 8 now and then
+            M = int(rng.integers(1, 700)); N = int(rng.integers(1, 700)); K = int(rng.integers(1, 700))
+        shapes.append((M, N, K))
+    return shapes
+
+
+@pytest.mark.parametrize("shape", _seeded_shapes(40, seed=20231), ids=lambda s: "x".join(map(str, s)))
+def test_seeded_shapes_through_the_dispatch(cuda_device, shape):
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=M * 7 + N * 3 + K, dist="normal" if M <= 128 else "uniform")
+    C = run(api.b200Hgemm, A, B, cuda_device)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"auto {shape} plan {api.select_plan(M, N, K).as_dict()}")
+
+
 @pytest.mark.parametrize("tma_store", [0, 1])
 @pytest.mark.parametrize("bn", [64, 128, 192, 256])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (384, 512, 320), (200, 264, 136), (1024, 1536, 512)],
