@@ -19,7 +19,8 @@ EXPORTED_SYMBOLS = (
     "b200_hgemm_set_workspace", "b200_hgemm_last_device_error", "b200_hgemm_status_string",
     "b200_hgemm_version", "b200_hgemm_launch_count", "b200_sched_tile_coord", "b200_sched_segments",
     "b200_sched_contributors", "b200_sched_partial_slot", "b200_debug_idesc", "b200_debug_smem_desc",
-    "b200_debug_wait_expiry",
+    "b200_debug_wait_expiry", "b200_partition_slab", "b200_mg_create", "b200_mg_destroy", "b200_mg_device_count",
+    "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
 )
 
 OK = 0
@@ -103,6 +104,24 @@ def load() -> ctypes.CDLL:
     lib.b200_sched_partial_slot.restype = c_uint32
     lib.b200_debug_wait_expiry.argtypes = [c_uint32, c_void_p]
     lib.b200_debug_wait_expiry.restype = c_int
+    lib.b200_partition_slab.argtypes = [c_size_t, c_int, c_int, POINTER(c_size_t), POINTER(c_size_t)]
+    lib.b200_partition_slab.restype = c_int
+    lib.b200_mg_create.argtypes = [POINTER(c_int), c_int, POINTER(c_void_p)]
+    lib.b200_mg_create.restype = c_int
+    lib.b200_mg_destroy.argtypes = [c_void_p]
+    lib.b200_mg_destroy.restype = c_int
+    lib.b200_mg_device_count.argtypes = [c_void_p]
+    lib.b200_mg_device_count.restype = c_int
+    lib.b200_mg_slab.argtypes = [c_void_p, c_size_t, c_int, POINTER(c_size_t), POINTER(c_size_t)]
+    lib.b200_mg_slab.restype = c_int
+    lib.b200_mg_hgemm.argtypes = [c_void_p, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), c_size_t, c_size_t, c_size_t]
+    lib.b200_mg_hgemm.restype = c_int
+    lib.b200_mg_gather_c.argtypes = [c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_size_t, c_size_t]
+    lib.b200_mg_gather_c.restype = c_int
+    lib.b200_mg_synchronize.argtypes = [c_void_p]
+    lib.b200_mg_synchronize.restype = c_int
+    lib.b200_mg_elapsed_ms_max.argtypes = [c_void_p, POINTER(ctypes.c_float)]
+    lib.b200_mg_elapsed_ms_max.restype = c_int
     lib.b200_debug_idesc.argtypes = [c_uint32, c_uint32]
     lib.b200_debug_idesc.restype = c_uint32
     lib.b200_debug_smem_desc.argtypes = [c_uint32]

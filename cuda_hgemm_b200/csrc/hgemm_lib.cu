@@ -1297,6 +1297,187 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     return B200_HGEMM_OK;
 }
 
+// ---- several GPUs from one process ----------------------------------------------------------
+struct b200_mg {
+    int n = 0;
+    int devices[kMaxDevices] = {};
+    cudaStream_t streams[kMaxDevices] = {};
+    cudaEvent_t start[kMaxDevices] = {};
+    cudaEvent_t stop[kMaxDevices] = {};
+    bool timed[kMaxDevices] = {};  // whether the last b200_mg_hgemm launched anything on the device
+};
+
+// Keeps the calling thread's current device across a loop over devices.
+struct DeviceRestore {
+    int prev = -1;
+    DeviceRestore() {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    }
+    ~DeviceRestore() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// Row blocks of 128 dealt out evenly over n devices, the first ones a block more.
+static void partition_slab(size_t M, int n, int index, size_t *row0, size_t *rows) {
+    const size_t blocks = (M + 127) / 128;
+    const size_t base = blocks / n, extra = blocks % n;
+    const size_t idx = static_cast<size_t>(index);
+    const size_t begin = idx * base + (idx < extra ? idx : extra);
+    const size_t count = base + (idx < extra ? 1 : 0);
+    const size_t lo = begin * 128 < M ? begin * 128 : M;
+    const size_t hi = (begin + count) * 128 < M ? (begin + count) * 128 : M;
+    *row0 = lo;
+    *rows = hi - lo;
+}
+
+static void mg_slab(const b200_mg *mg, size_t M, int index, size_t *row0, size_t *rows) {
+    partition_slab(M, mg->n, index, row0, rows);
+}
+
+int b200_partition_slab(size_t M, int n, int index, size_t *row0, size_t *rows) {
+    if (!row0 || !rows || n < 1 || index < 0 || index >= n) return B200_HGEMM_ERR_INVALID_ARG;
+    partition_slab(M, n, index, row0, rows);
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_create(const int *devices, int n, b200_mg **out) {
+    if (!devices || !out || n < 1 || n > kMaxDevices) return B200_HGEMM_ERR_INVALID_ARG;
+    int count = 0;
+    if (!cuda_ok(cudaGetDeviceCount(&count), "cudaGetDeviceCount")) return B200_HGEMM_ERR_CUDA;
+    for (int i = 0; i < n; ++i) {
+        if (devices[i] < 0 || devices[i] >= count) return B200_HGEMM_ERR_INVALID_ARG;
+        for (int j = 0; j < i; ++j) {
+            if (devices[j] == devices[i]) return B200_HGEMM_ERR_INVALID_ARG;
+        }
+    }
+    DeviceRestore restore;
+    b200_mg *mg = new b200_mg();
+    mg->n = n;
+    int rc = B200_HGEMM_OK;
+    for (int i = 0; i < n && rc == B200_HGEMM_OK; ++i) {
+        mg->devices[i] = devices[i];
+        DeviceState *st = nullptr;
+        if (!cuda_ok(cudaSetDevice(devices[i]), "cudaSetDevice")) {
+            rc = B200_HGEMM_ERR_CUDA;
+        } else if ((rc = current_state(&st)) == B200_HGEMM_OK && !st->sm100) {
+            rc = B200_HGEMM_ERR_NO_SM100;
+        } else if (rc == B200_HGEMM_OK &&
+                   (cudaStreamCreateWithFlags(&mg->streams[i], cudaStreamNonBlocking) != cudaSuccess ||
+                    cudaEventCreate(&mg->start[i]) != cudaSuccess || cudaEventCreate(&mg->stop[i]) != cudaSuccess)) {
+            rc = B200_HGEMM_ERR_CUDA;
+        }
+    }
+    if (rc != B200_HGEMM_OK) {
+        b200_mg_destroy(mg);
+        return rc;
+    }
+    *out = mg;
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_destroy(b200_mg *mg) {
+    if (!mg) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceRestore restore;
+    for (int i = 0; i < mg->n; ++i) {
+        if (cudaSetDevice(mg->devices[i]) != cudaSuccess) continue;
+        if (mg->streams[i]) {
+            cudaStreamSynchronize(mg->streams[i]);
+            cudaStreamDestroy(mg->streams[i]);
+        }
+        if (mg->start[i]) cudaEventDestroy(mg->start[i]);
+        if (mg->stop[i]) cudaEventDestroy(mg->stop[i]);
+    }
+    cudaGetLastError();
+    delete mg;
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_device_count(const b200_mg *mg) {
+    return mg ? mg->n : B200_HGEMM_ERR_INVALID_ARG;
+}
+
+int b200_mg_slab(const b200_mg *mg, size_t M, int index, size_t *row0, size_t *rows) {
+    if (!mg || !row0 || !rows || index < 0 || index >= mg->n) return B200_HGEMM_ERR_INVALID_ARG;
+    mg_slab(mg, M, index, row0, rows);
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_hgemm(b200_mg *mg, const void *const *A_slabs, const void *const *B_replicas, void *const *C_slabs, size_t M,
+                  size_t N, size_t K) {
+    if (!mg || !A_slabs || !B_replicas || !C_slabs || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceRestore restore;
+    // check everything before anything is launched
+    for (int i = 0; i < mg->n; ++i) {
+        size_t row0 = 0, rows = 0;
+        mg_slab(mg, M, i, &row0, &rows);
+        if (rows == 0) continue;
+        const int rc = check_args(A_slabs[i], B_replicas[i], C_slabs[i], rows, N, K);
+        if (rc != B200_HGEMM_OK) return rc;
+    }
+    for (int i = 0; i < mg->n; ++i) {
+        size_t row0 = 0, rows = 0;
+        mg_slab(mg, M, i, &row0, &rows);
+        mg->timed[i] = false;
+        if (rows == 0) continue;
+        if (!cuda_ok(cudaSetDevice(mg->devices[i]), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaEventRecord(mg->start[i], mg->streams[i]), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
+        const int rc = entry(A_slabs[i], B_replicas[i], C_slabs[i], rows, N, K, nullptr, -1, mg->streams[i]);
+        if (rc != B200_HGEMM_OK) return rc;
+        if (!cuda_ok(cudaEventRecord(mg->stop[i], mg->streams[i]), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
+        mg->timed[i] = true;
+    }
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_gather_c(b200_mg *mg, void *const *C_slabs, void *const *C_full, size_t M, size_t N) {
+    if (!mg || !C_slabs || !C_full || M == 0 || N == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceRestore restore;
+    for (int src = 0; src < mg->n; ++src) {
+        size_t row0 = 0, rows = 0;
+        mg_slab(mg, M, src, &row0, &rows);
+        if (rows == 0) continue;
+        if (!C_slabs[src]) return B200_HGEMM_ERR_INVALID_ARG;
+        if (!cuda_ok(cudaSetDevice(mg->devices[src]), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
+        for (int dst = 0; dst < mg->n; ++dst) {
+            if (!C_full[dst]) continue;
+            char *to = static_cast<char *>(C_full[dst]) + row0 * N * sizeof(__half);
+            // on the owner's stream, so the copy follows the multiply that produced the slab
+            if (!cuda_ok(cudaMemcpyPeerAsync(to, mg->devices[dst], C_slabs[src], mg->devices[src], rows * N * sizeof(__half),
+                                             mg->streams[src]),
+                         "cudaMemcpyPeerAsync")) {
+                return B200_HGEMM_ERR_CUDA;
+            }
+        }
+    }
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_synchronize(b200_mg *mg) {
+    if (!mg) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceRestore restore;
+    for (int i = 0; i < mg->n; ++i) {
+        if (!cuda_ok(cudaSetDevice(mg->devices[i]), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaStreamSynchronize(mg->streams[i]), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
+    }
+    return B200_HGEMM_OK;
+}
+
+int b200_mg_elapsed_ms_max(b200_mg *mg, float *ms) {
+    if (!mg || !ms) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceRestore restore;
+    float worst = 0.f;
+    for (int i = 0; i < mg->n; ++i) {
+        if (!mg->timed[i]) continue;
+        if (!cuda_ok(cudaSetDevice(mg->devices[i]), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
+        float t = 0.f;
+        if (!cuda_ok(cudaEventElapsedTime(&t, mg->start[i], mg->stop[i]), "cudaEventElapsedTime")) return B200_HGEMM_ERR_CUDA;
+        if (t > worst) worst = t;
+    }
+    *ms = worst;
+    return B200_HGEMM_OK;
+}
+
 // ---- host-side helpers for tests --------------------------------------------------------
 void b200_sched_tile_coord(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
                            uint32_t *n_blk) {

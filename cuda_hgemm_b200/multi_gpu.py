@@ -58,3 +58,66 @@ def slab_hgemm(A_slab, B, C_slab: Optional[object] = None, kernel=None):
         return C_slab
     (kernel or api.b200Hgemm)(A_slab, B, C_slab)
     return C_slab
+
+
+class SingleProcessGroup:
+    """Several GPUs driven from ONE process through the C ABI's ``b200_mg_*`` entry points.
+
+    The same row-slab partition as the one-process-per-GPU path above, for callers that hold all
+    devices in one process: ``hgemm`` launches every device's slab on a stream the handle owns and
+    returns; ``synchronize`` waits; ``elapsed_ms_max`` is the device time of the last multiply,
+    the maximum over the devices; ``gather_c`` copies the slabs into full C buffers by peer copies.
+    """
+
+    def __init__(self, devices):
+        import ctypes
+
+        from . import _native
+
+        self._native = _native
+        self._ct = ctypes
+        self.devices = [int(d) for d in devices]
+        arr = (ctypes.c_int * len(self.devices))(*self.devices)
+        handle = ctypes.c_void_p()
+        _native.check(_native.load().b200_mg_create(arr, len(self.devices), ctypes.byref(handle)))
+        self._handle = handle
+
+    def close(self):
+        if self._handle is not None:
+            self._native.load().b200_mg_destroy(self._handle)
+            self._handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def slab(self, M: int, index: int) -> Tuple[int, int]:
+        ct = self._ct
+        row0, rows = ct.c_size_t(), ct.c_size_t()
+        self._native.check(self._native.load().b200_mg_slab(self._handle, M, index, ct.byref(row0), ct.byref(rows)))
+        return row0.value, row0.value + rows.value
+
+    def _pointers(self, tensors):
+        ct = self._ct
+        return (ct.c_void_p * len(self.devices))(*[(t.data_ptr() if t is not None and t.numel() else None) for t in tensors])
+
+    def hgemm(self, A_slabs, B_replicas, C_slabs, M: int):
+        """``C_slabs[i] = A_slabs[i] * B_replicas[i]`` on ``devices[i]``; returns without waiting."""
+        N, K = B_replicas[0].shape
+        self._native.check(self._native.load().b200_mg_hgemm(
+            self._handle, self._pointers(A_slabs), self._pointers(B_replicas), self._pointers(C_slabs), M, N, K))
+
+    def gather_c(self, C_slabs, C_full, M: int, N: int):
+        """``C_full[i]`` (or ``None``) receives all slabs; ordered after the multiply on each owner's stream."""
+        self._native.check(self._native.load().b200_mg_gather_c(
+            self._handle, self._pointers(C_slabs), self._pointers(C_full), M, N))
+
+    def synchronize(self):
+        self._native.check(self._native.load().b200_mg_synchronize(self._handle))
+
+    def elapsed_ms_max(self) -> float:
+        ms = self._ct.c_float()
+        self._native.check(self._native.load().b200_mg_elapsed_ms_max(self._handle, self._ct.byref(ms)))
+        return float(ms.value)

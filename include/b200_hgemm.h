@@ -141,8 +141,37 @@ const char *b200_hgemm_version(void);
 /* Number of kernels this library has launched in this process (for launch accounting). */
 uint64_t b200_hgemm_launch_count(void);
 
+/* ---- several GPUs from one process: row slabs of C, B replicated --------------------------
+ * The reference is single-GPU (its only device knob is -gpu_rank, src/main.cu:45,51); these have no
+ * counterpart there. C (and A) are cut into contiguous row slabs, one per device, with boundaries on
+ * multiples of 128 rows (b200_mg_slab); every device multiplies its slab by its own copy of B with the
+ * single-GPU dispatch, on a stream the handle owns; no data crosses GPUs during the multiply. The
+ * launching thread loops over the devices (cudaSetDevice) and restores the device that was current. */
+typedef struct b200_mg b200_mg;
+
+/* `devices`: n distinct CUDA device ordinals, 1 <= n <= 64, every one an sm_100 GPU. */
+int b200_mg_create(const int *devices, int n, b200_mg **out);
+int b200_mg_destroy(b200_mg *mg);
+int b200_mg_device_count(const b200_mg *mg);
+/* Rows [*row0, *row0 + *rows) of C and A that device `index` (position in `devices`) owns; *rows may be 0. */
+int b200_mg_slab(const b200_mg *mg, size_t M, int index, size_t *row0, size_t *rows);
+/* A_slabs[i], B_replicas[i], C_slabs[i]: device pointers on devices[i] (A and C slabs as b200_mg_slab says,
+ * B complete). Launches on every device and returns without synchronising. M is the row count of the whole C. */
+int b200_mg_hgemm(b200_mg *mg, const void *const *A_slabs, const void *const *B_replicas, void *const *C_slabs, size_t M,
+                  size_t N, size_t K);
+/* Copies every slab of C into C_full[i] (M x N on devices[i]) for each i with C_full[i] != NULL, by peer copies
+ * ordered after the multiply on the owning device's stream: a gather when one entry is set, an all-gather
+ * when all are. */
+int b200_mg_gather_c(b200_mg *mg, void *const *C_slabs, void *const *C_full, size_t M, size_t N);
+/* Waits for everything launched through the handle. */
+int b200_mg_synchronize(b200_mg *mg);
+/* After b200_mg_synchronize: device time of the last b200_mg_hgemm, the maximum over the devices (ms). */
+int b200_mg_elapsed_ms_max(b200_mg *mg, float *ms);
+
 /* ---- host-side helpers exposed for tests (no GPU needed) -------------------------------- */
 
+/* The row slab of device `index` of `n` for a C of M rows: the rule b200_mg_slab applies (no handle needed). */
+int b200_partition_slab(size_t M, int n, int index, size_t *row0, size_t *rows);
 /* Tile rasterisation: linear tile id -> (m_blk, n_blk). */
 void b200_sched_tile_coord(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
                            uint32_t *n_blk);

@@ -404,6 +404,64 @@ def test_host_pointer_entry_point(cuda_device):
         assert_close_to_oracle(hC.numpy(), oracle.gemm_f32(A, B), f"host {M}x{N}x{K}")
 
 
+def _single_process_group_case(devices, M, N, K):
+    import torch
+
+    from cuda_hgemm_b200.multi_gpu import SingleProcessGroup
+
+    A, B = make_inputs(M, N, K, seed=51)
+    ref = oracle.gemm_f32(A, B)
+    with SingleProcessGroup(devices) as group:
+        slabs = [group.slab(M, i) for i in range(len(devices))]
+        assert slabs[0][0] == 0 and slabs[-1][1] == M and all(a[1] == b[0] for a, b in zip(slabs, slabs[1:]))
+        dA = [torch.from_numpy(A[lo:hi]).to(f"cuda:{d}") for d, (lo, hi) in zip(devices, slabs)]
+        dB = [torch.from_numpy(B).to(f"cuda:{d}") for d in devices]
+        dC = [torch.full((hi - lo, N), float("nan"), dtype=torch.float16, device=f"cuda:{d}") for d, (lo, hi) in zip(devices, slabs)]
+        full = [torch.full((M, N), float("nan"), dtype=torch.float16, device=f"cuda:{d}") for d in devices]
+        for _ in range(2):  # the second call reuses streams, events and cached tensor maps
+            group.hgemm(dA, dB, dC, M)
+            group.gather_c(dC, full, M, N)
+            group.synchronize()
+        assert group.elapsed_ms_max() > 0.0
+        for d in devices:
+            with torch.cuda.device(d):
+                assert api.last_device_error() == 0
+        for (lo, hi), c in zip(slabs, dC):
+            if hi > lo:
+                assert_close_to_oracle(c.cpu().numpy(), ref[lo:hi], f"slab rows {lo}:{hi}")
+        # the gathered copies are the slabs, bit for bit, on every device
+        whole = np.concatenate([c.cpu().numpy() for c in dC if c.shape[0]], axis=0)
+        for f in full:
+            assert np.array_equal(f.cpu().numpy().view(np.uint16), whole.view(np.uint16))
+        # and a slab is what the single-GPU call computes for those rows
+        single = run(api.b200Hgemm, A[slabs[0][0]:slabs[0][1]], B, torch.device(f"cuda:{devices[0]}"))
+        assert np.array_equal(single.view(np.uint16), dC[0].cpu().numpy().view(np.uint16))
+
+
+def test_single_process_group_on_one_device(cuda_device):
+    """The b200_mg_* entry points with a group of one: the same code path as with eight."""
+    _single_process_group_case([0], 640, 520, 328)
+
+
+def test_single_process_group_on_all_devices(cuda_device):
+    import torch
+
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("one GPU in this run")
+    _single_process_group_case(list(range(n)), 128 * (2 * n + 1) + 40, 1032, 576)  # uneven slabs and a ragged last one
+
+
+def test_single_process_group_rejects_bad_device_lists(cuda_device):
+    import ctypes
+
+    lib = _native.load()
+    handle = ctypes.c_void_p()
+    for devices in ([], [0, 0], [-1], [4096]):
+        arr = (ctypes.c_int * max(1, len(devices)))(*devices)
+        assert lib.b200_mg_create(arr, len(devices), ctypes.byref(handle)) == _native.ERR_INVALID_ARG
+
+
 def test_error_codes_on_device(cuda_device):
     import torch
 

@@ -25,6 +25,22 @@ def test_row_slabs_tile_aligned_and_complete(M, world):
     assert max(heights) - min(heights) < 256 or M < 128 * world
 
 
+def test_c_abi_partition_matches_the_python_rule(native_lib):
+    """b200_partition_slab (the rule b200_mg_hgemm applies) and partition.row_slabs are the same function."""
+    import ctypes
+
+    for M in (0, 1, 127, 128, 129, 300, 1000, 8192, 16384, 16385, 100000):
+        for world in (1, 2, 3, 4, 7, 8):
+            expected = row_slabs(M, world)
+            for index in range(world):
+                row0, rows = ctypes.c_size_t(), ctypes.c_size_t()
+                assert native_lib.b200_partition_slab(M, world, index, ctypes.byref(row0), ctypes.byref(rows)) == 0
+                assert (row0.value, row0.value + rows.value) == expected[index], (M, world, index)
+    row0, rows = ctypes.c_size_t(), ctypes.c_size_t()
+    assert native_lib.b200_partition_slab(1024, 0, 0, ctypes.byref(row0), ctypes.byref(rows)) == -1
+    assert native_lib.b200_partition_slab(1024, 2, 2, ctypes.byref(row0), ctypes.byref(rows)) == -1
+
+
 def test_benchmark_partitions():
     assert [h - l for l, h in row_slabs(16384, 8)] == [2048] * 8
     assert [h - l for l, h in row_slabs(8192, 4)] == [2048] * 4
