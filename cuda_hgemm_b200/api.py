@@ -131,6 +131,21 @@ def select_plan(M: int, N: int, K: int) -> Plan:
     return plan
 
 
+def select_plan_untuned(M: int, N: int, K: int) -> Plan:
+    """The plan the dispatch rules give, ignoring the table of tuned plans."""
+    plan = Plan()
+    check(_native.load().b200_hgemm_select_untuned(M, N, K, ctypes.byref(plan)))
+    return plan
+
+
+def load_plan_table(path) -> int:
+    """Replace the table of tuned plans with the file at ``path`` (``None``: no table); returns the entry count."""
+    n = _native.load().b200_hgemm_load_plan_table(None if path is None else str(path).encode())
+    if n < 0:
+        check(n)
+    return n
+
+
 def workspace_bytes(M: int, N: int, K: int, plan: Plan) -> int:
     return int(_native.load().b200_hgemm_workspace_bytes(M, N, K, ctypes.byref(plan)))
 

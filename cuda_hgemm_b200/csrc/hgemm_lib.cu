@@ -280,6 +280,79 @@ static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, 
     return static_cast<uint32_t>(parts);
 }
 
+// ------------------------------------------------------------------------------------------
+// tuned plans: shapes whose best plan was measured (autotune.py) override the rules below
+// ------------------------------------------------------------------------------------------
+// A text file, one line per shape: "M N K variant bn parts group_m tma_store"; '#' starts a comment.
+// It is read once, from B200_HGEMM_PLAN_TABLE if that is set, else from plan_table.txt in the
+// directory above the one this library lies in (the package directory); B200_HGEMM_NO_PLAN_TABLE
+// turns it off; b200_hgemm_load_plan_table() replaces it at run time. An entry that the
+// running configuration cannot serve (the multicast companion is absent) is skipped at look-up.
+struct TunedPlan {
+    uint64_t m, n, k;
+    b200_hgemm_plan plan;
+};
+static std::mutex g_table_mu;
+static std::vector<TunedPlan> g_table;
+static bool g_table_loaded = false;
+
+static int read_plan_table(const char *path, std::vector<TunedPlan> *out) {
+    FILE *f = fopen(path, "r");
+    if (!f) return -1;
+    char line[256];
+    int entries = 0;
+    while (fgets(line, sizeof(line), f)) {
+        char *hash = strchr(line, '#');
+        if (hash) *hash = 0;
+        unsigned long long m, n, k;
+        int variant, bn, parts, group_m, tma_store;
+        if (sscanf(line, "%llu %llu %llu %d %d %d %d %d", &m, &n, &k, &variant, &bn, &parts, &group_m, &tma_store) != 8) continue;
+        TunedPlan t;
+        t.m = m;
+        t.n = n;
+        t.k = k;
+        memset(&t.plan, 0, sizeof(t.plan));
+        t.plan.variant = variant;
+        t.plan.bn = bn;
+        t.plan.parts = parts;
+        t.plan.group_m = group_m;
+        t.plan.tma_store = tma_store;
+        out->push_back(t);
+        ++entries;
+    }
+    fclose(f);
+    return entries;
+}
+
+static void load_default_plan_table_locked() {
+    g_table_loaded = true;
+    if (getenv("B200_HGEMM_NO_PLAN_TABLE")) return;
+    if (const char *env = getenv("B200_HGEMM_PLAN_TABLE")) {
+        read_plan_table(env, &g_table);
+        return;
+    }
+    Dl_info info;
+    if (!dladdr(reinterpret_cast<const void *>(&g_launches), &info) || !info.dli_fname) return;
+    std::string path(info.dli_fname);
+    size_t slash = path.rfind('/');
+    path = slash == std::string::npos ? std::string(".") : path.substr(0, slash);
+    read_plan_table((path + "/../plan_table.txt").c_str(), &g_table);
+}
+
+static bool tuned_plan(size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
+    std::lock_guard<std::mutex> lock(g_table_mu);
+    if (!g_table_loaded) load_default_plan_table_locked();
+    for (const TunedPlan &t : g_table) {
+        if (t.m == M && t.n == N && t.k == K) {
+            if (validate_plan(t.plan, N, K) != B200_HGEMM_OK) return false;
+            if (t.plan.variant == B200_VARIANT_SKINNY && M > static_cast<size_t>(t.plan.bn)) return false;
+            *pl = t.plan;
+            return true;
+        }
+    }
+    return false;
+}
+
 // Shape -> plan, from measurements on B200 (square sizes 256..16384 in both timing protocols of
 // abtest.py, the decode shapes, the prefill shape):
 //  * M <= 64: the short-A kernel (B on the MMA's row operand);
@@ -290,12 +363,13 @@ static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, 
 //    whichever fills its waves best after what the larger tiles gain under the power cap;
 //  * in between: the candidate with the smallest estimated time among single-CTA tiles of three
 //    widths, pairs on 256 x 256 and 256 x 192, and stream-k.
-static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
+static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl, bool use_table = true) {
     memset(pl, 0, sizeof(*pl));
     if (K % 8 != 0) {
         pl->variant = B200_VARIANT_SIMT;
         return;
     }
+    if (use_table && tuned_plan(M, N, K, pl)) return;
     const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
     pl->tma_store = (N % 8 == 0) ? 1 : 0;
     pl->group_m = 0;
@@ -1133,6 +1207,30 @@ int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {
         return B200_HGEMM_OK;
     }
     select_plan(*st, M, N, K, plan);
+    return B200_HGEMM_OK;
+}
+
+int b200_hgemm_load_plan_table(const char *path) {
+    std::vector<TunedPlan> fresh;
+    int entries = 0;
+    if (path && (entries = read_plan_table(path, &fresh)) < 0) return B200_HGEMM_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_table_mu);
+    g_table.swap(fresh);
+    g_table_loaded = true;
+    return entries;
+}
+
+int b200_hgemm_select_untuned(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {
+    if (!plan || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    DeviceState *st = nullptr;
+    if (current_state(&st) != B200_HGEMM_OK) {
+        cudaGetLastError();
+        DeviceState nominal;
+        nominal.sm_count = 148;
+        select_plan(nominal, M, N, K, plan, false);
+        return B200_HGEMM_OK;
+    }
+    select_plan(*st, M, N, K, plan, false);
     return B200_HGEMM_OK;
 }
 

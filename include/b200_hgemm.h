@@ -121,6 +121,15 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
 /* Fills *plan with the library's choice for (M, N, K) on the current device. */
 int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan);
 
+/* Tuned plans. b200_hgemm_select() (and so b200_hgemm) first looks the shape up in a table of measured
+ * plans, a text file with one "M N K variant bn parts group_m tma_store" line per shape that
+ * `python -m cuda_hgemm_b200.autotune` writes: B200_HGEMM_PLAN_TABLE if set, else plan_table.txt in the
+ * directory above the library's; B200_HGEMM_NO_PLAN_TABLE=1 disables it. This call replaces the table at run
+ * time (NULL: empty table) and returns the number of entries read, or a negative status.
+ * b200_hgemm_select_untuned() answers from the rules alone. */
+int b200_hgemm_load_plan_table(const char *path);
+int b200_hgemm_select_untuned(size_t M, size_t N, size_t K, b200_hgemm_plan *plan);
+
 /* Bytes of device workspace `plan` needs for this shape (0 for whole-tile variants). */
 size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan);
 

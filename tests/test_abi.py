@@ -88,26 +88,54 @@ def test_plan_selection_covers_the_benchmark_shapes(native_lib):
     from cuda_hgemm_b200 import api
 
     # long k, many tiles: 256 x 256 outputs per CTA (pairs, or groups of four with the multicast companion)
-    big = api.select_plan(8192, 8192, 8192)
+    big = api.select_plan_untuned(8192, 8192, 8192)
     assert big.variant in (_native.VARIANT_CTA2, _native.VARIANT_CTA2_MCAST) and big.bn == 512
     # short k: the drain of a full tensor memory would show; 128 x 256 per CTA with two accumulator sets
-    short_k = api.select_plan(4096, 4096, 1024)
+    short_k = api.select_plan_untuned(4096, 4096, 1024)
     assert short_k.variant == _native.VARIANT_CTA2 and short_k.bn == 256
     # a last wave that the larger tiles would leave emptier
-    assert api.select_plan(3584, 3584, 3584).bn == 256
+    assert api.select_plan_untuned(3584, 3584, 3584).bn == 256
     # decode shapes: the kernel for a short A; whole k-ranges at N = 14336 (112 column tiles), cut at N = 4096
-    wide = api.select_plan(16, 14336, 4096)
+    wide = api.select_plan_untuned(16, 14336, 4096)
     assert wide.variant == _native.VARIANT_SKINNY and wide.bn == 16
     assert api.workspace_bytes(16, 14336, 4096, wide) == 0
-    skinny = api.select_plan(48, 4096, 14336)
+    skinny = api.select_plan_untuned(48, 4096, 14336)
     assert skinny.variant == _native.VARIANT_SKINNY and skinny.bn == 64
     assert api.workspace_bytes(48, 4096, 14336, skinny) > 0
     # 65 ... 128 rows keep the 128-row tiles
-    assert api.select_plan(128, 14336, 4096).variant == _native.VARIANT_CTA1
-    mid = api.select_plan(96, 4096, 14336)
+    assert api.select_plan_untuned(128, 14336, 4096).variant == _native.VARIANT_CTA1
+    mid = api.select_plan_untuned(96, 4096, 14336)
     assert mid.variant == _native.VARIANT_STREAMK and api.workspace_bytes(96, 4096, 14336, mid) > 0
     assert api.workspace_bytes(8192, 8192, 8192, big) == 0
-    odd = api.select_plan(48, 40, 100)
+    odd = api.select_plan_untuned(48, 40, 100)
     assert odd.variant == _native.VARIANT_SIMT  # K % 8 != 0: no TMA row pitch
-    ragged_n = api.select_plan(512, 1001, 512)
+    ragged_n = api.select_plan_untuned(512, 1001, 512)
     assert ragged_n.tma_store == 0
+
+
+def test_tuned_plan_table_overrides_the_rules(native_lib, tmp_path):
+    from cuda_hgemm_b200 import api
+
+    table = tmp_path / "plan_table.txt"
+    table.write_text("# a comment line\n"
+                     "2304 2304 2304 1 128 0 4 1   # pairs on 256 x 128, bands of 4\n"
+                     "40 4096 4096 5 32 0 0 1      # short-A tile of 32 rows for 40 rows: cannot be served\n"
+                     "not a plan line\n"
+                     "512 512 512 2 64 7 0 1\n")
+    try:
+        assert api.load_plan_table(table) == 3
+        tuned = api.select_plan(2304, 2304, 2304)
+        assert (tuned.variant, tuned.bn, tuned.group_m) == (_native.VARIANT_CTA2, 128, 4)
+        assert (api.select_plan(512, 512, 512).variant, api.select_plan(512, 512, 512).parts) == (_native.VARIANT_STREAMK, 7)
+        # the rules still answer when asked directly, and for every shape the table does not list or cannot serve
+        rules = api.select_plan_untuned(2304, 2304, 2304)
+        assert (rules.variant, rules.bn) != (tuned.variant, tuned.bn)
+        assert api.select_plan(2304, 2304, 2305).variant == api.select_plan_untuned(2304, 2304, 2305).variant
+        unserved = api.select_plan(40, 4096, 4096)
+        assert (unserved.variant, unserved.bn) == (_native.VARIANT_SKINNY, 64)
+        with pytest.raises(_native.HgemmError):
+            api.load_plan_table(tmp_path / "missing.txt")
+    finally:
+        assert api.load_plan_table(None) == 0
+    assert api.select_plan(2304, 2304, 2304).bn == api.select_plan_untuned(2304, 2304, 2304).bn
+
