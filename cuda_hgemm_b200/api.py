@@ -109,6 +109,24 @@ def hgemm_ex(A, B, C, plan: Plan):
     return C
 
 
+def hgemm_fused(A, B, C, alpha: float = 1.0, beta: float = 0.0, bias=None, c_in=None):
+    """``C = alpha * A @ B.T + beta * c_in + bias`` in one kernel (C ABI ``b200_hgemm_fused``); ``bias`` has one
+    FP16 value per column of C, ``c_in`` is an FP16 ``[M, N]`` tensor (``C`` itself for an in-place update)."""
+    import torch
+
+    M, N, K = _shape_of(A, B, C)
+    if bias is not None and (bias.dtype != torch.float16 or bias.numel() != N or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous float16 tensor with one value per column of C")
+    if c_in is not None and (c_in.dtype != torch.float16 or tuple(c_in.shape) != (M, N) or not c_in.is_contiguous()):
+        raise ValueError("c_in must be a contiguous float16 [M, N] tensor")
+    epi = _native.Epilogue(alpha, beta, bias.data_ptr() if bias is not None else None,
+                           c_in.data_ptr() if c_in is not None else None)
+    with torch.cuda.device(A.device):
+        check(_native.load().b200_hgemm_fused(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, ctypes.byref(epi),
+                                              _stream_of(A)))
+    return C
+
+
 def hgemm_host(A_host, B_host, C_host):
     """HOST tensors in, HOST tensor out (C ABI ``b200_hgemm_host``): uploads, multiplies, downloads, synchronises."""
     import torch

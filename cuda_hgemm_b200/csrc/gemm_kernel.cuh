@@ -62,6 +62,10 @@ struct alignas(64) GemmParams {
     uint32_t sk_parts;   // stream-k: workers that own a k-range (the first sk_parts; never more than there are units)
     uint32_t tma_store;  // 1: epilogue uses TMA stores (needs N % 8 == 0)
     uint32_t c_vec_ok;   // 1: 16-byte vector stores to C are aligned (N % 8 == 0)
+    // fused epilogue (kernels instantiated with EPI only): C = alpha * A*B^T + beta * c_in + bias
+    float alpha, beta;
+    const __half *bias;  // N values, one per column of C, or nullptr
+    const __half *c_in;  // M x N, row-major, read when beta != 0 (may be C itself), or nullptr
 #ifdef B200_TIMELINE
     unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
 #endif
@@ -164,10 +168,59 @@ __device__ __forceinline__ void store_row_chunk32(__half *c, uint32_t row, uint3
     }
 }
 
+// Fused epilogue on COUNT accumulator columns of one row, in place (FP32 bit patterns):
+// v = alpha * v + bias[col] + beta * c_in[row][col]. Out-of-range rows and columns are left alone
+// (they are clipped when stored).
+template <int COUNT>
+__device__ __forceinline__ void fused_epilogue(const GemmParams &p, uint32_t row, uint32_t col0, uint32_t *vals) {
+    const bool row_ok = row < p.m;
+    const bool vec_ok = p.c_vec_ok != 0 && col0 + COUNT <= p.n;
+    const __half *bias = p.bias ? p.bias + col0 : nullptr;
+    const __half *cin = (p.beta != 0.f && p.c_in && row_ok) ? p.c_in + static_cast<size_t>(row) * p.n + col0 : nullptr;
+#pragma unroll
+    for (int j = 0; j < COUNT; j += 8) {
+        float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (vec_ok) {
+            if (bias) {
+                const uint4 b = *reinterpret_cast<const uint4 *>(bias + j);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&b);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h[e]);
+                    add[2 * e] += f.x;
+                    add[2 * e + 1] += f.y;
+                }
+            }
+            if (cin) {
+                const uint4 c = *reinterpret_cast<const uint4 *>(cin + j);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&c);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h[e]);
+                    add[2 * e] += p.beta * f.x;
+                    add[2 * e + 1] += p.beta * f.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (col0 + j + e < p.n) {
+                    if (bias) add[e] += __half2float(bias[j + e]);
+                    if (cin) add[e] += p.beta * __half2float(cin[j + e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vals[j + e] = __float_as_uint(fmaf(p.alpha, __uint_as_float(vals[j + e]), add[e]));
+    }
+}
+
 // KPS = k-blocks per stage. With KPS = 2, GemmParams::k_blocks and every k index of the work
 // decomposition count pairs of k-blocks (one stage each); a pair that reaches past K reads zeros there.
-template <int BN, int STAGES, int CG, int MODE, int KPS = 1>
+// EPI: apply GemmParams' alpha / beta / bias in the epilogue (whole tiles only).
+template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+    static_assert(!EPI || MODE == kModeTiles, "the fused epilogue is applied to whole tiles");
     using T = KernelTraits<BN, STAGES, CG, KPS>;
     static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
 
@@ -401,6 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         }
                         const bool live = warp_rows_live && (n0 + c * 64u) < p.n;
                         if (live) {
+                            if (EPI) fused_epilogue<64>(p, m0 + row_in_tile, n0 + c * 64u, cur);
                             uint8_t *buf = my_staging_ptr + (store_buf & 1u) * 4096u;
                             // the store issued two chunks ago read this buffer: wait until it has
                             if (lane == 0) tma_store_wait_read<1>();
@@ -432,6 +486,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         uint32_t r[32];
                         tmem_ld_32x32b_x32(taddr + c * 32u, r);
                         tmem_ld_wait();
+                        if (EPI) fused_epilogue<32>(p, m0 + row_in_tile, n0 + c * 32u, r);
                         store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
                     }
                 }

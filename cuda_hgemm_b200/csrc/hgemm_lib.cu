@@ -70,8 +70,8 @@ struct DeviceState {
     size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
     cudaStream_t host_stream[3] = {nullptr, nullptr, nullptr};  // upload, GEMMs, download
     cudaEvent_t host_event[2] = {nullptr, nullptr};
-    bool attr_set[16] = {};
-    int max_clusters[16] = {};  // CTA pairs the device can keep resident at once, per pair kernel
+    bool attr_set[32] = {};
+    int max_clusters[32] = {};  // CTA pairs the device can keep resident at once, per pair kernel
     TensorMapSlot tm_cache[64];
 };
 
@@ -494,10 +494,10 @@ static bool pdl_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, int CG, int MODE, int KPS = 1>
+template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false>
 static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
     using T = KernelTraits<BN, STAGES, CG, KPS>;
-    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE, KPS>;
+    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE, KPS, EPI>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -828,7 +828,7 @@ static int check_args(const void *A, const void *B, const void *C, size_t M, siz
 
 static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                     const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes,
-                    uint32_t *error_word_override = nullptr) {
+                    uint32_t *error_word_override = nullptr, const b200_hgemm_epilogue *epi = nullptr) {
     int rc = validate_plan(pl, N, K);
     if (rc != B200_HGEMM_OK) return rc;
     if (pl.variant == B200_VARIANT_SIMT) return run_simt(A, B, C, M, N, K, stream);
@@ -886,6 +886,17 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
     p.tma_store = pl.tma_store ? 1u : 0u;
     p.c_vec_ok = (N % 8 == 0) ? 1u : 0u;
+    if (epi) {
+        // whole-tile kernels only; c_vec_ok also covers the 16-byte loads of bias and c_in
+        if (pl.variant != B200_VARIANT_CTA1 && !(pl.variant == B200_VARIANT_CTA2 && !big)) return B200_HGEMM_ERR_UNSUPPORTED;
+        if (bn == 192) return B200_HGEMM_ERR_UNSUPPORTED;
+        p.alpha = epi->alpha;
+        p.beta = epi->beta;
+        p.bias = static_cast<const __half *>(epi->bias);
+        p.c_in = static_cast<const __half *>(epi->c_in);
+        if (p.beta != 0.f && !p.c_in) return B200_HGEMM_ERR_INVALID_ARG;
+        if ((reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.c_in)) & 15u) return B200_HGEMM_ERR_MISALIGNED;
+    }
 #ifdef B200_TIMELINE
     p.timeline = g_timeline;
 #endif
@@ -926,6 +937,15 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         grid = workers * cg;
     }
 
+    if (epi) {
+        if (pl.variant == B200_VARIANT_CTA1) {
+            if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles, 1, true>(st, 16, p, grid, stream);
+            if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2, true>(st, 17, p, grid, stream);
+            return launch_kernel<64, 4, 1, kModeTiles, 2, true>(st, 18, p, grid, stream);
+        }
+        if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles, 1, true>(st, 19, p, grid, stream);
+        return launch_kernel<128, 4, 2, kModeTiles, 2, true>(st, 20, p, grid, stream);
+    }
     if (pl.variant == B200_VARIANT_CTA1) {
         if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles>(st, 0, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 4, 1, kModeTiles>(st, 9, p, grid, stream);
@@ -1192,6 +1212,54 @@ int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, siz
                   b200_stream_t stream) {
     if (!plan) return B200_HGEMM_ERR_INVALID_ARG;
     return entry(A, B, C, M, N, K, plan, -1, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// The plan among the whole-tile kernels (the ones that carry the fused epilogue) closest to what
+// the dispatch would run for this shape.
+static int fused_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
+    select_plan(st, M, N, K, pl);
+    const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
+    switch (pl->variant) {
+        case B200_VARIANT_SIMT:
+            return B200_HGEMM_ERR_UNSUPPORTED;  // K % 8 != 0
+        case B200_VARIANT_CTA1:
+            if (pl->bn == 192) pl->bn = 256;
+            break;
+        case B200_VARIANT_CTA2:
+            if (pl->bn != 128) pl->bn = 256;
+            break;
+        case B200_VARIANT_CTA2_MCAST:
+            pl->variant = B200_VARIANT_CTA2;
+            pl->bn = 256;
+            break;
+        case B200_VARIANT_SKINNY:
+            pl->variant = B200_VARIANT_CTA1;
+            pl->bn = ceil_div_u32(N, 128) * 2 >= sms ? 128 : 64;
+            break;
+        default:  // k-ranges: the same tiles, walked whole
+            pl->variant = B200_VARIANT_CTA1;
+            break;
+    }
+    pl->parts = 0;
+    pl->grid = 0;
+    pl->group_m = 0;
+    pl->tma_store = (N % 8 == 0) ? 1 : 0;
+    return B200_HGEMM_OK;
+}
+
+int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_epilogue *epilogue,
+                     b200_stream_t stream) {
+    if (!epilogue) return B200_HGEMM_ERR_INVALID_ARG;
+    int rc = check_args(A, B, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    b200_hgemm_plan pl;
+    rc = fused_plan(*st, M, N, K, &pl);
+    if (rc != B200_HGEMM_OK) return rc;
+    return run_plan(*st, A, B, C, M, N, K, pl, reinterpret_cast<cudaStream_t>(stream), nullptr, 0, nullptr, epilogue);
 }
 
 int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {

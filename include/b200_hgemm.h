@@ -111,6 +111,20 @@ int b200_hgemm_simt(const void *A, const void *B, void *C, size_t M, size_t N, s
 int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_plan *plan,
                   b200_stream_t stream);
 
+/* GEMM with a fused epilogue: C = alpha * (A * B^T) + beta * c_in + bias, everything after the product in
+ * FP32 on the accumulator before the one rounding to FP16. The reference fixes alpha = 1, beta = 0
+ * (src/cublas_tensor_op.cu:19-20) and has no counterpart; this is the step either side of a GEMM in
+ * decode/prefill use. Runs on the whole-tile kernels (single CTAs or pairs, the dispatch's choice mapped
+ * onto them); needs K % 8 == 0. */
+typedef struct b200_hgemm_epilogue {
+    float alpha;
+    float beta;
+    const void *bias; /* N halves, one per column of C, 16-byte aligned; or NULL */
+    const void *c_in; /* M x N halves, row-major, 16-byte aligned, read when beta != 0; may be C itself; or NULL */
+} b200_hgemm_epilogue;
+int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+                     const b200_hgemm_epilogue *epilogue, b200_stream_t stream);
+
 /* HOST-pointer GEMM: copies A and B to the device, runs b200_hgemm, copies C back and
  * synchronises. This is the path of reference Matrix (src/common/matrix.h:23-35 upload,
  * :83-85 moveToHost) + one kernel call, behind one entry point. Returns after C_host is complete. */

@@ -462,6 +462,80 @@ def test_single_process_group_rejects_bad_device_lists(cuda_device):
         assert lib.b200_mg_create(arr, len(devices), ctypes.byref(handle)) == _native.ERR_INVALID_ARG
 
 
+FUSED_CASES = [
+    # M, N, K, alpha, beta, bias?, in place?
+    (256, 256, 256, 0.5, 0.0, False, False),     # alpha only
+    (384, 512, 320, 1.0, 0.0, True, False),      # bias only
+    (200, 264, 136, -1.25, 0.75, True, False),   # everything, tails in M, N, K
+    (200, 1001, 136, 2.0, -0.5, True, False),    # N not a multiple of 8: guarded loads and stores
+    (1024, 1536, 512, 1.0, 1.0, False, True),    # C += A * B^T in place
+    (2304, 2304, 256, 0.25, 2.0, True, True),    # pairs (the dispatch's 256 x 192 mapped to 256 x 256)
+    (16, 1024, 2048, 1.5, 0.5, True, False),     # a decode batch: mapped from the short-A kernel to 128-row tiles
+    (96, 4096, 1024, 1.0, 0.5, True, True),      # mapped from k-ranges to whole tiles
+    (4096, 4096, 1536, 1.0, 0.5, True, False),   # many waves of pairs
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-a{c[3]}-b{c[4]}")
+def test_fused_epilogue(cuda_device, case):
+    """C = alpha * A B^T + beta * c_in + bias in one kernel, against the same expression on the oracle's product."""
+    import torch
+
+    M, N, K, alpha, beta, with_bias, in_place = case
+    A, B = make_inputs(M, N, K, seed=61)
+    rng = np.random.default_rng(62)
+    c_in = rng.uniform(-4, 4, size=(M, N)).astype(np.float16)
+    bias = rng.uniform(-2, 2, size=(N,)).astype(np.float16)
+    ref = alpha * oracle.gemm_f32(A, B)
+    if beta != 0.0:
+        ref = ref + np.float32(beta) * c_in.astype(np.float32)
+    if with_bias:
+        ref = ref + bias.astype(np.float32)[None, :]
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    d_bias = to_dev(bias, cuda_device) if with_bias else None
+    if in_place:
+        C = to_dev(c_in, cuda_device).clone()
+        api.hgemm_fused(dA, dB, C, alpha, beta, d_bias, C)
+    else:
+        C = poisoned(M, N, cuda_device).view(M, N)
+        api.hgemm_fused(dA, dB, C, alpha, beta, d_bias, to_dev(c_in, cuda_device) if beta != 0.0 else None)
+    torch.cuda.synchronize(cuda_device)
+    assert api.last_device_error() == 0
+    assert_close_to_oracle(C.cpu().numpy(), ref.astype(np.float32), f"fused {case}")
+
+
+def test_fused_epilogue_with_identity_matches_the_plain_product(cuda_device):
+    A, B = make_inputs(512, 768, 448, seed=63)
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    C = poisoned(512, 768, cuda_device).view(512, 768)
+    api.hgemm_fused(dA, dB, C, 1.0, 0.0)
+    plain = run(api.b200HgemmCta1, A, B, cuda_device)
+    assert np.array_equal(C.cpu().numpy().view(np.uint16), plain.view(np.uint16))
+
+
+def test_fused_epilogue_error_codes(cuda_device):
+    import ctypes
+
+    import torch
+
+    A, B = make_inputs(128, 128, 128, seed=64)
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    C = torch.empty((128, 128), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_native.HgemmError) as e:
+        api.hgemm_fused(dA, dB, C, 1.0, 0.5)  # beta without c_in
+    assert e.value.status == _native.ERR_INVALID_ARG
+    lib = _native.load()
+    assert lib.b200_hgemm_fused(dA.data_ptr(), dB.data_ptr(), C.data_ptr(), 128, 128, 128, None, None) == _native.ERR_INVALID_ARG
+    A2, B2 = make_inputs(64, 64, 100, seed=65)  # K % 8 != 0: no tensor-core kernel, so no fused epilogue
+    C2 = torch.empty((64, 64), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_native.HgemmError) as e:
+        api.hgemm_fused(to_dev(A2, cuda_device), to_dev(B2, cuda_device), C2, 2.0, 0.0)
+    assert e.value.status == _native.ERR_UNSUPPORTED
+    epi = _native.Epilogue(1.0, 0.0, dA.data_ptr() + 2, None)  # bias not 16-byte aligned
+    assert lib.b200_hgemm_fused(dA.data_ptr(), dB.data_ptr(), C.data_ptr(), 128, 128, 128, ctypes.byref(epi), None) == _native.ERR_MISALIGNED
+    torch.cuda.synchronize(cuda_device)
+
+
 def test_error_codes_on_device(cuda_device):
     import torch
 
