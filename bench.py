@@ -162,6 +162,7 @@ NCU_TRAFFIC_BYTES = {
     ("square16384", _native.VARIANT_CTA2_MCAST, 512): 9.43e9,
     ("square16384", _native.VARIANT_CTA2, 512): 8.46e9,
     ("square16384", _native.VARIANT_CTA2, 256): 16.5e9,
+    ("square8192", _native.VARIANT_CTA2_MCAST, 512): 0.936e9,  # profiles/hgemm_tcgen05_mc512_square8192.md
     ("square8192", _native.VARIANT_CTA2, 256): 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
     ("skinny16", _native.VARIANT_SKINNY, 16): 121.7e6,    # profiles/hgemm_skinny_skinny16.md
     ("skinny16", _native.VARIANT_CTA1, 128): 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
