@@ -319,13 +319,25 @@ def run_ours(args):
     hC = torch.empty((rows, N), dtype=torch.float16).pin_memory()
     hA.copy_(A)
     hB.copy_(B)
-    if rows:
-        api.hgemm_host(hA, hB, hC)  # warm-up: staging buffers and streams are created here
+    # Several ranks: every rank uploads its rows of A and 1/world of B, the shares of B are exchanged between
+    # the GPUs (NCCL all-gather over NVLink), then the slab is multiplied and comes back: the host link of a GPU
+    # carries (M*K + N*K) / world halves up and M*N / world down instead of all of B.
+    from cuda_hgemm_b200 import multi_gpu
+
+    sharded_b = world > 1 and N % world == 0
+    dB_e2e = torch.empty((N, K), dtype=torch.float16, device=device) if sharded_b else None
+
+    def e2e_once():
+        if sharded_b:
+            multi_gpu.slab_hgemm_host(hA, hB, hC, dB_e2e)
+        elif rows:
+            api.hgemm_host(hA, hB, hC)
+
+    e2e_once()  # warm-up: staging buffers, streams and the communicator's buffers are created here
     barrier(torch, world)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        if rows:
-            api.hgemm_host(hA, hB, hC)
+        e2e_once()
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(torch, (time.perf_counter() - t0) / e2e_steps, world, device)
     barrier(torch, world)
@@ -377,9 +389,13 @@ def run_ours(args):
         "pct_fp16_dense_peak": round(100.0 * value / (NOMINAL_FP16_DENSE_TFLOPS * world), 2),
         "clocks": clocks,
         "e2e": {"value": round(flops_job / e2e_s / 1e12, 2), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": int((rows * K + N * K) * 2), "d2h_bytes_per_step": int(rows * N * 2),
+                "h2d_bytes_per_step": int((rows * K + (N // world if sharded_b else N) * K) * 2),
+                "d2h_bytes_per_step": int(rows * N * 2),
+                "nvlink_bytes_per_step": int((N - N // world) * K * 2) if sharded_b else 0,
                 "steps": e2e_steps, "matches_device_result": e2e_ok,
-                "api": "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
+                "api": ("multi_gpu.slab_hgemm_host (per rank: pinned host buffers -> H2D of A's rows and 1/N of B -> "
+                        "NCCL all-gather of B -> b200_hgemm_host_a -> D2H)") if sharded_b else
+                       "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
         "roofline": roofline(args.workload, plan, rows, N, K, ms_per_step, peaks),
     }
 

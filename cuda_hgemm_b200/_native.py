@@ -19,7 +19,7 @@ EXPORTED_SYMBOLS = (
     "b200_hgemm_set_workspace", "b200_hgemm_last_device_error", "b200_hgemm_status_string",
     "b200_hgemm_version", "b200_hgemm_launch_count", "b200_sched_tile_coord", "b200_sched_segments",
     "b200_sched_contributors", "b200_sched_partial_slot", "b200_debug_idesc", "b200_debug_smem_desc",
-    "b200_debug_wait_expiry", "b200_hgemm_fused", "b200_hgemm_load_plan_table", "b200_hgemm_select_untuned", "b200_partition_slab", "b200_mg_create", "b200_mg_destroy", "b200_mg_device_count",
+    "b200_debug_wait_expiry", "b200_hgemm_fused", "b200_hgemm_host_a", "b200_hgemm_load_plan_table", "b200_hgemm_select_untuned", "b200_partition_slab", "b200_mg_create", "b200_mg_destroy", "b200_mg_device_count",
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
 )
 
@@ -87,6 +87,8 @@ def load() -> ctypes.CDLL:
     lib.b200_hgemm_fused.restype = c_int
     lib.b200_hgemm_host.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]
     lib.b200_hgemm_host.restype = c_int
+    lib.b200_hgemm_host_a.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]
+    lib.b200_hgemm_host_a.restype = c_int
     lib.b200_hgemm_select.argtypes = [c_size_t, c_size_t, c_size_t, POINTER(Plan)]
     lib.b200_hgemm_select.restype = c_int
     lib.b200_hgemm_select_untuned.argtypes = [c_size_t, c_size_t, c_size_t, POINTER(Plan)]

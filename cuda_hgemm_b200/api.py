@@ -142,6 +142,26 @@ def hgemm_host(A_host, B_host, C_host):
     return C_host
 
 
+def hgemm_host_a(A_host, B_dev, C_host):
+    """HOST ``A`` in, HOST ``C`` out, ``B`` already on the GPU (C ABI ``b200_hgemm_host_a``); the current stream's
+    work on ``B_dev`` must be complete (this call synchronises that stream first)."""
+    import torch
+
+    for name, t in (("A", A_host), ("C", C_host)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.float16 or t.is_cuda or not t.is_contiguous():
+            raise TypeError(f"{name} must be a contiguous float16 CPU tensor")
+    if not B_dev.is_cuda or B_dev.dtype != torch.float16 or not B_dev.is_contiguous():
+        raise TypeError("B must be a contiguous float16 CUDA tensor")
+    M, K = A_host.shape
+    N, Kb = B_dev.shape
+    if Kb != K or tuple(C_host.shape) != (M, N):
+        raise ValueError("shape mismatch")
+    with torch.cuda.device(B_dev.device):
+        torch.cuda.current_stream().synchronize()
+        check(_native.load().b200_hgemm_host_a(A_host.data_ptr(), B_dev.data_ptr(), C_host.data_ptr(), int(M), int(N), int(K)))
+    return C_host
+
+
 def select_plan(M: int, N: int, K: int) -> Plan:
     """The plan ``b200Hgemm`` would run for this shape on the current device (C ABI ``b200_hgemm_select``)."""
     plan = Plan()

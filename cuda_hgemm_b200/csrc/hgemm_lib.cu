@@ -1393,8 +1393,10 @@ static int grow(void **ptr, size_t *have, size_t need) {
     return B200_HGEMM_OK;
 }
 
-int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t M, size_t N, size_t K) {
-    int rc = check_args(A_host, B_host, C_host, M, N, K);
+// A and C on the host; B on the host (b_on_device = false: uploaded first) or already on the device.
+static int host_pipeline(const void *A_host, const void *B_any, void *C_host, size_t M, size_t N, size_t K, bool b_on_device) {
+    const void *B_host = B_any;
+    int rc = check_args(A_host, B_any, C_host, M, N, K);
     if (rc != B200_HGEMM_OK) return rc;
     DeviceState *st = nullptr;
     rc = current_state(&st);
@@ -1409,7 +1411,7 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     {
         std::lock_guard<std::mutex> lock(st->mu);
         if ((rc = grow(&st->host_a, &st->host_a_bytes, a_bytes)) != B200_HGEMM_OK) return rc;
-        if ((rc = grow(&st->host_b, &st->host_b_bytes, b_bytes)) != B200_HGEMM_OK) return rc;
+        if (!b_on_device && (rc = grow(&st->host_b, &st->host_b_bytes, b_bytes)) != B200_HGEMM_OK) return rc;
         if ((rc = grow(&st->host_c, &st->host_c_bytes, c_bytes)) != B200_HGEMM_OK) return rc;
         for (int i = 0; i < 3; ++i) {
             if (!st->host_stream[i] && cudaStreamCreateWithFlags(&st->host_stream[i], cudaStreamNonBlocking) != cudaSuccess)
@@ -1427,7 +1429,11 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     // GEMM and the download of the last slab: slabs of about 1024 rows keep that under a millisecond
     // at N = K = 16384.
     cudaStream_t s_up = st->host_stream[0], s_run = st->host_stream[1], s_down = st->host_stream[2];
-    if (!cuda_ok(cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
+    const void *b_dev = B_any;
+    if (!b_on_device) {
+        if (!cuda_ok(cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
+        b_dev = st->host_b;
+    }
     size_t slabs = 1;
     if (M >= 2048 && M % 128 == 0) {
         slabs = M >= 16384 ? 16 : M >= 8192 ? 8 : 4;
@@ -1449,7 +1455,7 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
             return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaEventRecord(st->host_event[0], s_up), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaStreamWaitEvent(s_run, st->host_event[0], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
-        rc = entry(a_dst, st->host_b, c_dev, rows_here, N, K, nullptr, -1, s_run);
+        rc = entry(a_dst, b_dev, c_dev, rows_here, N, K, nullptr, -1, s_run);
         if (rc != B200_HGEMM_OK) return rc;
         if (!cuda_ok(cudaEventRecord(st->host_event[1], s_run), "cudaEventRecord")) return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaStreamWaitEvent(s_down, st->host_event[1], 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
@@ -1461,6 +1467,15 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
     if (!cuda_ok(cudaStreamSynchronize(s_run), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     if (!cuda_ok(cudaStreamSynchronize(s_up), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     return B200_HGEMM_OK;
+}
+
+int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t M, size_t N, size_t K) {
+    return host_pipeline(A_host, B_host, C_host, M, N, K, false);
+}
+
+int b200_hgemm_host_a(const void *A_host, const void *B_device, void *C_host, size_t M, size_t N, size_t K) {
+    if (reinterpret_cast<uintptr_t>(B_device) & 15u) return B200_HGEMM_ERR_MISALIGNED;
+    return host_pipeline(A_host, B_device, C_host, M, N, K, true);
 }
 
 // ---- several GPUs from one process ----------------------------------------------------------

@@ -121,3 +121,48 @@ class SingleProcessGroup:
         ms = self._ct.c_float()
         self._native.check(self._native.load().b200_mg_elapsed_ms_max(self._handle, self._ct.byref(ms)))
         return float(ms.value)
+
+
+def share_of_b(N: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Rows ``[begin, end)`` of B (columns of C) that ``rank`` brings to the exchange: equal shares."""
+    if N % world_size != 0:
+        raise ValueError("B is exchanged in equal shares: N must be a multiple of the number of ranks")
+    share = N // world_size
+    return rank * share, (rank + 1) * share
+
+
+def exchange_b(B_full, rank: int, world_size: int, group=None):
+    """All-gather B in place: on entry rank r's rows ``share_of_b(N, r, world)`` of ``B_full`` are valid,
+    on return all of it is, on every rank. The one exchange step of the partitioned multiply when B
+    starts on the hosts: every GPU pulls 1/world of B over its own host link and the rest over
+    NVLink/NVSwitch (NCCL), instead of all of B over the host link."""
+    import torch.distributed as dist
+
+    lo, hi = share_of_b(B_full.shape[0], rank, world_size)
+    dist.all_gather_into_tensor(B_full, B_full[lo:hi], group=group)
+    return B_full
+
+
+def slab_hgemm_host(A_host_slab, B_host, C_host_slab, B_dev, group=None):
+    """This rank's slab from HOST memory: ``C_host_slab = A_host_slab * B_host^T``.
+
+    ``B_host`` is the whole of B in this rank's (pinned) host memory, ``B_dev`` a device buffer of
+    the same shape that the call fills: the rank's own share from the host, the other shares from
+    the other ranks. With one rank this is ``api.hgemm_host``.
+    """
+    import torch
+    import torch.distributed as dist
+
+    from . import api
+
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if world == 1 or B_host.shape[0] % world != 0:
+        return api.hgemm_host(A_host_slab, B_host, C_host_slab)
+    rank = dist.get_rank(group)
+    lo, hi = share_of_b(B_host.shape[0], rank, world)
+    B_dev[lo:hi].copy_(B_host[lo:hi], non_blocking=True)
+    exchange_b(B_dev, rank, world, group)
+    if A_host_slab.shape[0] == 0:
+        torch.cuda.current_stream().synchronize()
+        return C_host_slab
+    return api.hgemm_host_a(A_host_slab, B_dev, C_host_slab)

@@ -130,6 +130,12 @@ int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, 
  * :83-85 moveToHost) + one kernel call, behind one entry point. Returns after C_host is complete. */
 int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t M, size_t N, size_t K);
 
+/* The same with B already on the current device (complete, 16-byte aligned): only A goes up and C comes down.
+ * For weights that stay resident, and for several GPUs, where each one uploads a share of B and the shares are
+ * exchanged between the GPUs instead of every GPU pulling all of B over its own host link. Work queued on other
+ * streams that produces B must have completed (or the caller must have synchronised) before the call. */
+int b200_hgemm_host_a(const void *A_host, const void *B_device, void *C_host, size_t M, size_t N, size_t K);
+
 /* ---- planning, workspace, status ------------------------------------------------------- */
 
 /* Fills *plan with the library's choice for (M, N, K) on the current device. */

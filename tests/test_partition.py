@@ -80,3 +80,40 @@ def test_allgather_of_slabs_rebuilds_c_on_every_rank(tmp_path, M):
     mp.spawn(_worker, args=(world, _free_port(), M, 96, 64, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
+def _exchange_worker(rank, world, port, N, K, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cuda_hgemm_b200 import multi_gpu
+        from tests.helpers import make_inputs
+
+        _, B = make_inputs(8, N, K, seed=78)  # the whole of B, as every rank's host memory holds it
+        lo, hi = multi_gpu.share_of_b(N, rank, world)
+        device_copy = torch.full((N, K), float("nan"), dtype=torch.float16)  # stand-in for the device buffer
+        device_copy[lo:hi] = torch.from_numpy(B[lo:hi])                      # the share this rank uploads
+        multi_gpu.exchange_b(device_copy, rank, world)
+        ok = np.array_equal(device_copy.numpy().view(np.uint16), B.view(np.uint16))
+        with open(os.path.join(result_dir, f"exchange{rank}.txt"), "w") as f:
+            f.write("ok" if ok else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_of_b_shares_rebuilds_b_on_every_rank(tmp_path):
+    """Each rank holds 1/world of B on its device; the in-place all-gather completes every copy."""
+    world = 2
+    mp.spawn(_exchange_worker, args=(world, _free_port(), 192, 64, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"exchange{r}.txt").read_text() == "ok"
+
+
+def test_shares_of_b_are_equal_and_complete():
+    from cuda_hgemm_b200 import multi_gpu
+
+    assert [multi_gpu.share_of_b(16384, r, 8) for r in range(8)] == [(r * 2048, (r + 1) * 2048) for r in range(8)]
+    with pytest.raises(ValueError):
+        multi_gpu.share_of_b(1000, 0, 3)
+
