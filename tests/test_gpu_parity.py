@@ -404,6 +404,22 @@ def test_host_pointer_entry_point(cuda_device):
         assert_close_to_oracle(hC.numpy(), oracle.gemm_f32(A, B), f"host {M}x{N}x{K}")
 
 
+def test_host_entry_point_with_b_resident_on_the_device(cuda_device):
+    """b200_hgemm_host_a: A up and C down in slabs, B already on the GPU; same bits as the all-host entry point."""
+    import torch
+
+    for M, N, K in ((256, 256, 256), (4096, 512, 256), (2048 + 512, 264, 136), (300, 264, 136)):
+        A, B = make_inputs(M, N, K, seed=13)
+        hA = torch.from_numpy(A).pin_memory()
+        hC = torch.full((M, N), float("nan"), dtype=torch.float16).pin_memory()
+        hC2 = torch.full((M, N), float("nan"), dtype=torch.float16).pin_memory()
+        dB = to_dev(B, cuda_device)
+        api.hgemm_host_a(hA, dB, hC)
+        assert_close_to_oracle(hC.numpy(), oracle.gemm_f32(A, B), f"host A, resident B {M}x{N}x{K}")
+        api.hgemm_host(hA, torch.from_numpy(B).pin_memory(), hC2)
+        assert np.array_equal(hC.numpy().view(np.uint16), hC2.numpy().view(np.uint16))
+
+
 def _single_process_group_case(devices, M, N, K):
     import torch
 
