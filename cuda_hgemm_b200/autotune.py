@@ -94,6 +94,19 @@ def tune_shape(torch, M, N, K, rounds, steps, margin, sustained, device):
         "tflops": {"/".join(map(str, key)): round(gflop / ms, 1) for key, ms in sorted(med.items(), key=lambda kv: kv[1])}}
 
 
+def _options_without_paths(args):
+    """The command line as recorded in the table's header: everything but where the files went."""
+    out, skip = [], False
+    for a in args:
+        if skip:
+            skip = False
+        elif a in ("--out", "--log"):
+            skip = True
+        elif not a.startswith(("--out=", "--log=")):
+            out.append(a)
+    return out
+
+
 def main(argv=None) -> int:
     import torch
 
@@ -129,7 +142,7 @@ def main(argv=None) -> int:
     protocol = "sustained (pre-heated, under the power cap)" if args.sustained else "burst (idle pause, 3 warm-up, %d launches)" % args.steps
     header = ["# Plans measured faster than the dispatch rules' own choice by more than %.0f %% (median of %d rounds, %s)." %
               (100 * args.margin, args.rounds, protocol),
-              "# Written by: python -m cuda_hgemm_b200.autotune " + " ".join(sys.argv[1:] if argv is None else argv),
+              "# Written by: python -m cuda_hgemm_b200.autotune " + " ".join(_options_without_paths(sys.argv[1:] if argv is None else argv)),
               "# M N K variant bn parts group_m tma_store"]
     with open(args.out, "w") as f:
         f.write("\n".join(header + lines) + "\n")
