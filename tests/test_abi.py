@@ -139,3 +139,43 @@ def test_tuned_plan_table_overrides_the_rules(native_lib, tmp_path):
         assert api.load_plan_table(None) == 0
     assert api.select_plan(2304, 2304, 2304).bn == api.select_plan_untuned(2304, 2304, 2304).bn
 
+
+
+def test_every_plan_the_rules_pick_is_one_the_kernels_can_serve(native_lib):
+    """Seeded shapes over six orders of magnitude: the plan's fields stay inside what run_plan accepts."""
+    import numpy as np
+
+    from cuda_hgemm_b200 import api
+
+    rng = np.random.default_rng(99)
+    V = _native
+    seen = set()
+    for _ in range(3000):
+        M, N, K = (int(2 ** rng.uniform(0, 15)) for _ in range(3))
+        if rng.random() < 0.5:
+            K = max(8, K // 8 * 8)
+        if rng.random() < 0.5:
+            N = max(8, N // 8 * 8)
+        p = api.select_plan_untuned(M, N, K)
+        seen.add((p.variant, p.bn))
+        what = f"{(M, N, K)} -> {p.as_dict()}"
+        if K % 8 != 0:
+            assert p.variant == V.VARIANT_SIMT, what
+            continue
+        assert p.variant in (V.VARIANT_CTA1, V.VARIANT_CTA2, V.VARIANT_STREAMK, V.VARIANT_CTA2_MCAST, V.VARIANT_SKINNY), what
+        assert p.parts == 0 and p.grid == 0 and p.group_m == 0, what
+        if p.variant == V.VARIANT_SKINNY:
+            assert M <= 64 and p.bn in (16, 32, 64) and M <= p.bn and (p.bn == 16 or M > p.bn // 2), what
+            continue
+        assert M > 64, what
+        assert p.tma_store == (1 if N % 8 == 0 else 0), what
+        if p.variant == V.VARIANT_CTA1:
+            assert p.bn in (64, 128, 256), what
+        elif p.variant == V.VARIANT_STREAMK:
+            assert p.bn in (64, 128, 256) and -(-K // 64) >= 8, what
+        elif p.variant == V.VARIANT_CTA2:
+            assert p.bn in (192, 256, 512) and M > 128, what
+        if p.bn == 512:  # 256 x 256 outputs per CTA: TMA stores only, long k, long runs
+            assert N % 8 == 0 and -(-K // 64) >= 24 and 2.0 * M * N * K >= 2.0 * 4096 ** 3, what
+    # the draw reaches every family
+    assert {V.VARIANT_SIMT, V.VARIANT_CTA1, V.VARIANT_CTA2, V.VARIANT_STREAMK, V.VARIANT_SKINNY} <= {v for v, _ in seen}
