@@ -179,3 +179,28 @@ def test_every_plan_the_rules_pick_is_one_the_kernels_can_serve(native_lib):
             assert N % 8 == 0 and -(-K // 64) >= 24 and 2.0 * M * N * K >= 2.0 * 4096 ** 3, what
     # the draw reaches every family
     assert {V.VARIANT_SIMT, V.VARIANT_CTA1, V.VARIANT_CTA2, V.VARIANT_STREAMK, V.VARIANT_SKINNY} <= {v for v, _ in seen}
+
+
+def test_workspace_sizes_callers_can_rely_on(native_lib):
+    """b200_hgemm_workspace_bytes for the kernels that cut k (a caller sizing its own workspace uses these)."""
+    from cuda_hgemm_b200 import api
+
+    def plan(variant, bn, parts=0):
+        p = _native.Plan()
+        p.variant, p.bn, p.parts, p.tma_store = variant, bn, parts, 1
+        return p
+
+    header = 64 * 1024
+    # stream-k: two FP32 partial-tile slots of 128 x bn per k-range, one k-range per SM of a 148-SM part by default
+    assert api.workspace_bytes(96, 4096, 14336, plan(_native.VARIANT_STREAMK, 128)) == header + 148 * 2 * 128 * 128 * 4
+    assert api.workspace_bytes(96, 4096, 14336, plan(_native.VARIANT_STREAMK, 256, parts=40)) == header + 40 * 2 * 128 * 256 * 4
+    # never more k-ranges than (tile, stage) units: 2 tiles x 2 stages of two k-blocks each
+    assert api.workspace_bytes(128, 256, 256, plan(_native.VARIANT_STREAMK, 128)) == header + 4 * 2 * 128 * 128 * 4
+    assert api.workspace_bytes(128, 256, 256, plan(_native.VARIANT_HYBRID, 128)) == header + 4 * 2 * 128 * 128 * 4
+    # short A: slices x tile height x padded N floats when k is cut (32 column tiles -> 4 slices), nothing otherwise
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY, 64)) == 4 * 64 * 4096 * 4
+    assert api.workspace_bytes(48, 4100, 14336, plan(_native.VARIANT_SKINNY, 64, parts=3)) == 3 * 64 * 4128 * 4
+    assert api.workspace_bytes(16, 14336, 4096, plan(_native.VARIANT_SKINNY, 16)) == 0
+    # whole-tile kernels need none
+    for variant, bn in ((_native.VARIANT_CTA1, 256), (_native.VARIANT_CTA2, 512), (_native.VARIANT_CTA2_MCAST, 512)):
+        assert api.workspace_bytes(8192, 8192, 8192, plan(variant, bn)) == 0
