@@ -204,3 +204,30 @@ def test_workspace_sizes_callers_can_rely_on(native_lib):
     # whole-tile kernels need none
     for variant, bn in ((_native.VARIANT_CTA1, 256), (_native.VARIANT_CTA2, 512), (_native.VARIANT_CTA2_MCAST, 512)):
         assert api.workspace_bytes(8192, 8192, 8192, plan(variant, bn)) == 0
+
+
+def test_short_a_k_slices_are_never_empty(native_lib):
+    """The short-A kernel gives every CTA one k-range; the launcher must never hand out an empty one.
+    The slice count is read back from the workspace size (slices x tile height x padded N floats)."""
+    import numpy as np
+
+    from cuda_hgemm_b200 import api
+
+    rng = np.random.default_rng(7)
+    for _ in range(2000):
+        N = int(rng.integers(1, 20000))
+        K = int(rng.integers(1, 4000)) * 8
+        bn = int(rng.choice([16, 32, 64]))
+        parts = int(rng.choice([0, 0, 1, 2, 3, 5, 8, 37, 300]))
+        p = _native.Plan()
+        p.variant, p.bn, p.parts = _native.VARIANT_SKINNY, bn, parts
+        n_pad = (N + 31) // 32 * 32
+        ws = api.workspace_bytes(8, N, K, p)
+        assert ws % (bn * n_pad * 4) == 0
+        slices = ws // (bn * n_pad * 4) or 1
+        k_blocks = -(-K // 64)
+        per = -(-k_blocks // slices)
+        assert 1 <= slices <= k_blocks, (N, K, bn, parts, slices)
+        assert (slices - 1) * per < k_blocks, f"slice {slices - 1} of {slices} would be empty: {(N, K, bn, parts)}"
+        if parts == 0 and slices > 1:
+            assert per >= 8 and slices * -(-N // 128) <= 148, (N, K, slices)
