@@ -94,3 +94,34 @@ def test_stream_k_ranges_cover_every_unit_once(native_lib, tiles, k_blocks, part
             slot = native_lib.b200_sched_partial_slot(part, parts, tiles, k_blocks, tile)
             assert slot // 2 == part and slot not in used
             used.add(slot)
+
+
+@pytest.mark.parametrize("tiles,k_blocks,workers", [
+    (162, 36, 148),   # 2304^3 with 128 x 256 tiles: one full wave whole, 14 tiles cut
+    (324, 4, 148),    # two whole tiles per worker, 28 cut tiles of 4 stages: fewer units than workers
+    (450, 4, 148),    # 6 cut tiles, 24 units for 148 workers
+    (40, 18, 7), (18, 18, 33), (100, 5, 10), (7, 1, 3), (1, 9, 4),
+])
+def test_whole_tiles_then_k_ranges_cover_every_unit_once(native_lib, tiles, k_blocks, workers):
+    """The HYBRID plan's walk, restated on the host with the library's own range arithmetic: worker w takes
+    tiles w, w + W, ... below dp_tiles whole, then (if it is one of the first sk_parts workers) its k-range of
+    the remaining tiles. Every (tile, k-block) must come up exactly once, and no k-range may be empty."""
+    dp_tiles = (tiles // workers) * workers
+    cut_tiles = tiles - dp_tiles
+    sk_parts = min(cut_tiles * k_blocks, workers)
+    seen = {}
+    buf = (ctypes.c_uint32 * (3 * 64))()
+    for w in range(workers):
+        for t in range(w, dp_tiles, workers):
+            for kb in range(k_blocks):
+                seen[(t, kb)] = seen.get((t, kb), 0) + 1
+        if w < sk_parts:
+            n = native_lib.b200_sched_segments(w, sk_parts, cut_tiles, k_blocks, buf, 64)
+            assert 1 <= n <= 64, "a worker that owns a k-range must get at least one segment"
+            for i in range(n):
+                tile, kb0, kb1 = buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]
+                assert kb0 < kb1 <= k_blocks and tile < cut_tiles
+                for kb in range(kb0, kb1):
+                    key = (dp_tiles + tile, kb)
+                    seen[key] = seen.get(key, 0) + 1
+    assert len(seen) == tiles * k_blocks and set(seen.values()) == {1}
