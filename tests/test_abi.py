@@ -231,3 +231,20 @@ def test_short_a_k_slices_are_never_empty(native_lib):
         assert (slices - 1) * per < k_blocks, f"slice {slices - 1} of {slices} would be empty: {(N, K, bn, parts)}"
         if parts == 0 and slices > 1:
             assert per >= 8 and slices * -(-N // 128) <= 148, (N, K, slices)
+
+
+def test_public_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 (and as C++) on its own."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = Path(__file__).resolve().parents[1]
+    src = tmp_path / "include_test.c"
+    src.write_text('#include "b200_hgemm.h"\n'
+                   "int main(void) { b200_hgemm_plan p; b200_hgemm_epilogue e; b200_mg *mg = 0; (void)p; (void)e; (void)mg; "
+                   "return b200_hgemm_status_string(0) != 0; }\n")
+    for args in (["-std=c99", "-pedantic"], ["-x", "c++", "-std=c++11"]):
+        subprocess.run([gcc, *args, "-Wall", "-Wextra", "-Werror", "-fsyntax-only", f"-I{root / 'include'}", str(src)], check=True)
