@@ -21,6 +21,8 @@ EXPORTED_SYMBOLS = (
     "b200_sched_contributors", "b200_sched_partial_slot", "b200_debug_idesc", "b200_debug_smem_desc",
     "b200_debug_wait_expiry", "b200_hgemm_fused", "b200_hgemm_host_a", "b200_hgemm_load_plan_table", "b200_hgemm_select_untuned", "b200_partition_slab", "b200_mg_create", "b200_mg_destroy", "b200_mg_device_count",
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
+    "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
+    "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
 )
 
 OK = 0
@@ -40,6 +42,8 @@ VARIANT_SIMT = 3
 VARIANT_CTA2_MCAST = 4
 VARIANT_SKINNY = 5
 VARIANT_HYBRID = 6
+
+MULTICAST_OFF, MULTICAST_ON, MULTICAST_LOCKED_OFF = 0, 1, 2
 
 
 class Plan(Structure):
@@ -101,6 +105,18 @@ def load() -> ctypes.CDLL:
     lib.b200_hgemm_set_workspace.restype = c_int
     lib.b200_hgemm_last_device_error.argtypes = []
     lib.b200_hgemm_last_device_error.restype = c_int
+    lib.b200_hgemm_streamk_static_last_error.argtypes = []
+    lib.b200_hgemm_streamk_static_last_error.restype = c_int
+    lib.b200_hgemm_synchronize.argtypes = [c_void_p]
+    lib.b200_hgemm_synchronize.restype = c_int
+    lib.b200_hgemm_release_workspaces.argtypes = []
+    lib.b200_hgemm_release_workspaces.restype = c_int
+    lib.b200_hgemm_enable_multicast.argtypes = [c_int]
+    lib.b200_hgemm_enable_multicast.restype = c_int
+    lib.b200_hgemm_multicast_state.argtypes = []
+    lib.b200_hgemm_multicast_state.restype = c_int
+    lib.b200_hgemm_plan_supported.argtypes = [c_size_t, c_size_t, c_size_t, POINTER(Plan)]
+    lib.b200_hgemm_plan_supported.restype = c_int
     lib.b200_hgemm_status_string.argtypes = [c_int]
     lib.b200_hgemm_status_string.restype = c_char_p
     lib.b200_hgemm_version.argtypes = []

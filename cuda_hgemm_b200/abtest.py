@@ -71,6 +71,9 @@ def main(argv=None) -> int:
         B = (torch.randn((N, K), generator=g, device=dev) / K ** 0.5).half()
     C = torch.empty((M, N), dtype=torch.float16, device=dev)
 
+    if any(text.startswith("mcast") for text in args.plans.split(",")) and not api.enable_multicast(True):
+        print("the multicast kernels are not available in this process", file=sys.stderr)
+        return 1
     candidates = {}
     cmp_lib = load_compare()
     if cmp_lib is not None:

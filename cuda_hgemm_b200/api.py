@@ -192,5 +192,23 @@ def last_device_error() -> int:
     return int(_native.load().b200_hgemm_last_device_error())
 
 
+def enable_multicast(on: bool = True) -> bool:
+    """Switch the single-GPU kernels with multicast operand loads on or off (C ABI
+    ``b200_hgemm_enable_multicast``). Returns whether they are on afterwards: never in a process that is
+    one rank of several or that holds a multi-device handle, and never without the companion library."""
+    lib = _native.load()
+    lib.b200_hgemm_enable_multicast(1 if on else 0)
+    return lib.b200_hgemm_multicast_state() == _native.MULTICAST_ON
+
+
+def synchronize(device=None) -> None:
+    """Wait for torch's current stream and raise if a kernel on it gave up on a bounded wait
+    (C ABI ``b200_hgemm_synchronize``)."""
+    import torch
+
+    with torch.cuda.device(device):
+        check(_native.load().b200_hgemm_synchronize(int(torch.cuda.current_stream().cuda_stream)))
+
+
 def launch_count() -> int:
     return int(_native.load().b200_hgemm_launch_count())

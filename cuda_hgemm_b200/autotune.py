@@ -119,7 +119,11 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--margin", type=float, default=0.03)
     ap.add_argument("--sustained", action="store_true", help="time under the power cap instead of in bursts")
+    ap.add_argument("--multicast", action="store_true",
+                    help="tune for a process that owns one GPU and has switched the multicast kernels on")
     args = ap.parse_args(argv)
+    if args.multicast and not api.enable_multicast(True):
+        ap.error("the multicast kernels are not available in this process")
 
     shapes = []
     if args.squares:

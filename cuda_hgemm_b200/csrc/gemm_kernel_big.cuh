@@ -38,11 +38,9 @@ constexpr uint32_t kBigTmemCols = 512;
 constexpr uint32_t kBigSmemBytes = 1024 + kBigStages * kBigStageBytes + kBigStagingBytes + 256;
 static_assert(kBigSmemBytes <= 232448, "over the 227 KB a CTA can have");
 
-// The barrier of the pair's leader CTA, as seen from either CTA of the pair: shared-window
-// addresses carry the CTA's rank in the cluster from bit 24 up, and the two CTAs of a pair differ
-// in bit 24 only.
-__device__ __forceinline__ uint32_t pair_leader_bar(uint32_t local_bar) {
-    return local_bar & 0xFEFFFFFFu;
+// The barrier of the pair's leader CTA (the even rank of the pair), as seen from either CTA of the pair.
+__device__ __forceinline__ uint32_t pair_leader_bar(uint32_t local_bar, uint32_t cluster_rank) {
+    return map_to_cta(local_bar, cluster_rank & ~1u);
 }
 
 // Stands in for MulticastLoad where no group of four exists.
@@ -133,7 +131,7 @@ __device__ __forceinline__ void hgemm_big_body(const GemmParams &p) {
                     const uint32_t sb = sa + kBigABytes;
                     const int32_t kx = static_cast<int32_t>(kb * kBK);
                     if (half == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * kBigStageBytes);
-                    const uint32_t leader = pair_leader_bar(full_bar + 8u * stage);
+                    const uint32_t leader = pair_leader_bar(full_bar + 8u * stage, rank);
                     if (quad) {
                         // rows [pair * 128, +128) of the slab, for this CTA and its twin in the other pair
                         MulticastLoad::load(sa + pair * (kBigABytes / 2), &p.tm_a, kx, row_a0 + static_cast<int32_t>(pair * 128u), leader,

@@ -14,6 +14,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <initializer_list>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -50,7 +51,8 @@ struct TensorMapSlot {
 
 struct DeviceState {
     std::mutex mu;
-    bool probed = false;
+    bool probed = false;       // attributes known and the error word allocated
+    bool attrs_known = false;  // sm100 / sm_count filled in (no allocation needed for that)
     bool sm100 = false;
     int sm_count = 0;
     uint32_t *error_word = nullptr;
@@ -63,8 +65,10 @@ struct DeviceState {
         cudaStream_t stream;
         void *ptr;
         size_t bytes;
+        uint64_t last_use;
     };
     std::vector<StreamWorkspace> owned_ws;
+    uint64_t ws_clock = 0;
     // staging buffers of the host-pointer entry point
     void *host_a = nullptr, *host_b = nullptr, *host_c = nullptr;
     size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
@@ -110,6 +114,20 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Compute capability and SM count of `dev`, asked for once; allocates nothing. Call with st.mu held.
+static int probe_attributes_locked(DeviceState &st, int dev) {
+    if (st.attrs_known) return B200_HGEMM_OK;
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return B200_HGEMM_ERR_CUDA;
+    }
+    st.sm100 = (major == 10);
+    st.sm_count = sms;
+    st.attrs_known = true;
+    return B200_HGEMM_OK;
+}
+
 static int current_state(DeviceState **out) {
     int dev = 0;
     if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return B200_HGEMM_ERR_CUDA;
@@ -126,13 +144,8 @@ static int current_state(DeviceState **out) {
     DeviceState &st = g_dev[dev];
     std::lock_guard<std::mutex> lock(st.mu);
     if (!st.probed) {
-        int major = 0, sms = 0;
-        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
-            return B200_HGEMM_ERR_CUDA;
-        }
-        st.sm100 = (major == 10);
-        st.sm_count = sms;
+        const int rc = probe_attributes_locked(st, dev);
+        if (rc != B200_HGEMM_OK) return rc;
         if (st.sm100) {
             if (!cuda_ok(cudaMalloc(&st.error_word, 256), "cudaMalloc")) return B200_HGEMM_ERR_CUDA;
             if (!cuda_ok(cudaMemset(st.error_word, 0, 256), "cudaMemset")) return B200_HGEMM_ERR_CUDA;
@@ -179,11 +192,18 @@ static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint6
 }
 
 // ------------------------------------------------------------------------------------------
-// optional single-GPU companion library (the kernel variant whose operand loads are shared
+// optional single-GPU companion library (the kernel variants whose operand loads are shared
 // between the CTAs of a cluster)
 // ------------------------------------------------------------------------------------------
-// It is a separate shared object next to this one so that it can be left out wholesale: runs on
-// several GPUs do not carry it, and everything here works without it.
+// It is a separate shared object next to this one so that it can be left out wholesale, and it is
+// OFF unless the process asks for it (b200_hgemm_enable_multicast(1), or B200_HGEMM_MULTICAST=1 in
+// the environment). A process that drives two or more GPUs can never switch it on: the kernels'
+// tensor maps must cover the memory of the one GPU they run on, and a process that owns one GPU
+// is the one setting in which that holds by construction (the reference's model: one device per
+// process, src/main.cu:45,51). Such a process is recognised by
+//   * WORLD_SIZE or LOCAL_WORLD_SIZE > 1 in the environment (one rank of several), or
+//   * a b200_mg_create() call that names two or more devices,
+// and either locks the switch in the off position for the rest of the process's life.
 typedef int (*McLaunchFn)(const void *params, void *stream, int use_pdl);
 
 struct McEntryPoints {
@@ -191,10 +211,19 @@ struct McEntryPoints {
     McLaunchFn launch512 = nullptr;  // 512 x 512 super-tiles, 256 x 256 per CTA
 };
 
+enum : int { kMcOff = 0, kMcOn = 1, kMcLocked = 2 };
+static std::atomic<int> g_mc_state{kMcOff};
+static std::once_flag g_mc_env_once;
+
+static bool env_int_above_one(const char *name) {
+    const char *v = getenv(name);
+    return v && atol(v) > 1;
+}
+
+// The companion's entry points; the library is opened on first request only.
 static const McEntryPoints &mc_entry_points() {
     static McEntryPoints ep = []() -> McEntryPoints {
         McEntryPoints e;
-        if (getenv("B200_HGEMM_NO_MULTICAST")) return e;
         Dl_info info;
         if (!dladdr(reinterpret_cast<const void *>(&g_launches), &info) || !info.dli_fname) return e;
         std::string path(info.dli_fname);
@@ -209,7 +238,41 @@ static const McEntryPoints &mc_entry_points() {
     return ep;
 }
 
+static void mc_lock_off() {
+    g_mc_state.store(kMcLocked, std::memory_order_release);
+}
+
+static int mc_enable(bool on) {
+    if (g_mc_state.load(std::memory_order_acquire) == kMcLocked) return on ? B200_HGEMM_ERR_UNSUPPORTED : B200_HGEMM_OK;
+    if (!on) {
+        int expected = kMcOn;
+        g_mc_state.compare_exchange_strong(expected, kMcOff);
+        return B200_HGEMM_OK;
+    }
+    if (getenv("B200_HGEMM_NO_MULTICAST")) return B200_HGEMM_ERR_UNSUPPORTED;
+    const McEntryPoints &ep = mc_entry_points();
+    if (!ep.launch256 || !ep.launch512) return B200_HGEMM_ERR_UNSUPPORTED;
+    int expected = kMcOff;
+    g_mc_state.compare_exchange_strong(expected, kMcOn);  // loses against a lock taken meanwhile
+    return g_mc_state.load(std::memory_order_acquire) == kMcOn ? B200_HGEMM_OK : B200_HGEMM_ERR_UNSUPPORTED;
+}
+
+// The switch as the environment sets it, read once: ranks of a multi-process job lock it off,
+// B200_HGEMM_MULTICAST=1 asks for it.
+static int mc_state() {
+    std::call_once(g_mc_env_once, []() {
+        if (env_int_above_one("WORLD_SIZE") || env_int_above_one("LOCAL_WORLD_SIZE")) {
+            mc_lock_off();
+        } else if (const char *v = getenv("B200_HGEMM_MULTICAST")) {
+            if (atoi(v) != 0) mc_enable(true);
+        }
+    });
+    return g_mc_state.load(std::memory_order_acquire);
+}
+
+// The launcher of the multicast kernel for this arrangement, or null when the process may not use it.
 static McLaunchFn mc_launch_fn(int bn = 256) {
+    if (mc_state() != kMcOn) return nullptr;
     return bn == 512 ? mc_entry_points().launch512 : mc_entry_points().launch256;
 }
 
@@ -627,6 +690,8 @@ constexpr size_t kMaxStreamWorkspaces = 64;
 
 // The workspace a stream-k launch on `stream` may use: the caller's when one was handed over,
 // else this stream's own, allocated or grown here (cudaMalloc / cudaFree: never during capture).
+// At most kMaxStreamWorkspaces streams hold one at a time; when a further stream asks, the
+// workspace used longest ago is given up (its cudaFree waits for the work that still uses it).
 static int workspace_for(DeviceState &st, cudaStream_t stream, size_t need, uint8_t **out) {
     std::lock_guard<std::mutex> lock(st.mu);
     if (st.ws) {
@@ -640,10 +705,19 @@ static int workspace_for(DeviceState &st, cudaStream_t stream, size_t need, uint
         if (w.stream == stream) slot = &w;
     }
     if (!slot) {
-        if (st.owned_ws.size() >= kMaxStreamWorkspaces) return B200_HGEMM_ERR_WORKSPACE;
-        st.owned_ws.push_back({stream, nullptr, 0});
-        slot = &st.owned_ws.back();
+        if (st.owned_ws.size() >= kMaxStreamWorkspaces) {
+            size_t oldest = 0;
+            for (size_t i = 1; i < st.owned_ws.size(); ++i) {
+                if (st.owned_ws[i].last_use < st.owned_ws[oldest].last_use) oldest = i;
+            }
+            slot = &st.owned_ws[oldest];
+            slot->stream = stream;  // the buffer itself is kept when it is large enough
+        } else {
+            st.owned_ws.push_back({stream, nullptr, 0, 0});
+            slot = &st.owned_ws.back();
+        }
     }
+    slot->last_use = ++st.ws_clock;
     if (slot->bytes < need) {
         if (slot->ptr) {
             if (!cuda_ok(cudaFree(slot->ptr), "cudaFree")) return B200_HGEMM_ERR_CUDA;  // synchronises the device
@@ -840,6 +914,15 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
                           error_word_override ? error_word_override : st.error_word);
     }
     if (pl.variant == B200_VARIANT_CTA2_MCAST) {
+        // the multicast loads may only ever read this GPU's own memory: every operand must be an
+        // allocation of the device the kernel is launched on (not a peer's, not host memory)
+        int cur_dev = -1;
+        if (!cuda_ok(cudaGetDevice(&cur_dev), "cudaGetDevice")) return B200_HGEMM_ERR_CUDA;
+        for (const void *ptr : {A, B, static_cast<const void *>(C)}) {
+            cudaPointerAttributes pa;
+            if (!cuda_ok(cudaPointerGetAttributes(&pa, ptr), "cudaPointerGetAttributes")) return B200_HGEMM_ERR_CUDA;
+            if (pa.type != cudaMemoryTypeDevice || pa.device != cur_dev) return B200_HGEMM_ERR_UNSUPPORTED;
+        }
         GemmParams mp;
         memset(&mp, 0, sizeof(mp));
         mp.c = static_cast<__half *>(C);
@@ -1172,7 +1255,8 @@ int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N,
 //    partial tiles are always written before they are read. Two calls whose kernels overlap on
 //    the GPU (different streams with no dependency between them) race on the array: serialise them.
 //  * A bounded wait that expires inside this variant is recorded in the first word of the
-//    array, not in the word b200_hgemm_last_device_error() reads.
+//    array, not in the word b200_hgemm_last_device_error() reads: b200_hgemm_streamk_static_last_error()
+//    reads and clears it (it allocates nothing either).
 int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                               b200_stream_t stream) {
     int rc = check_args(A, B, C, M, N, K);
@@ -1199,7 +1283,13 @@ int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, s
     uint32_t parts = static_cast<uint32_t>(sd.sm_count);
     if (parts > kStaticMaxParts) parts = kStaticMaxParts;
     pl.parts = static_cast<int32_t>(parts);
-    // g_dev[dev] serves as the cache of tensor maps and kernel attributes; nothing in it is allocated here
+    // g_dev[dev] serves as the cache of tensor maps and kernel attributes; its attributes are filled
+    // in here if no other entry point has yet, and nothing in it is allocated on this path
+    {
+        std::lock_guard<std::mutex> lock(g_dev[dev].mu);
+        rc = probe_attributes_locked(g_dev[dev], dev);
+        if (rc != B200_HGEMM_OK) return rc;
+    }
     return run_plan(g_dev[dev], A, B, C, M, N, K, pl, s, sd.scratch + kStaticHeaderBytes,
                     kCounterBytes + kStaticPartialBytes, reinterpret_cast<uint32_t *>(sd.scratch));
 }
@@ -1278,6 +1368,23 @@ int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {
     return B200_HGEMM_OK;
 }
 
+int b200_hgemm_enable_multicast(int on) {
+    mc_state();  // what the environment says comes first (it may lock the switch)
+    return mc_enable(on != 0);
+}
+
+int b200_hgemm_multicast_state(void) {
+    return mc_state();
+}
+
+int b200_hgemm_plan_supported(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan) {
+    if (!plan || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    const int rc = validate_plan(*plan, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (plan->variant == B200_VARIANT_SKINNY && M > static_cast<size_t>(plan->bn)) return B200_HGEMM_ERR_UNSUPPORTED;
+    return B200_HGEMM_OK;
+}
+
 int b200_hgemm_load_plan_table(const char *path) {
     std::vector<TunedPlan> fresh;
     int entries = 0;
@@ -1338,6 +1445,56 @@ int b200_hgemm_set_workspace(void *workspace, size_t bytes) {
     st->ws = workspace;
     st->ws_bytes = workspace ? bytes : 0;
     return B200_HGEMM_OK;
+}
+
+int b200_hgemm_release_workspaces(void) {
+    DeviceState *st = nullptr;
+    int rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    std::lock_guard<std::mutex> lock(st->mu);
+    int freed = 0;
+    for (auto &w : st->owned_ws) {
+        if (w.ptr && cuda_ok(cudaFree(w.ptr), "cudaFree")) ++freed;  // waits for work that still uses it
+    }
+    st->owned_ws.clear();
+    return freed;
+}
+
+// Reads the error word behind work already complete on `stream` (4 bytes, ordered on that stream).
+static int read_error_word(uint32_t *word_dev, cudaStream_t stream, uint32_t *word) {
+    *word = 0;
+    if (!cuda_ok(cudaMemcpyAsync(word, word_dev, sizeof(*word), cudaMemcpyDeviceToHost, stream), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
+    if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
+    if (*word != 0) {
+        if (!cuda_ok(cudaMemsetAsync(word_dev, 0, sizeof(*word), stream), "cudaMemsetAsync")) return B200_HGEMM_ERR_CUDA;
+        if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
+    }
+    return B200_HGEMM_OK;
+}
+
+int b200_hgemm_synchronize(b200_stream_t stream) {
+    DeviceState *st = nullptr;
+    int rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    uint32_t word = 0;
+    rc = read_error_word(st->error_word, reinterpret_cast<cudaStream_t>(stream), &word);
+    if (rc != B200_HGEMM_OK) return rc;
+    return word != 0 ? B200_HGEMM_ERR_DEVICE_WAIT : B200_HGEMM_OK;
+}
+
+int b200_hgemm_streamk_static_last_error(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_HGEMM_ERR_CUDA;
+    StaticDevice sd;
+    int rc = static_device(dev, &sd);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!sd.sm100) return B200_HGEMM_ERR_NO_SM100;
+    if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return B200_HGEMM_ERR_CUDA;
+    uint32_t word = 0;
+    if (!cuda_ok(cudaMemcpy(&word, sd.scratch, sizeof(word), cudaMemcpyDeviceToHost), "cudaMemcpy")) return B200_HGEMM_ERR_CUDA;
+    if (word != 0) cudaMemset(sd.scratch, 0, sizeof(word));
+    return static_cast<int>(word);
 }
 
 int b200_hgemm_last_device_error(void) {
@@ -1429,6 +1586,15 @@ static int host_pipeline(const void *A_host, const void *B_any, void *C_host, si
     // GEMM and the download of the last slab: slabs of about 1024 rows keep that under a millisecond
     // at N = K = 16384.
     cudaStream_t s_up = st->host_stream[0], s_run = st->host_stream[1], s_down = st->host_stream[2];
+    // Whatever ends the call, it returns only when nothing it queued is still running: the caller
+    // may free or reuse its host buffers at once, and the staging buffers are free for the next call.
+    struct Drain {
+        cudaStream_t s[3];
+        ~Drain() {
+            for (cudaStream_t x : s) cudaStreamSynchronize(x);
+            cudaGetLastError();
+        }
+    } drain{{s_up, s_run, s_down}};
     const void *b_dev = B_any;
     if (!b_on_device) {
         if (!cuda_ok(cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
@@ -1524,6 +1690,9 @@ int b200_partition_slab(size_t M, int n, int index, size_t *row0, size_t *rows) 
 
 int b200_mg_create(const int *devices, int n, b200_mg **out) {
     if (!devices || !out || n < 1 || n > kMaxDevices) return B200_HGEMM_ERR_INVALID_ARG;
+    // A process that sets out to drive several GPUs never runs the kernels with multicast loads;
+    // the switch is locked before anything else can fail.
+    if (n >= 2) mc_lock_off();
     int count = 0;
     if (!cuda_ok(cudaGetDeviceCount(&count), "cudaGetDeviceCount")) return B200_HGEMM_ERR_CUDA;
     for (int i = 0; i < n; ++i) {
@@ -1641,7 +1810,19 @@ int b200_mg_synchronize(b200_mg *mg) {
         if (!cuda_ok(cudaSetDevice(mg->devices[i]), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
         if (!cuda_ok(cudaStreamSynchronize(mg->streams[i]), "cudaStreamSynchronize")) return B200_HGEMM_ERR_CUDA;
     }
-    return B200_HGEMM_OK;
+    // a bounded wait that expired on any of the devices ends the call with an error (the word is cleared)
+    bool gave_up = false;
+    for (int i = 0; i < mg->n; ++i) {
+        if (!cuda_ok(cudaSetDevice(mg->devices[i]), "cudaSetDevice")) return B200_HGEMM_ERR_CUDA;
+        DeviceState *st = nullptr;
+        int rc = current_state(&st);
+        if (rc != B200_HGEMM_OK) return rc;
+        uint32_t word = 0;
+        rc = read_error_word(st->error_word, mg->streams[i], &word);
+        if (rc != B200_HGEMM_OK) return rc;
+        gave_up = gave_up || word != 0;
+    }
+    return gave_up ? B200_HGEMM_ERR_DEVICE_WAIT : B200_HGEMM_OK;
 }
 
 int b200_mg_elapsed_ms_max(b200_mg *mg, float *ms) {

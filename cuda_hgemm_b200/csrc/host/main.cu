@@ -45,6 +45,7 @@ DEFINE_string(dist, "uniform", "input distribution: uniform ([-1,1)) or normal (
 DEFINE_uint32(check_rows, 512, "rows of C checked against the host GEMM when M is larger (0 = all rows)");
 DEFINE_uint32(l2_rotate, 1, "distinct B buffers cycled through the timed loop so that B is not served from L2");
 DEFINE_string(json, "", "append one JSON line per evaluated kernel to this file");
+DEFINE_bool(enable_multicast, false, "let the auto dispatch use the kernels with multicast operand loads (this process owns one GPU)");
 
 namespace {
 
@@ -162,6 +163,9 @@ int main(int argc, char *argv[]) {
     }
 
     if (FLAGS_enable_b200) {
+        if (FLAGS_enable_multicast && b200_hgemm_enable_multicast(1) != B200_HGEMM_OK) {
+            HLOG("multicast kernels not available (companion library absent, or this process is one rank of several)");
+        }
         tester.evaluate(b200Hgemm, "B200-Tcgen05-Auto");
         if (FLAGS_enable_variants && FLAGS_K % 8 == 0) {
             tester.evaluate(b200HgemmCta1, "B200-Tcgen05-1Cta");

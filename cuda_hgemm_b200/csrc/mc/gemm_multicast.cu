@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_mc_kernel(const __g
                     const uint32_t sb = sa + kMcABytes;
                     const int32_t kx = static_cast<int32_t>(kb * kBK);
                     if (half == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * kMcStageBytes);
-                    const uint32_t leader = pair_leader_bar(full_bar + 8u * stage);
+                    const uint32_t leader = pair_leader_bar(full_bar + 8u * stage, rank);
                     if (quad) {
                         tma_load_2d_pair_multicast(sa + pair * (kMcABytes / 2), &p.tm_a, kx, row_a0 + static_cast<int32_t>(pair * 64u),
                                                    leader, a_mask);

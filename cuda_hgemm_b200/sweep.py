@@ -23,7 +23,8 @@ from . import build
 REF_PREFIXES = ("Wmma-", "Mma-", "Simt-")
 
 
-def run_size(binary: Path, n: int, out_dir: Path, ref_lib: str | None, warmup: int, iters: int, check: bool):
+def run_size(binary: Path, n: int, out_dir: Path, ref_lib: str | None, warmup: int, iters: int, check: bool,
+             multicast: bool = False):
     log = out_dir / "log" / f"hgemm_{n}_{n}_{n}.log"
     js = out_dir / "json" / f"hgemm_{n}.jsonl"
     log.parent.mkdir(parents=True, exist_ok=True)
@@ -33,6 +34,8 @@ def run_size(binary: Path, n: int, out_dir: Path, ref_lib: str | None, warmup: i
     cmd = [str(binary), f"-M={n}", f"-N={n}", f"-K={n}", f"-warmup_iterations={warmup}",
            f"-profiling_iterations={iters}", "-sleep_duration=1", f"-enable_check={'true' if check else 'false'}",
            "-enable_variants=false", f"-json={js}"]
+    if multicast:
+        cmd.append("-enable_multicast=true")
     if ref_lib:
         cmd.append(f"-ref_lib={ref_lib}")
     else:
@@ -71,6 +74,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ref-lib", default=None, help="library built from the reference's kernels (optional)")
     ap.add_argument("--check-up-to", type=int, default=2048, help="run -enable_check for sizes up to this")
+    ap.add_argument("--multicast", action="store_true", help="pass -enable_multicast=true to the driver (one GPU per process)")
     args = ap.parse_args(argv)
 
     binary = build.DRIVER_BIN
@@ -81,7 +85,7 @@ def main(argv=None) -> int:
     summary = []
     with open(out_dir / "sweep.jsonl", "w") as allf:
         for n in range(args.first, args.last + 1, args.step):
-            rc, rows = run_size(binary, n, out_dir, args.ref_lib, args.warmup, args.iters, n <= args.check_up_to)
+            rc, rows = run_size(binary, n, out_dir, args.ref_lib, args.warmup, args.iters, n <= args.check_up_to, args.multicast)
             for r in rows:
                 allf.write(json.dumps(r) + "\n")
             s = summarise(n, rows)

@@ -40,7 +40,7 @@ enum {
     B200_HGEMM_ERR_NO_SM100 = -4,     /* current device is not compute capability 10.x */
     B200_HGEMM_ERR_CUDA = -5,         /* a CUDA runtime / driver call failed */
     B200_HGEMM_ERR_WORKSPACE = -6,    /* split-k workspace missing or too small */
-    B200_HGEMM_ERR_DEVICE_WAIT = -7,  /* a kernel gave up on a bounded wait (see last_device_error) */
+    B200_HGEMM_ERR_DEVICE_WAIT = -7,  /* a kernel gave up on a bounded wait (b200_hgemm_synchronize, b200_mg_synchronize) */
     B200_HGEMM_ERR_TOO_LARGE = -8     /* size beyond a stated maximum of the entry point */
 };
 
@@ -51,8 +51,10 @@ enum {
     B200_VARIANT_STREAMK = 2, /* cta_group::1, k-ranges split across CTAs, FP32 workspace reduce */
     B200_VARIANT_SIMT = 3,    /* CUDA-core kernel for shapes the tensor path rejects (K % 8 != 0) */
     B200_VARIANT_CTA2_MCAST = 4, /* CTA pairs in clusters of four with the A slab delivered by TMA multicast;
-                                   single-GPU builds only: it lives in libb200_hgemm_mc.so, which the library
-                                   loads when present (B200_HGEMM_ERR_UNSUPPORTED otherwise); needs N % 8 == 0 */
+                                   single-GPU processes only and off by default: it lives in libb200_hgemm_mc.so,
+                                   which the library opens after b200_hgemm_enable_multicast(1)
+                                   (B200_HGEMM_ERR_UNSUPPORTED otherwise); needs N % 8 == 0; A, B and C must be
+                                   allocations of the GPU the call runs on */
     B200_VARIANT_SKINNY = 5,     /* M <= 64 (decode batches): B streams through the MMA's row operand and C is
                                    accumulated transposed; plan.bn = rows of A per tile (16, 32 or 64, >= M),
                                    plan.parts = equal k-ranges per column tile (0 = library's choice), summed
@@ -99,9 +101,14 @@ int b200_hgemm_streamk(const void *A, const void *B, void *C, size_t M, size_t N
  * Limits: K % 8 == 0; ceil(M/128) * ceil(N/128) <= 16384 tiles, else B200_HGEMM_ERR_TOO_LARGE.
  * The first call on a device resolves the array's device address and should come before any
  * stream capture. Calls share the array: kernels of two calls that overlap on the GPU race.
- * A device-side wait expiry in this variant is recorded in the array's first word only. */
+ * A device-side wait expiry in this variant is recorded in the array's first word only, which
+ * b200_hgemm_streamk_static_last_error() reads. */
 int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                               b200_stream_t stream);
+/* Synchronises the current device and returns the error word of the static array (0 = none, 1 = a
+ * bounded wait expired inside b200_hgemm_streamk_static), clearing it. Allocates nothing. Like the
+ * entry point it serves, it has no counterpart in the reference. */
+int b200_hgemm_streamk_static_last_error(void);
 
 /* Any-shape CUDA-core kernel with FP32 accumulation: the counterpart of the reference's
  * simtNaive (src/simt_naive.cu:9-32), with the bounds guard corrected. */
@@ -160,9 +167,36 @@ size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm
  * may overlap freely. Pass (NULL, 0) to go back to that. */
 int b200_hgemm_set_workspace(void *workspace, size_t bytes);
 
+/* The library keeps at most 64 of those per-stream workspaces on a device (32 MiB or more each); when
+ * a 65th stream needs one, the workspace used longest ago changes hands (a cudaFree, which waits for the
+ * work that used it, only if it is too small). This call frees all of them on the current device, e.g.
+ * after a burst of short-lived streams; returns how many were freed, or a negative status. */
+int b200_hgemm_release_workspaces(void);
+
 /* Synchronises the current device and returns the device-side error word (0 = none,
  * 1 = a bounded wait expired), clearing it. */
 int b200_hgemm_last_device_error(void);
+
+/* Waits for `stream` and reports what the kernels on it left in the device-side error word:
+ * B200_HGEMM_OK, or B200_HGEMM_ERR_DEVICE_WAIT when a kernel gave up on a bounded wait (the word is
+ * cleared). Unlike b200_hgemm_last_device_error() it waits for this stream only. The reference has
+ * no counterpart: its launches are never checked (src/mma/mma_async_stage4.cu:643). */
+int b200_hgemm_synchronize(b200_stream_t stream);
+
+/* Whether `plan` can run for this shape in this process (B200_HGEMM_OK) or why not; no device is touched. */
+int b200_hgemm_plan_supported(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan);
+
+/* The kernels that share operand loads between the CTAs of a cluster (B200_VARIANT_CTA2_MCAST, in
+ * libb200_hgemm_mc.so) are OFF unless the process switches them on here (or starts with
+ * B200_HGEMM_MULTICAST=1 in its environment). They are for processes that own ONE GPU, the
+ * reference's model (its only device knob is -gpu_rank, src/main.cu:45,51): in a process that is one
+ * rank of several (WORLD_SIZE or LOCAL_WORLD_SIZE > 1) or that has called b200_mg_create() with two or
+ * more devices the switch is locked off for good, b200_hgemm_enable_multicast(1) returns
+ * B200_HGEMM_ERR_UNSUPPORTED, b200_hgemm_select() never picks the variant and an explicit plan that
+ * names it is refused. Also B200_HGEMM_ERR_UNSUPPORTED when the companion library is absent.
+ * b200_hgemm_multicast_state(): 0 = off, 1 = on, 2 = locked off. */
+int b200_hgemm_enable_multicast(int on);
+int b200_hgemm_multicast_state(void);
 
 const char *b200_hgemm_status_string(int status);
 const char *b200_hgemm_version(void);
@@ -192,7 +226,8 @@ int b200_mg_hgemm(b200_mg *mg, const void *const *A_slabs, const void *const *B_
  * ordered after the multiply on the owning device's stream: a gather when one entry is set, an all-gather
  * when all are. */
 int b200_mg_gather_c(b200_mg *mg, void *const *C_slabs, void *const *C_full, size_t M, size_t N);
-/* Waits for everything launched through the handle. */
+/* Waits for everything launched through the handle; B200_HGEMM_ERR_DEVICE_WAIT when a kernel on any of
+ * the devices gave up on a bounded wait (the error words are cleared). */
 int b200_mg_synchronize(b200_mg *mg);
 /* After b200_mg_synchronize: device time of the last b200_mg_hgemm, the maximum over the devices (ms). */
 int b200_mg_elapsed_ms_max(b200_mg *mg, float *ms);

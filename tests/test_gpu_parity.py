@@ -127,14 +127,23 @@ def test_cta_pair_tiles(cuda_device, shape, bn):
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta2 bn={bn} {shape}")
 
 
-@pytest.mark.parametrize("shape", [(256, 512, 64), (256, 256, 320), (328, 776, 136), (1024, 2048, 1024), (2304, 2560, 512)],
-                         ids=lambda s: "x".join(map(str, s)))
-def test_cluster_multicast_pairs(cuda_device, shape):
-    """The single-GPU companion kernel: CTA pairs in clusters of four, A slabs delivered by TMA multicast."""
+@pytest.fixture
+def multicast_on():
+    """Switches the single-GPU multicast kernels on for one test (they are off by default)."""
     from cuda_hgemm_b200 import build
 
     if not build.MULTICAST_SO.exists():
         pytest.skip("libb200_hgemm_mc.so is not part of this run (it is left out on multi-GPU runs)")
+    if not api.enable_multicast(True):
+        pytest.skip("this process may not use the multicast kernels (it drives several GPUs)")
+    yield
+    api.enable_multicast(False)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 64), (256, 256, 320), (328, 776, 136), (1024, 2048, 1024), (2304, 2560, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_cluster_multicast_pairs(cuda_device, multicast_on, shape):
+    """The single-GPU companion kernel: CTA pairs in clusters of four, A slabs delivered by TMA multicast."""
     M, N, K = shape
     A, B = make_inputs(M, N, K, seed=12)
     C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2_MCAST, 256))
@@ -169,18 +178,47 @@ def test_pair_tiles_of_256_rows_per_cta(cuda_device, shape):
 
 
 @pytest.mark.parametrize("shape", BIG_TILE_SHAPES, ids=lambda s: "x".join(map(str, s)))
-def test_cluster_multicast_groups_of_256_rows_per_cta(cuda_device, shape):
+def test_cluster_multicast_groups_of_256_rows_per_cta(cuda_device, multicast_on, shape):
     """512 x 512 tiles on groups of four CTAs, A slab halves delivered by TMA multicast."""
-    from cuda_hgemm_b200 import build
-
-    if not build.MULTICAST_SO.exists():
-        pytest.skip("libb200_hgemm_mc.so is not part of this run (it is left out on multi-GPU runs)")
     M, N, K = shape
     A, B = make_inputs(M, N, K, seed=22)
     C = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2_MCAST, 512))
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"multicast 512x512 {shape}")
     C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_CTA2, 512))
     assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
+def test_multicast_kernels_are_off_until_asked_for_and_take_local_device_memory_only(cuda_device):
+    """Default: the dispatch never picks them and an explicit plan is refused. Switched on: operands that
+    are not allocations of the current GPU (here: pinned host memory) are refused before anything is launched."""
+    import torch
+
+    from cuda_hgemm_b200 import build
+
+    lib = _native.load()
+    if lib.b200_hgemm_multicast_state() == _native.MULTICAST_ON:
+        api.enable_multicast(False)
+    M = N = K = 512
+    A, B = make_inputs(M, N, K, seed=24)
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    C = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+    for bn in (256, 512):
+        with pytest.raises(_native.HgemmError) as e:
+            api.hgemm_ex(dA, dB, C, plan_of(_native.VARIANT_CTA2_MCAST, bn))
+        assert e.value.status == _native.ERR_UNSUPPORTED
+    assert api.select_plan_untuned(16384, 16384, 16384).variant == _native.VARIANT_CTA2
+    if not build.MULTICAST_SO.exists() or not api.enable_multicast(True):
+        return
+    try:
+        hA = torch.from_numpy(A).pin_memory()
+        rc = lib.b200_hgemm_ex(hA.data_ptr(), dB.data_ptr(), C.data_ptr(), M, N, K,
+                               ctypes.byref(plan_of(_native.VARIANT_CTA2_MCAST, 512)), None)
+        assert rc == _native.ERR_UNSUPPORTED
+        api.hgemm_ex(dA, dB, C, plan_of(_native.VARIANT_CTA2_MCAST, 512))
+        torch.cuda.synchronize()
+        assert_close_to_oracle(C.cpu().numpy(), oracle.gemm_f32(A, B), "multicast after a refused call")
+    finally:
+        api.enable_multicast(False)
 
 
 def test_large_tiles_refuse_what_their_epilogue_cannot_store(cuda_device):
