@@ -45,6 +45,9 @@ WORKLOADS = {
     "skinny16": (16, 14336, 4096, "normal", "decode-style HGEMM M=16 N=14336 K=4096"),
     "skinny128": (128, 14336, 4096, "normal", "decode-style HGEMM M=128 N=14336 K=4096"),
     "skinny128t": (128, 4096, 14336, "normal", "decode-style HGEMM M=128 N=4096 K=14336"),
+    "skinny32": (32, 14336, 4096, "normal", "decode-style HGEMM M=32 N=14336 K=4096"),
+    "skinny64": (64, 14336, 4096, "normal", "decode-style HGEMM M=64 N=14336 K=4096"),
+    "skinny16t": (16, 4096, 14336, "normal", "decode-style HGEMM M=16 N=4096 K=14336"),
 }
 
 
@@ -150,30 +153,33 @@ def make_inputs(torch, M, N, K, dist, device, row_lo, row_hi):
 
 
 from cuda_hgemm_b200 import _native  # noqa: E402
-from cuda_hgemm_b200.timing import (cublas_callable, load_compare, preheat, time_graph,  # noqa: E402
+from cuda_hgemm_b200.timing import (PREHEAT_S, cublas_callable, load_compare, time_burst, time_graph,  # noqa: E402
                                     time_launches, time_native_loop)
+
+MIN_TIMED_MS = 120.0  # the timed region is at least this long, so that the 2 ms clock sampler sees it often enough
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
-# captures under profiles/, keyed by workload and by the kernel the dispatch picks for it
-# (variant, bn); scaled captures say so there.
+# captures under profiles/, keyed by the shape one launch multiplies (a rank's slab, not the job)
+# and by the kernel the dispatch picks for it (variant, bn); scaled captures say so there.
 NCU_TRAFFIC_BYTES = {
     # profiles/hgemm_tcgen05_big_vs_cublas_square16384.md
-    ("square16384", _native.VARIANT_CTA2_MCAST, 512): 9.43e9,
-    ("square16384", _native.VARIANT_CTA2, 512): 8.46e9,
-    ("square16384", _native.VARIANT_CTA2, 256): 16.5e9,
-    ("square8192", _native.VARIANT_CTA2_MCAST, 512): 0.936e9,  # profiles/hgemm_tcgen05_mc512_square8192.md
-    ("square8192", _native.VARIANT_CTA2, 256): 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
-    ("skinny16", _native.VARIANT_SKINNY, 16): 121.7e6,    # profiles/hgemm_skinny_skinny16.md
-    ("skinny16", _native.VARIANT_CTA1, 128): 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
+    ((16384, 16384, 16384), _native.VARIANT_CTA2_MCAST, 512): 9.43e9,
+    ((16384, 16384, 16384), _native.VARIANT_CTA2, 512): 8.46e9,
+    ((16384, 16384, 16384), _native.VARIANT_CTA2, 256): 16.5e9,
+    ((8192, 8192, 8192), _native.VARIANT_CTA2_MCAST, 512): 0.936e9,  # profiles/hgemm_tcgen05_mc512_square8192.md
+    ((8192, 8192, 8192), _native.VARIANT_CTA2, 256): 1.118e9,   # profiles/hgemm_tcgen05_cta2_square8192.md
+    ((16, 14336, 4096), _native.VARIANT_SKINNY, 16): 121.7e6,    # profiles/hgemm_skinny_skinny16.md
+    ((16, 14336, 4096), _native.VARIANT_CTA1, 128): 121.6e6,     # profiles/hgemm_tcgen05_cta1_skinny16.md
 }
 
 
-def ncu_traffic(workload, plan):
-    return NCU_TRAFFIC_BYTES.get((workload, plan.variant, plan.bn)) if plan is not None else None
+def ncu_traffic(shape, plan):
+    """Measured DRAM bytes of one launch on `shape` = (rows, N, K), or None where no capture exists."""
+    return NCU_TRAFFIC_BYTES.get((tuple(shape), plan.variant, plan.bn)) if plan is not None else None
 
 
-def roofline(workload, plan, rows, N, K, ms_per_step, peaks):
+def roofline(plan, rows, N, K, ms_per_step, peaks):
     """Roofline entry of the dominant kernel for one launch of this rank's slab."""
     skinny = rows <= 128
     if skinny:
@@ -181,7 +187,7 @@ def roofline(workload, plan, rows, N, K, ms_per_step, peaks):
         achieved = algo / (ms_per_step * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": f"{peaks['source']} copy bandwidth",
-                "traffic": ncu_traffic(workload, plan)}
+                "traffic": ncu_traffic((rows, N, K), plan)}
     achieved = 2.0 * rows * N * K / (ms_per_step * 1e-3) / 1e12
     # the timed region follows a pre-heat and runs back to back under the power cap: the sustained
     # cuBLAS figure is the matching denominator; the burst figure is printed beside it
@@ -190,7 +196,52 @@ def roofline(workload, plan, rows, N, K, ms_per_step, peaks):
             "frac": round(achieved / peak, 4),
             "peak_source": f"{peaks['source']} cuBLAS bf16, sustained (kernel timed in a back-to-back loop after a pre-heat)",
             "frac_of_burst_peak": round(achieved / peaks["tflops"], 4), "burst_peak": peaks["tflops"],
-            "traffic": ncu_traffic(workload, plan)}
+            "traffic": ncu_traffic((rows, N, K), plan)}
+
+
+EXTRA_WORKLOADS = ("skinny16", "skinny32", "skinny64", "skinny128", "skinny16t", "skinny128t", "prefill")
+
+
+def measure_workload(torch, api, cmp_lib, name, device, peaks, warmup, steps):
+    """One more configuration of the benchmark on this GPU: ms, TFLOP/s, roofline and both cuBLAS modes."""
+    M, N, K, dist_name, desc = WORKLOADS[name]
+    A, B = make_inputs(torch, M, N, K, dist_name, device, 0, M)
+    C = torch.empty((M, N), dtype=torch.float16, device=device)
+    Bs = [B]
+    if (M * K + N * K + M * N) * 2 < (512 << 20):
+        while len(Bs) * N * K * 2 < (768 << 20) and len(Bs) < 64:
+            Bs.append(B.clone())
+    plan = api.select_plan(M, N, K)
+    turn = [0]
+
+    def ours():
+        api.b200Hgemm(A, Bs[turn[0] % len(Bs)], C)
+        turn[0] += 1
+    before = api.launch_count()
+    ours()
+    per_call = api.launch_count() - before
+    ms = time_launches(torch, ours, warmup, steps)
+    flops = 2.0 * M * N * K
+    entry = {"workload": f"{name}: {desc}", "M": M, "N": N, "K": K, "plan": plan.as_dict(), "ms": round(ms, 5),
+             "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "kernels_per_call": int(per_call),
+             "l2": f"B cycled through {len(Bs)} copies" if len(Bs) > 1 else "operands larger than L2",
+             "roofline": roofline(plan, M, N, K, ms, peaks)}
+    if cmp_lib is not None:
+        Cc = torch.empty_like(C)
+        for key, sym in (("cublas_fp16_compute_tflops", "hgemm_compare_cublas_fp16"),
+                         ("cublas_fp32_compute_tflops", "hgemm_compare_cublas_fp32")):
+            calls = [cublas_callable(torch, cmp_lib, sym, A, b, Cc) for b in Bs]
+            t = [0]
+
+            def cublas_step():
+                calls[t[0] % len(calls)]()
+                t[0] += 1
+            entry[key] = round(flops / (time_launches(torch, cublas_step, warmup, steps) * 1e-3) / 1e12, 2)
+        entry["vs_cublas_best"] = round(entry["tflops"] / max(entry["cublas_fp16_compute_tflops"],
+                                                              entry["cublas_fp32_compute_tflops"]), 4)
+    if api.last_device_error() != 0:
+        raise RuntimeError(f"{name}: a kernel gave up on a bounded wait")
+    return entry
 
 
 def cpu_baseline(M, N, K, dist):
@@ -274,6 +325,9 @@ def run_ours(args):
     A, B = make_inputs(torch, M, N, K, dist_name, device, lo, hi)
     C = torch.empty((hi - lo, N), dtype=torch.float16, device=device)
     rows = hi - lo
+    # one process, one GPU: the kernels with multicast operand loads may be switched on (the library
+    # refuses in a process that is one rank of several, and works the same without them)
+    multicast = api.enable_multicast(True) if world == 1 else False
     plan = api.select_plan(rows, N, K) if rows else None
     # Operands that fit in the 126 MB L2 (the decode-style shapes: B is 117 MB) would be served from
     # L2 on every step after the first: cycle through enough copies of B to exceed L2 several times.
@@ -290,27 +344,53 @@ def run_ours(args):
             counter[0] += 1
 
     # ---- device-resident timing: the headline kernel number ----
-    preheat(torch, step)
+    # Every N is timed in the same regime: ranks meet at the barrier FIRST, then each runs about
+    # 0.3 s of back-to-back steps (the GPU settles under its power cap), and the timed blocks follow
+    # with no host synchronisation in between. A block is `steps` launches between two events; blocks
+    # repeat until the clock sampler has read the GPU often enough inside the timed region.
+    step()
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
     for _ in range(warmup):
         step()
+    p1.record()
+    torch.cuda.synchronize()
+    one_ms = max(p0.elapsed_time(p1) / warmup, 1e-3)
+    preheat_steps = int(max_over_ranks(torch, min(20000.0, PREHEAT_S * 1e3 / one_ms), world, device)) if rows else 0
+    blocks = max(1, min(64, int(-(-MIN_TIMED_MS // (one_ms * steps))))) if rows else 1
+    blocks = int(max_over_ranks(torch, float(blocks), world, device))
     barrier(torch, world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(preheat_steps):
+        step()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
     with ClockSampler(local) as sampler:
         launches_timed0 = api.launch_count()
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
+        marks[0].record()
+        for b in range(blocks):
+            for _ in range(steps):
+                step()
+            marks[b + 1].record()
         torch.cuda.synchronize()
-        launches_timed = api.launch_count() - launches_timed0
+        launches_timed = (api.launch_count() - launches_timed0) // blocks
     barrier(torch, world)
-    ms_total = max_over_ranks(torch, e0.elapsed_time(e1), world, device)
+    block_ms = [marks[b].elapsed_time(marks[b + 1]) for b in range(blocks)]
+    ms_total = max_over_ranks(torch, sum(block_ms) / blocks, world, device)
     if api.last_device_error() != 0:
         raise RuntimeError("a kernel gave up on a bounded wait")
     ms_per_step = ms_total / steps
     flops_job = 2.0 * M * N * K
     value = flops_job / (ms_per_step * 1e-3) / 1e12
     clocks = sampler.summary()
+    clocks["timed_blocks"] = blocks
+    clocks["enough_samples"] = clocks["samples"] >= 5
+    if clocks["sm_mhz"]:
+        # time x clock: comparable between runs that were granted different clocks under the cap
+        clocks["ms_x_mhz_per_step"] = round(ms_per_step * clocks["sm_mhz"], 2)
+    # the reference driver's own protocol beside it: idle pause, 3 warm-up, 10 launches, no pre-heat
+    barrier(torch, world)
+    burst_ms = max_over_ranks(torch, time_burst(torch, step, 3, 10) if rows else 0.0, world, device)
+    barrier(torch, world)
 
     # ---- end to end through the host-pointer entry point ----
     e2e_steps = max(1, min(steps, 5))
@@ -384,7 +464,11 @@ def run_ours(args):
                    "partition": f"{world} row slab(s) of C, B replicated, no collective",
                    "l2": (f"B cycled through {len(Bs)} distinct copies ({len(Bs) * N * K * 2 >> 20} MiB in total) so that no step "
                           "finds its operands in L2") if len(Bs) > 1 else "operands larger than L2",
-                   "plan": plan.as_dict() if plan else None},
+                   "plan": plan.as_dict() if plan else None, "multicast_kernels": multicast},
+        "timed_region": (f"barrier, {preheat_steps} untimed steps back to back (about {PREHEAT_S} s), then {blocks} block(s) of "
+                         f"{steps} steps between CUDA events with no host synchronisation; ms_per_step is the mean over the blocks"),
+        "burst": {"value": round(flops_job / (burst_ms * 1e-3) / 1e12, 2) if burst_ms else None, "unit": "TFLOP/s",
+                  "protocol": "idle 0.25 s, 3 warm-up, 10 launches (the reference driver's, reference src/common/tester.h:55-64,91-95)"},
         "gpu_launches": int(launches_timed),
         "pct_fp16_dense_peak": round(100.0 * value / (NOMINAL_FP16_DENSE_TFLOPS * world), 2),
         "clocks": clocks,
@@ -396,7 +480,7 @@ def run_ours(args):
                 "api": ("multi_gpu.slab_hgemm_host (per rank: pinned host buffers -> H2D of A's rows and 1/N of B -> "
                         "NCCL all-gather of B -> b200_hgemm_host_a -> D2H)") if sharded_b else
                        "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
-        "roofline": roofline(args.workload, plan, rows, N, K, ms_per_step, peaks),
+        "roofline": roofline(plan, rows, N, K, ms_per_step, peaks),
     }
 
     # ---- comparisons on the same operands (outside the timed region) ----
@@ -442,6 +526,11 @@ def run_ours(args):
                              "code, best of 3); graph_*: 20 launches per CUDA graph, 5 replays; operands of the small sizes stay "
                              "in L2 for every library alike")
 
+    if world == 1 and not args.no_workloads:
+        # the other benchmark configurations, each with its own roofline (decode shapes: HBM bound, B cycled
+        # through copies totalling > 768 MiB; prefill: tensor bound), timed like the headline and next to cuBLAS
+        out["workloads"] = [measure_workload(torch, api, cmp_lib, name, device, peaks, warmup, steps)
+                            for name in EXTRA_WORKLOADS if name != args.workload]
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(M, N, K, dist_name)
     if gather_ms is not None:
@@ -543,6 +632,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square16384")
     ap.add_argument("--gather", action="store_true", help="with N > 1: also time the optional all-gather of C")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra square sizes measured after the timed region")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the other benchmark configurations measured after the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = (
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
     "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
     "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
+    "b200_debug_wait_expiry_static",
 )
 
 OK = 0
@@ -133,6 +134,8 @@ def load() -> ctypes.CDLL:
     lib.b200_sched_partial_slot.restype = c_uint32
     lib.b200_debug_wait_expiry.argtypes = [c_uint32, c_void_p]
     lib.b200_debug_wait_expiry.restype = c_int
+    lib.b200_debug_wait_expiry_static.argtypes = [c_uint32, c_void_p]
+    lib.b200_debug_wait_expiry_static.restype = c_int
     lib.b200_partition_slab.argtypes = [c_size_t, c_int, c_int, POINTER(c_size_t), POINTER(c_size_t)]
     lib.b200_partition_slab.restype = c_int
     lib.b200_mg_create.argtypes = [POINTER(c_int), c_int, POINTER(c_void_p)]

@@ -711,6 +711,9 @@ static int workspace_for(DeviceState &st, cudaStream_t stream, size_t need, uint
                 if (st.owned_ws[i].last_use < st.owned_ws[oldest].last_use) oldest = i;
             }
             slot = &st.owned_ws[oldest];
+            // the previous owner's kernels may still be using the buffer (and its stream handle may be
+            // gone by now): wait for the device once; this path is rare
+            if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return B200_HGEMM_ERR_CUDA;
             slot->stream = stream;  // the buffer itself is kept when it is large enough
         } else {
             st.owned_ws.push_back({stream, nullptr, 0, 0});
@@ -1883,6 +1886,20 @@ int b200_debug_wait_expiry(uint32_t limit_ms, b200_stream_t stream) {
     if (rc != B200_HGEMM_OK) return rc;
     if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
     wait_expiry_probe_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(st->error_word,
+                                                                                   static_cast<uint64_t>(limit_ms) * 1000000ull);
+    if (!cuda_ok(cudaGetLastError(), "wait_expiry_probe_kernel")) return B200_HGEMM_ERR_CUDA;
+    return B200_HGEMM_OK;
+}
+
+int b200_debug_wait_expiry_static(uint32_t limit_ms, b200_stream_t stream) {
+    if (limit_ms == 0 || limit_ms > 1000) return B200_HGEMM_ERR_INVALID_ARG;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_HGEMM_ERR_CUDA;
+    StaticDevice sd;
+    const int rc = static_device(dev, &sd);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!sd.sm100) return B200_HGEMM_ERR_NO_SM100;
+    wait_expiry_probe_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<uint32_t *>(sd.scratch),
                                                                                    static_cast<uint64_t>(limit_ms) * 1000000ull);
     if (!cuda_ok(cudaGetLastError(), "wait_expiry_probe_kernel")) return B200_HGEMM_ERR_CUDA;
     return B200_HGEMM_OK;

@@ -168,8 +168,8 @@ size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm
 int b200_hgemm_set_workspace(void *workspace, size_t bytes);
 
 /* The library keeps at most 64 of those per-stream workspaces on a device (32 MiB or more each); when
- * a 65th stream needs one, the workspace used longest ago changes hands (a cudaFree, which waits for the
- * work that used it, only if it is too small). This call frees all of them on the current device, e.g.
+ * a 65th stream needs one, the workspace used longest ago changes hands (after a device synchronisation,
+ * so that its previous owner's kernels are done with it). This call frees all of them on the current device, e.g.
  * after a burst of short-lived streams; returns how many were freed, or a negative status. */
 int b200_hgemm_release_workspaces(void);
 
@@ -250,6 +250,9 @@ uint32_t b200_sched_partial_slot(uint32_t part, uint32_t parts, uint32_t tiles, 
  * arrives on -- the way a kernel of this library would notice a protocol failure -- and raises the
  * device error word. b200_hgemm_last_device_error() then returns 1 and the device stays usable. */
 int b200_debug_wait_expiry(uint32_t limit_ms, b200_stream_t stream);
+/* The same, reported where b200_hgemm_streamk_static reports: in the first word of its static array
+ * (b200_hgemm_streamk_static_last_error() then returns 1). Allocates nothing. */
+int b200_debug_wait_expiry_static(uint32_t limit_ms, b200_stream_t stream);
 /* tcgen05 descriptor encoders (instruction descriptor; shared-memory matrix descriptor). */
 uint32_t b200_debug_idesc(uint32_t m, uint32_t n);
 uint64_t b200_debug_smem_desc(uint32_t smem_addr);

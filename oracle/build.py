@@ -21,7 +21,8 @@ HERE = Path(__file__).resolve().parent
 ORACLE_SO = HERE / "libhgemm_oracle.so"
 REF_DIR = HERE / "_ref"
 REF_SO = REF_DIR / "libcuda_hgemm_ref.so"
-REFERENCE_ROOT = Path(os.environ.get("CUDA_HGEMM_REFERENCE", "/root/reference"))
+# the reference checkout: CUDA_HGEMM_REFERENCE, else a directory named "reference" beside this repository
+REFERENCE_ROOT = Path(os.environ.get("CUDA_HGEMM_REFERENCE") or HERE.parent.parent / "reference")
 
 # reference kernels: entry point -> log name used by its driver (reference src/main.cu:100-123)
 REF_KERNELS = {

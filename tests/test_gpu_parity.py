@@ -679,6 +679,57 @@ def test_an_expired_wait_is_reported_and_the_device_stays_usable(cuda_device):
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), "after an expired wait")
 
 
+def test_synchronize_reports_an_expired_wait_as_a_status(cuda_device):
+    """b200_hgemm_synchronize: waits for one stream and turns a raised error word into B200_HGEMM_ERR_DEVICE_WAIT."""
+    import torch
+
+    lib = _native.load()
+    stream = torch.cuda.Stream(device=cuda_device)
+    assert lib.b200_hgemm_synchronize(stream.cuda_stream) == _native.OK
+    assert lib.b200_debug_wait_expiry(20, stream.cuda_stream) == _native.OK
+    assert lib.b200_hgemm_synchronize(stream.cuda_stream) == _native.ERR_DEVICE_WAIT
+    assert lib.b200_hgemm_synchronize(stream.cuda_stream) == _native.OK   # cleared
+    assert api.last_device_error() == 0
+    A, B = make_inputs(256, 256, 256, seed=41)
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    C = poisoned(256, 256, cuda_device).view(256, 256)
+    with torch.cuda.stream(stream):
+        api.b200Hgemm(dA, dB, C)
+        api.synchronize(cuda_device)
+    assert_close_to_oracle(C.cpu().numpy(), oracle.gemm_f32(A, B), "after a reported wait")
+
+
+def test_more_streams_than_workspace_slots(cuda_device):
+    """The library keeps a stream-k workspace per stream, 64 at most: the 65th stream and every later one
+    still gets one (the one used longest ago changes hands), and they can all be released."""
+    import torch
+
+    lib = _native.load()
+    M, N, K = 96, 1024, 2048
+    A, B = make_inputs(M, N, K, seed=42, dist="normal")
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    expect = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+    api.b200HgemmStreamK(dA, dB, expect)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in range(70)]
+    out = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+    for s in streams:
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s):
+            api.b200HgemmStreamK(dA, dB, out)
+        s.synchronize()
+        assert torch.equal(out, expect)
+    torch.cuda.synchronize()
+    freed = lib.b200_hgemm_release_workspaces()
+    assert 1 <= freed <= 64
+    assert lib.b200_hgemm_release_workspaces() == 0
+    api.b200HgemmStreamK(dA, dB, out)   # allocates afresh
+    torch.cuda.synchronize()
+    assert torch.equal(out, expect)
+    assert api.last_device_error() == 0
+
+
 @pytest.mark.parametrize("shape", [
     (1, 8, 8), (1, 8, 4096), (4096, 8, 64), (8, 4096, 64), (128, 256, 8), (129, 257 * 8, 72), (16, 16, 65536),
     (40000, 16, 64), (24, 40000, 64), (2304, 2304, 2304), (3000, 1000, 520),
@@ -701,3 +752,83 @@ def test_static_scratch_and_every_variant_on_a_lopsided_shape(cuda_device):
                         (_native.VARIANT_SIMT, 0)):
         C = run(None, A, B, cuda_device, plan_of(variant, bn))
         assert_close_to_oracle(C, ref, f"variant {variant} bn {bn}")
+
+
+# ---- the benchmark's own sizes -------------------------------------------------------------
+def device_inputs(M, N, K, dist, seed, device):
+    """Seeded FP16 operands drawn on the GPU (the host would need minutes for 16384^2 draws): uniform [-1, 1),
+    or activations ~ N(0, 1) and weights ~ N(0, 1/K)."""
+    import torch
+
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    if dist == "uniform":
+        A = torch.rand((M, K), generator=g, device=device, dtype=torch.float32).mul_(2).sub_(1).half()
+        B = torch.rand((N, K), generator=g, device=device, dtype=torch.float32).mul_(2).sub_(1).half()
+    else:
+        A = torch.randn((M, K), generator=g, device=device, dtype=torch.float32).half()
+        B = torch.randn((N, K), generator=g, device=device, dtype=torch.float32).div_(K ** 0.5).half()
+    return A, B
+
+
+def check_sampled_row_blocks(C, dA, hB, row_blocks, what):
+    """128-row blocks of C against the oracle: together they cover every column tile and every k-block."""
+    import torch
+
+    rows = torch.cat([torch.arange(r, r + 128, device=dA.device) for r in row_blocks])
+    ref = oracle.gemm_f32(dA[rows].cpu().numpy(), hB)
+    assert_close_to_oracle(C[rows].cpu().numpy(), ref, what)
+
+
+@pytest.mark.parametrize("plan_name", ["auto", "pairs_512x256", "multicast_512x512", "pairs_256x256"])
+def test_square_16384_sampled_rows(cuda_device, plan_name, request):
+    """The benchmark's headline shape under every arrangement the dispatch can give it: many tiles per CTA,
+    256 k-blocks per tile."""
+    import torch
+
+    if plan_name == "multicast_512x512":
+        request.getfixturevalue("multicast_on")
+    plan = {"auto": None, "pairs_512x256": plan_of(_native.VARIANT_CTA2, 512),
+            "multicast_512x512": plan_of(_native.VARIANT_CTA2_MCAST, 512),
+            "pairs_256x256": plan_of(_native.VARIANT_CTA2, 256)}[plan_name]
+    M = N = K = 16384
+    dA, dB = device_inputs(M, N, K, "uniform", 2023, cuda_device)
+    C = poisoned(M, N, cuda_device).view(M, N)
+    if plan is None:
+        api.b200Hgemm(dA, dB, C)
+    else:
+        api.hgemm_ex(dA, dB, C, plan)
+    torch.cuda.synchronize()
+    assert api.last_device_error() == 0
+    assert torch.isfinite(C).all()
+    check_sampled_row_blocks(C, dA, dB.cpu().numpy(), (0, 8192 + 384, M - 128), f"16384^3 {plan_name}")
+
+
+def test_prefill_shape_sampled_rows(cuda_device):
+    """8192 x 28672 x 8192, activations ~ N(0,1), weights ~ N(0, 1/K)."""
+    import torch
+
+    M, N, K = 8192, 28672, 8192
+    dA, dB = device_inputs(M, N, K, "normal", 2024, cuda_device)
+    C = poisoned(M, N, cuda_device).view(M, N)
+    api.b200Hgemm(dA, dB, C)
+    torch.cuda.synchronize()
+    assert api.last_device_error() == 0
+    assert torch.isfinite(C).all()
+    check_sampled_row_blocks(C, dA, dB.cpu().numpy(), (0, 4096 - 128, M - 128), "prefill")
+
+
+@pytest.mark.parametrize("NK", [(14336, 4096), (4096, 14336)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("M", [16, 32, 64, 128])
+def test_decode_shapes_at_full_size(cuda_device, M, NK):
+    """The decode configurations at their true N and K, every row against the oracle, through the dispatch."""
+    import torch
+
+    N, K = NK
+    dA, dB = device_inputs(M, N, K, "normal", 2025 + M, cuda_device)
+    C = poisoned(M, N, cuda_device).view(M, N)
+    api.b200Hgemm(dA, dB, C)
+    torch.cuda.synchronize()
+    assert api.last_device_error() == 0
+    ref = oracle.gemm_f32(dA.cpu().numpy(), dB.cpu().numpy())
+    assert_close_to_oracle(C.cpu().numpy(), ref, f"decode {M}x{N}x{K} plan {api.select_plan(M, N, K).as_dict()}")

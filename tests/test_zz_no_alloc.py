@@ -7,10 +7,8 @@ point whose scratch (the FP32 partial tiles of split k-ranges) is a static 16 Mi
 This test calls it through the C ABI twice in a row -- the second call finds the array as the
 first one left it -- and compares each result with the ordinary stream-k entry point and with
 the CPU oracle, on the tolerance the other parity tests use. It also checks that the call
-really allocates nothing and that sizes beyond its stated maximum are refused.
-
-The file name sorts last on purpose: a run that stops at the first failure has then already
-run every other test.
+really allocates nothing, that sizes beyond its stated maximum are refused, and that a wait
+that expires inside it can be read back by the caller.
 """
 import numpy as np
 import pytest
@@ -58,6 +56,7 @@ def test_static_scratch_matches_stream_k_on_two_calls_in_a_row(cuda_device, shap
         if call == 1:
             # set-up (kernel attributes, module data) is behind us: nothing may have been allocated
             assert free_after == free_before
+        assert lib.b200_hgemm_streamk_static_last_error() == 0
         got = out.cpu().numpy()
         assert_close_to_oracle(got, ref, f"static call {call}")
         # same products and the same FP32 accumulation, grouped into a different number of k-ranges:
@@ -80,3 +79,26 @@ def test_static_scratch_refuses_what_does_not_fit(cuda_device):
     assert lib.b200_hgemm_streamk_static(p, p, p, 64, 64, 60, None) == _native.ERR_UNSUPPORTED
     assert lib.b200_hgemm_streamk_static(None, p, p, 64, 64, 64, None) == _native.ERR_INVALID_ARG
     torch.cuda.synchronize()
+
+
+def test_an_expired_wait_inside_the_static_variant_can_be_read_back(cuda_device):
+    """The static variant reports a bounded wait that ran out in the first word of its array; the caller reads
+    it with b200_hgemm_streamk_static_last_error(), which allocates nothing either. The expiry is produced
+    without any fault: one CTA waits 50 ms on a barrier that nothing arrives on."""
+    import torch
+
+    lib = _native.load()
+    assert lib.b200_hgemm_streamk_static_last_error() == 0
+    assert lib.b200_debug_wait_expiry_static(50, None) == _native.OK
+    assert lib.b200_hgemm_streamk_static_last_error() == 1   # reported once ...
+    assert lib.b200_hgemm_streamk_static_last_error() == 0   # ... and cleared
+    assert api.last_device_error() == 0                      # the other entry points' word is a different one
+    # the next call through the static variant starts clean and is correct
+    M, N, K = 128, 512, 1024
+    A, B = make_inputs(M, N, K, seed=22, dist="normal")
+    dA, dB = torch.from_numpy(A).to(cuda_device), torch.from_numpy(B).to(cuda_device)
+    out = torch.full((M, N), float("nan"), dtype=torch.float16, device=cuda_device)
+    assert call_static(lib, dA, dB, out, M, N, K) == _native.OK
+    torch.cuda.synchronize()
+    assert lib.b200_hgemm_streamk_static_last_error() == 0
+    assert_close_to_oracle(out.cpu().numpy(), oracle.gemm_f32(A, B), "static after an expired wait")
