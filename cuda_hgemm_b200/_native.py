@@ -43,6 +43,7 @@ VARIANT_SIMT = 3
 VARIANT_CTA2_MCAST = 4
 VARIANT_SKINNY = 5
 VARIANT_HYBRID = 6
+VARIANT_SKINNY_PAIR = 7
 
 MULTICAST_OFF, MULTICAST_ON, MULTICAST_LOCKED_OFF = 0, 1, 2
 

@@ -56,6 +56,22 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_SO
 
 
+TIMELINE_SO = LIB_DIR / "libb200_hgemm_timeline.so"
+
+
+def build_timeline(force: bool = False) -> Path:
+    """nvcc -DB200_TIMELINE -> lib/libb200_hgemm_timeline.so: the same library with per-CTA time stamps
+    (launch, set-up done, first load, first MMA, last store, exit) written to a buffer the caller hands over
+    with b200_debug_set_timeline(); used by ``python -m cuda_hgemm_b200.timeline`` only."""
+    if not force and _up_to_date(TIMELINE_SO, _lib_sources()):
+        return TIMELINE_SO
+    LIB_DIR.mkdir(exist_ok=True)
+    cmd = [nvcc(), *COMMON_FLAGS, "-DB200_TIMELINE", "--shared", "-Xcompiler", "-fPIC", "-cudart", "static",
+           "-o", str(TIMELINE_SO), *[str(s) for s in sorted(CSRC.glob("*.cu"))]]
+    subprocess.run(cmd, check=True)
+    return TIMELINE_SO
+
+
 def build_multicast(force: bool = False) -> Path | None:
     """nvcc -> lib/libb200_hgemm_mc.so, the single-GPU companion with the cluster-multicast kernel.
     Its source is not shipped to multi-GPU runs; without it there is nothing to build."""

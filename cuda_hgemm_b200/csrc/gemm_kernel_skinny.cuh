@@ -1,4 +1,4 @@
-// Kernel for a short A (M <= 64 rows): the weight matrix B streams through the MMA's row operand.
+// Kernel for a short A (M <= 128 rows): the weight matrix B streams through the MMA's row operand.
 //
 // C[M x N] = A[M x K] * B^T with M of a decode batch (16 ... 64 rows) is bound by reading B once from
 // HBM. hgemm_tcgen05_kernel puts A on the 128 rows of the MMA, so every k-block stages a 16 KB slab of
@@ -10,9 +10,24 @@
 // column operand (UMMA 128 x MT x 16), and the accumulator holds C transposed: tensor-memory lane = column
 // of C, tensor-memory column = row of C. A stage is two k-blocks (32 KB of B and 2 x MT x 128 B of A)
 // under one barrier round trip, six stages deep for MT = 16: twice the bytes of B in flight per SM and
-// 0.20 us of issue time per k-block. One CTA computes one (128-column tile, k-range) pair; when the tiles
+// 0.20 us of issue time per k-block. One CTA computes one (column tile, k-range) pair; when the tiles
 // are too few to fill the GPU (N = 4096: 32) the k-range is cut into equal slices whose FP32 partial
 // results go to a workspace and are summed by skinny_reduce_kernel, which follows in the stream.
+//
+// A column tile is tile_w <= 128 columns of C wide (a multiple of 8): the TMA box of B has tile_w rows,
+// the MMA still multiplies 128 rows of the stage's slab, and whatever lies in the rows the box did not
+// write only reaches tensor-memory lanes that are never read. The launcher picks the width that spreads
+// N over the SMs best: N = 14336 gives 112 tiles of 128 columns on 148 SMs, but 138 tiles of 104.
+//
+// CG = 2 runs a pair of CTAs (cta_group::2) on two neighbouring column tiles: every CTA stages its own
+// tile_w rows of B but only half of the rows of A, the leader issues MMAs of 256 x MT for both, and the
+// rows of A cross from L2 to an SM once per pair instead of once per CTA. With 65 ... 128 rows of A
+// that traffic is as large as B's own (a 16 KB slab of A beside at most 16 KB of B per k-block) and, not
+// HBM, bounds the single-CTA form; the pair form also leaves room for a deeper ring.
+//
+// The epilogue turns the accumulator (lane = column of C) back into rows of C in shared memory (the
+// ring's first stage: every MMA has retired by then) and writes the tile with one TMA store; when C
+// cannot have a tensor map (N % 8 != 0) or when FP32 partials are wanted it stores by element.
 //
 // Operand layouts, swizzle, bounded waits and the error word are those of hgemm_tcgen05_kernel
 // (gemm_kernel.cuh); the reference has no counterpart (its kernels tile every shape alike,
@@ -24,25 +39,34 @@
 namespace b200 {
 
 struct alignas(64) SkinnyParams {
-    CUtensorMap tm_w;  // B as {K, N}, box {64, 128}
-    CUtensorMap tm_x;  // A as {K, M}, box {64, MT}
+    CUtensorMap tm_w;  // B as {K, N}, box {64, tile_w}, 128-byte swizzle
+    CUtensorMap tm_x;  // A as {K, M}, box {64, MT / CG}, 128-byte swizzle
+    CUtensorMap tm_c;  // C as {N, M}, box {tile_w, MT}, no swizzle (only valid when tma_store != 0)
     __half *c;
     float *partials;  // slices x MT x n_pad FP32, used when slices > 1
     uint32_t *error_word;
     uint32_t m, n, k;
     uint32_t k_blocks;
-    uint32_t n_tiles;        // 128-column tiles of C
+    uint32_t n_tiles;        // column tiles of C (even for pairs: a tile past N reads zeros and stores nothing)
+    uint32_t tile_w;         // columns of C per tile: a multiple of 8, at most 128 (= rows of the TMA box of B)
     uint32_t slices;         // k-ranges per tile
     uint32_t kb_per_slice;   // k-blocks per k-range (the last one may be shorter, never empty)
     uint32_t n_pad;          // row pitch of the partial results, in floats
+    uint32_t tma_store;      // 1: whole results leave through tm_c
+    uint32_t prefetch_kb;    // k-blocks of B asked into L2 before waiting for the previous kernel
+#ifdef B200_TIMELINE
+    unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
+#endif
 };
 
-template <int MT, int STAGES, int KPS>
+template <int MT, int STAGES, int KPS, int CG = 1>
 struct SkinnyTraits {
-    static_assert(MT == 16 || MT == 32 || MT == 64, "rows of A per tile");
+    static_assert(MT == 16 || MT == 32 || MT == 64 || MT == 128, "rows of A per tile");
     static_assert(KPS == 1 || KPS == 2, "k-blocks per stage");
+    static_assert(CG == 1 || CG == 2, "single CTAs or CTA pairs");
     static constexpr uint32_t kWBytes = 128 * kBK * 2;
-    static constexpr uint32_t kXBytes = MT * kBK * 2;
+    static constexpr uint32_t kXRows = MT / CG;  // rows of A this CTA stages
+    static constexpr uint32_t kXBytes = kXRows * kBK * 2;
     static constexpr uint32_t kBlockBytes = kWBytes + kXBytes;
     static constexpr uint32_t kStageBytes = KPS * kBlockBytes;
     static constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
@@ -50,11 +74,12 @@ struct SkinnyTraits {
     static_assert((kBlockBytes % 1024) == 0, "operand slabs must keep 1024-byte alignment");
     static_assert(kSmemBytes <= 232448, "exceeds 227 KB of shared memory");
     static_assert((2 * STAGES + 1) * 8 + 16 <= 256, "barrier area too small");
+    static_assert(STAGES * kStageBytes >= MT * 128 * 2, "the ring must hold one tile of C for the epilogue");
 };
 
-template <int MT, int STAGES, int KPS>
+template <int MT, int STAGES, int KPS, int CG = 1>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_constant__ SkinnyParams p) {
-    using T = SkinnyTraits<MT, STAGES, KPS>;
+    using T = SkinnyTraits<MT, STAGES, KPS, CG>;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -70,12 +95,15 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t cta_rank = (CG == 2) ? cluster_cta_rank() : 0u;
+    // consecutive CTAs take consecutive column tiles (the two CTAs of a pair: tiles 2i and 2i + 1 of one k-range)
     const uint32_t tile = blockIdx.x % p.n_tiles;
     const uint32_t slice = blockIdx.x / p.n_tiles;
     const uint32_t kb0 = slice * p.kb_per_slice;
     const uint32_t kb1 = min(p.k_blocks, kb0 + p.kb_per_slice);
-    const uint32_t n0 = tile * 128u;
+    const uint32_t n0 = tile * p.tile_w;
 
+    if (threadIdx.x == 0) B200_STAMP(0);
     if (warp == 0) {
         if (lane < static_cast<uint32_t>(STAGES)) {
             mbar_init(full_bar + 8u * lane, 1);
@@ -91,52 +119,82 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
     if (warp == 2 && lane == 0) {
         tma_prefetch_desc(&p.tm_w);
         tma_prefetch_desc(&p.tm_x);
+        if (p.tma_store) tma_prefetch_desc(&p.tm_c);
     }
     if (warp == 1) {
-        tmem_alloc<1>(smem_u32(const_cast<uint32_t *>(tmem_slot)), T::kTmemCols);
-        tmem_relinquish<1>();
+        tmem_alloc<CG>(smem_u32(const_cast<uint32_t *>(tmem_slot)), T::kTmemCols);
+        tmem_relinquish<CG>();
     }
     tcgen05_fence_before_sync();
-    // The producer warp initialised the barriers itself and needs no tensor memory: it only
-    // announces its arrival and starts loading while the allocation completes.
-    if (warp == 0) {
-        __threadfence_block();
-        named_bar_arrive(2, kThreads);
+    if (CG == 2) {
+        // the peer's copies and arrivals target this CTA's barriers: both CTAs must have set up
+        __syncthreads();
+        cluster_sync_all();
     } else {
-        named_bar_sync(2, kThreads);
+        // The producer warp initialised the barriers itself and needs no tensor memory: it only
+        // announces its arrival and starts loading while the allocation completes.
+        if (warp == 0) {
+            __threadfence_block();
+            named_bar_arrive(2, kThreads);
+        } else {
+            named_bar_sync(2, kThreads);
+        }
     }
     tcgen05_fence_after_sync();
-    const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
+    const uint32_t tmem_base = (CG == 1 && warp == 0) ? 0u : *tmem_slot;
     pdl_launch_dependents();
+    if (threadIdx.x == 0) B200_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
+            const uint32_t block_tx = p.tile_w * kBK * 2u + T::kXBytes;  // bytes one CTA stages per k-block
+            const int32_t row_x = static_cast<int32_t>(cta_rank * T::kXRows);
+            // While the previous kernel in the stream finishes, ask L2 for the first k-blocks of this tile's
+            // rows of B: the kernel is bound by HBM and the previous one's last CTAs leave it idle. Only a
+            // hint -- nothing is read into the SM before the wait below.
+            for (uint32_t kb = kb0; kb < kb1 && kb < kb0 + p.prefetch_kb; ++kb) {
+                tma_prefetch_l2_2d(&p.tm_w, static_cast<int32_t>(kb * kBK), static_cast<int32_t>(n0));
+            }
             pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
+            B200_STAMP(2);
             for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
                 if (!mbar_wait(empty_bar + 8u * stage, phase ^ 1u, abort_flag)) break;
                 const uint32_t slot = base + stage * T::kStageBytes;
                 // a k-block past the end of this k-range is not loaded; its share of the stage is not waited for
                 const uint32_t blocks = min(static_cast<uint32_t>(KPS), kb1 - kb);
-                mbar_arrive_expect_tx(full_bar + 8u * stage, blocks * T::kBlockBytes);
-                for (uint32_t j = 0; j < blocks; ++j) {
-                    const uint32_t sw = slot + j * T::kBlockBytes;
-                    const int32_t kx = static_cast<int32_t>((kb + j) * kBK);
-                    tma_load_2d(sw, &p.tm_w, kx, static_cast<int32_t>(n0), full_bar + 8u * stage);
-                    tma_load_2d(sw + T::kWBytes, &p.tm_x, kx, 0, full_bar + 8u * stage);
+                if (CG == 1) {
+                    mbar_arrive_expect_tx(full_bar + 8u * stage, blocks * block_tx);
+                    for (uint32_t j = 0; j < blocks; ++j) {
+                        const uint32_t sw = slot + j * T::kBlockBytes;
+                        const int32_t kx = static_cast<int32_t>((kb + j) * kBK);
+                        tma_load_2d(sw, &p.tm_w, kx, static_cast<int32_t>(n0), full_bar + 8u * stage);
+                        tma_load_2d(sw + T::kWBytes, &p.tm_x, kx, 0, full_bar + 8u * stage);
+                    }
+                } else {
+                    // both CTAs' copies complete on the leader's barrier; the leader posts the byte count of the pair
+                    if (cta_rank == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * blocks * block_tx);
+                    const uint32_t leader_bar = map_to_cta(full_bar + 8u * stage, 0);
+                    for (uint32_t j = 0; j < blocks; ++j) {
+                        const uint32_t sw = slot + j * T::kBlockBytes;
+                        const int32_t kx = static_cast<int32_t>((kb + j) * kBK);
+                        tma_load_2d_pair(sw, &p.tm_w, kx, static_cast<int32_t>(n0), leader_bar);
+                        tma_load_2d_pair(sw + T::kWBytes, &p.tm_x, kx, row_x, leader_bar);
+                    }
                 }
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
             }
+            B200_STAMP(3);
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_f16_f32(128, MT);
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16_f32(128 * CG, MT);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
@@ -145,6 +203,9 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
                     break;
                 }
                 tcgen05_fence_after_sync();
+#ifdef B200_TIMELINE
+                if (kb == kb0) B200_STAMP(4);
+#endif
                 const uint32_t slot = base + stage * T::kStageBytes;
                 const uint32_t blocks = min(static_cast<uint32_t>(KPS), kb1 - kb);
                 for (uint32_t j = 0; j < blocks; ++j) {
@@ -152,36 +213,62 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
                     const uint64_t dx = umma_smem_desc_sw128(slot + j * T::kBlockBytes + T::kWBytes);
 #pragma unroll
                     for (uint32_t k = 0; k < kBK / 16; ++k) {
-                        umma_f16<1>(tmem_base, dw + 2u * k, dx + 2u * k, idesc, (kb > kb0 || j > 0 || k > 0) ? 1u : 0u);
+                        umma_f16<CG>(tmem_base, dw + 2u * k, dx + 2u * k, idesc, (kb > kb0 || j > 0 || k > 0) ? 1u : 0u);
                     }
                 }
-                umma_commit(empty_bar + 8u * stage);
+                if (CG == 1) {
+                    umma_commit(empty_bar + 8u * stage);
+                } else {
+                    umma_commit_pair(empty_bar + 8u * stage, 0x3);
+                }
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
             }
-            if (ok) umma_commit(tfull_bar);
+            if (ok) {
+                if (CG == 1) {
+                    umma_commit(tfull_bar);
+                } else {
+                    umma_commit_pair(tfull_bar, 0x3);
+                }
+            }
+            B200_STAMP(5);
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ epilogue
         // lane of tensor memory = column of C (n), column of tensor memory = row of C (m)
         const uint32_t q = warp & 3u;
-        const uint32_t n = n0 + q * 32u + lane;
+        const uint32_t col_in_tile = q * 32u + lane;
+        const uint32_t n = n0 + col_in_tile;
+        const bool col_live = n < p.n && col_in_tile < p.tile_w;
+        const bool staged = p.slices == 1 && p.tma_store != 0;  // whole results, through shared memory and one TMA store
         pdl_wait_prior_grids();  // C (or the workspace) may still be read by the previous kernel
         uint32_t ready = 1;
         if (lane == 0) ready = mbar_wait(tfull_bar, 0, abort_flag) ? 1u : 0u;
         ready = __shfl_sync(0xffffffffu, ready, 0);
         if (ready) {
             tcgen05_fence_after_sync();
+            if (threadIdx.x == 64) B200_STAMP(6);
             const uint32_t taddr = tmem_base + ((q * 32u) << 16);
+            // every MMA has retired and with it every read of the ring: its first bytes now hold the tile of C,
+            // row-major [MT][tile_w] halves
+            __half *tile_c = reinterpret_cast<__half *>(base_ptr);
 #pragma unroll
             for (uint32_t c = 0; c < MT / 16; ++c) {
                 uint32_t r[16];
                 tmem_ld_32x32b_x16(taddr + c * 16u, r);
                 tmem_ld_wait();
-                if (n < p.n) {
+                if (staged) {
+                    if (col_in_tile < p.tile_w) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; ++j) {
+                            // 32 lanes write 32 consecutive halves of one row of the tile
+                            tile_c[(c * 16u + j) * p.tile_w + col_in_tile] = __float2half_rn(__uint_as_float(r[j]));
+                        }
+                    }
+                } else if (col_live) {
                     if (p.slices == 1) {
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
@@ -200,6 +287,18 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
                 }
             }
         }
+        if (staged) {
+            // all four warps have written their columns (a warp that gave up still arrives): one TMA store
+            // of tile_w x MT; rows past M and columns past N are clipped by the tensor map
+            fence_proxy_async_smem();
+            named_bar_sync(3, kEpiThreads);
+            if (threadIdx.x == 64 && ready && *abort_flag == 0 && n0 < p.n) {
+                tma_store_2d(&p.tm_c, base, static_cast<int32_t>(n0), 0);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+            }
+        }
+        if (threadIdx.x == 64) B200_STAMP(8);
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -213,10 +312,12 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
         if (threadIdx.x == 0) atomicExch(p.error_word, static_cast<uint32_t>(kDevWaitTimeout));
         __syncthreads();
     }
+    if (CG == 2) cluster_sync_all();
     if (warp == 1) {
         tcgen05_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, T::kTmemCols);
+        tmem_dealloc<CG>(tmem_base, T::kTmemCols);
     }
+    if (threadIdx.x == 32) B200_STAMP(10);
 }
 
 constexpr int kSkinnyReduceThreads = 256;

@@ -38,16 +38,20 @@ struct TensorMapKey {
     const void *ptr;
     uint64_t rows, cols;
     uint32_t box_rows, box_cols;
+    bool swizzle;
     bool operator==(const TensorMapKey &o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols;
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+               swizzle == o.swizzle;
     }
 };
 
 struct TensorMapSlot {
     bool used = false;
+    uint64_t last_use = 0;
     TensorMapKey key{};
     CUtensorMap map{};
 };
+constexpr size_t kTensorMapWays = 4;
 
 struct DeviceState {
     std::mutex mu;
@@ -76,7 +80,8 @@ struct DeviceState {
     cudaEvent_t host_event[2] = {nullptr, nullptr};
     bool attr_set[32] = {};
     int max_clusters[32] = {};  // CTA pairs the device can keep resident at once, per pair kernel
-    TensorMapSlot tm_cache[64];
+    TensorMapSlot tm_cache[64 * kTensorMapWays];
+    uint64_t tm_clock = 0;
 };
 
 static DeviceState g_dev[kMaxDevices];
@@ -157,19 +162,26 @@ static int current_state(DeviceState **out) {
 }
 
 // A 2-D FP16 tensor of `rows` x `cols` (cols contiguous) viewed through boxes of
-// box_rows x box_cols with the 128-byte swizzle. Out-of-range elements read as zero and
-// are dropped on store.
+// box_rows x box_cols, with the 128-byte swizzle (box_cols = 64) or, for plain row-major staging
+// tiles, without. Out-of-range elements read as zero and are dropped on store. The cache is 4-way
+// set-associative (64 sets): a handful of operands in rotation never evict each other.
 static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                          uint32_t box_cols, CUtensorMap *out) {
-    TensorMapKey key{ptr, rows, cols, box_rows, box_cols};
+                          uint32_t box_cols, CUtensorMap *out, bool swizzle = true) {
+    TensorMapKey key{ptr, rows, cols, box_rows, box_cols, swizzle};
     size_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
-    h ^= rows * 0xC2B2AE3D27D4EB4Full + cols * 0x165667B19E3779F9ull + box_rows * 131u + box_cols;
-    const size_t idx = (h >> 20) & 63u;
+    h ^= rows * 0xC2B2AE3D27D4EB4Full + cols * 0x165667B19E3779F9ull + box_rows * 131u + box_cols + (swizzle ? 0u : 77u);
+    const size_t set = ((h >> 20) & 63u) * kTensorMapWays;
     std::lock_guard<std::mutex> lock(st.mu);
-    TensorMapSlot &slot = st.tm_cache[idx];
-    if (slot.used && slot.key == key) {
-        *out = slot.map;
-        return B200_HGEMM_OK;
+    TensorMapSlot *slot = nullptr;
+    for (size_t w = 0; w < kTensorMapWays; ++w) {
+        TensorMapSlot &cand = st.tm_cache[set + w];
+        if (cand.used && cand.key == key) {
+            cand.last_use = ++st.tm_clock;
+            *out = cand.map;
+            return B200_HGEMM_OK;
+        }
+        // the victim, should there be no hit: a free way, else the one used longest ago
+        if (!slot || (slot->used && (!cand.used || cand.last_use < slot->last_use))) slot = &cand;
     }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return B200_HGEMM_ERR_CUDA;
@@ -177,17 +189,18 @@ static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint6
     cuuint64_t strides[1] = {cols * sizeof(__half)};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t elem_strides[2] = {1, 1};
-    CUresult r = enc(&slot.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box,
-                     elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    CUresult r = enc(&slot->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box,
+                     elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        slot.used = false;
+        slot->used = false;
         if (getenv("B200_HGEMM_DEBUG")) fprintf(stderr, "[b200_hgemm] cuTensorMapEncodeTiled failed: CUresult %d\n", static_cast<int>(r));
         return B200_HGEMM_ERR_CUDA;
     }
-    slot.used = true;
-    slot.key = key;
-    *out = slot.map;
+    slot->used = true;
+    slot->key = key;
+    slot->last_use = ++st.tm_clock;
+    *out = slot->map;
     return B200_HGEMM_OK;
 }
 
@@ -290,15 +303,18 @@ static bool plan_cuts_k(const b200_hgemm_plan &pl) {
 
 static bool plan_is_tensor(const b200_hgemm_plan &pl) {
     return pl.variant == B200_VARIANT_CTA1 || pl.variant == B200_VARIANT_CTA2 || plan_cuts_k(pl) ||
-           pl.variant == B200_VARIANT_CTA2_MCAST || pl.variant == B200_VARIANT_SKINNY;
+           pl.variant == B200_VARIANT_CTA2_MCAST || pl.variant == B200_VARIANT_SKINNY ||
+           pl.variant == B200_VARIANT_SKINNY_PAIR;
 }
 
 static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     if (pl.variant == B200_VARIANT_SIMT) return B200_HGEMM_OK;
     if (!plan_is_tensor(pl)) return B200_HGEMM_ERR_UNSUPPORTED;
-    if (pl.variant == B200_VARIANT_SKINNY) {
+    if (pl.variant == B200_VARIANT_SKINNY || pl.variant == B200_VARIANT_SKINNY_PAIR) {
         // bn is the number of rows of A a tile holds (M may not exceed it; checked where M is known)
-        if (pl.bn != 16 && pl.bn != 32 && pl.bn != 64) return B200_HGEMM_ERR_UNSUPPORTED;
+        if (pl.bn != 16 && pl.bn != 32 && pl.bn != 64 && pl.bn != 128) return B200_HGEMM_ERR_UNSUPPORTED;
+        // group_m is the width of a column tile here: a multiple of 8 from 8 to 128, or 0 for the library's choice
+        if (pl.group_m != 0 && (pl.group_m < 8 || pl.group_m > 128 || pl.group_m % 8 != 0)) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.variant == B200_VARIANT_CTA2_MCAST) {
         // bn names the CTA arrangement here: 256 = 128 x 256 per CTA, 512 = 256 x 256 per CTA
         if ((pl.bn != 256 && pl.bn != 512) || N % 8 != 0 || !mc_launch_fn(pl.bn)) return B200_HGEMM_ERR_UNSUPPORTED;
@@ -313,7 +329,8 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     }
     if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 64) return B200_HGEMM_ERR_UNSUPPORTED;
     if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
-    if (pl.tma_store && N % 8 != 0 && pl.variant != B200_VARIANT_SKINNY) return B200_HGEMM_ERR_UNSUPPORTED;  // (that kernel stores by element)
+    const bool short_a = pl.variant == B200_VARIANT_SKINNY || pl.variant == B200_VARIANT_SKINNY_PAIR;
+    if (pl.tma_store && N % 8 != 0 && !short_a) return B200_HGEMM_ERR_UNSUPPORTED;  // (the short-A kernels then store by element)
     if (pl.parts < 0 || pl.group_m < 0 || pl.grid < 0) return B200_HGEMM_ERR_INVALID_ARG;
     return B200_HGEMM_OK;
 }
@@ -408,7 +425,10 @@ static bool tuned_plan(size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
     for (const TunedPlan &t : g_table) {
         if (t.m == M && t.n == N && t.k == K) {
             if (validate_plan(t.plan, N, K) != B200_HGEMM_OK) return false;
-            if (t.plan.variant == B200_VARIANT_SKINNY && M > static_cast<size_t>(t.plan.bn)) return false;
+            if ((t.plan.variant == B200_VARIANT_SKINNY || t.plan.variant == B200_VARIANT_SKINNY_PAIR) &&
+                M > static_cast<size_t>(t.plan.bn)) {
+                return false;
+            }
             *pl = t.plan;
             return true;
         }
@@ -419,8 +439,9 @@ static bool tuned_plan(size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
 // Shape -> plan, from measurements on B200 (square sizes 256..16384 in both timing protocols of
 // abtest.py, the decode shapes, the prefill shape):
 //  * M <= 64: the short-A kernel (B on the MMA's row operand);
-//  * 65 <= M <= 128 (decode-like, HBM-bound): whole 128-wide tiles when they cover most SMs, else equal
-//    k-ranges over all SMs with the FP32 workspace reduce;
+//  * 65 <= M <= 128 (decode-like, HBM-bound): the short-A kernel on CTA pairs when B is large; for small
+//    problems whole 128-wide tiles when they cover most SMs, else equal k-ranges over all SMs with the
+//    FP32 workspace reduce;
 //  * two or more full waves of CTA pairs on 256 x 256 tiles: those pairs, or - for long runs with long
 //    k - 256 x 256 outputs per CTA (pairs on 512 x 256, groups of four on 512 x 512 with A multicast),
 //    whichever fills its waves best after what the larger tiles gain under the power cap;
@@ -447,6 +468,14 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         // +18 % at M = 16, +10 % at M = 64)
         pl->variant = B200_VARIANT_SKINNY;
         pl->bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        return;
+    }
+    if (M <= 128 && N >= 2048 && K >= 1024) {
+        // 65 ... 128 rows against a large weight matrix: the short-A kernel on CTA pairs, which fetch the rows
+        // of A once per pair (measured at N = 14336, K = 4096, M = 128: 26.3 us against 28.0 for 128-row tiles
+        // of single CTAs; at N = 4096, K = 14336 with four k-ranges: 30.6 against 33.7 for stream-k)
+        pl->variant = B200_VARIANT_SKINNY_PAIR;
+        pl->bn = 128;
         return;
     }
     if (M <= 128) {
@@ -779,9 +808,30 @@ static int run_simt(const void *A, const void *B, void *C, size_t M, size_t N, s
     return B200_HGEMM_OK;
 }
 
-// ---- short A (M <= 64): B streams through the MMA's row operand (gemm_kernel_skinny.cuh) ----
+// ---- short A (M <= 128): B streams through the MMA's row operand (gemm_kernel_skinny.cuh) ----
+// Width of a column tile, in columns of C. Every CTA streams the tile's rows of B over its whole
+// k-range, so the kernel takes as long as its busiest SM: waves x width is what to minimise. 128
+// columns give N = 14336 112 tiles for 148 SMs; 104 give it 138. Below 64 columns the MMAs (always
+// 128 rows tall) would cost more issue time than the narrower tile saves; when k is cut into slices
+// the tiles stay 128 wide.
+static uint32_t skinny_tile_w(const b200_hgemm_plan &pl, const DeviceState &st, size_t N) {
+    if (pl.group_m > 0) return static_cast<uint32_t>(pl.group_m);
+    const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
+    if (pl.parts > 1 || ceil_div_u32(N, 128) * 5 < sms * 3) return 128u;  // few tiles: k is cut instead
+    uint32_t best_w = 128u;
+    uint64_t best_cost = static_cast<uint64_t>(ceil_div_u32(ceil_div_u32(N, 128), sms)) * 128u;
+    for (uint32_t w = 120; w >= 64; w -= 8) {
+        const uint64_t cost = static_cast<uint64_t>(ceil_div_u32(ceil_div_u32(N, w), sms)) * w;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best_w = w;
+        }
+    }
+    return best_w;
+}
+
 static uint32_t skinny_slices(const b200_hgemm_plan &pl, const DeviceState &st, size_t N, size_t K) {
-    const uint32_t tiles = ceil_div_u32(N, 128);
+    const uint32_t tiles = ceil_div_u32(N, skinny_tile_w(pl, st, N));
     const uint32_t k_blocks = ceil_div_u32(K, 64);
     const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
     uint32_t slices = pl.parts > 0 ? static_cast<uint32_t>(pl.parts) : 0u;
@@ -804,10 +854,22 @@ static size_t skinny_workspace_bytes(const b200_hgemm_plan &pl, const DeviceStat
     return static_cast<size_t>(slices) * pl.bn * n_pad * sizeof(float);
 }
 
-template <int MT, int STAGES, int KPS>
+// k-blocks of B a short-A CTA asks into L2 before it waits for the previous kernel (B200_HGEMM_SKINNY_PREFETCH
+// overrides it for measurements; 0 switches the prefetch off). Without programmatic dependent launch there
+// is no previous kernel to overlap with.
+static uint32_t skinny_prefetch_kb() {
+    static const uint32_t kb = []() -> uint32_t {
+        if (!pdl_enabled()) return 0u;
+        const char *v = getenv("B200_HGEMM_SKINNY_PREFETCH");
+        return v ? static_cast<uint32_t>(atoi(v)) : 8u;  // measured: 8 k-blocks -4 % at M = 16 ... 64; 32 and more lose
+    }();
+    return kb;
+}
+
+template <int MT, int STAGES, int KPS, int CG = 1>
 static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream) {
-    using T = SkinnyTraits<MT, STAGES, KPS>;
-    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS>;
+    using T = SkinnyTraits<MT, STAGES, KPS, CG>;
+    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS, CG>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -823,11 +885,22 @@ static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, 
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = T::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchAttribute attrs[2];
+    int n_attrs = 0;
+    if (pdl_enabled()) {
+        attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attrs;
+    }
+    if (CG == 2) {  // the grid is a whole number of pairs (n_tiles is even)
+        attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[n_attrs].val.clusterDim.x = 2;
+        attrs[n_attrs].val.clusterDim.y = 1;
+        attrs[n_attrs].val.clusterDim.z = 1;
+        ++n_attrs;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n_attrs;
     if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, p), "cudaLaunchKernelEx")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
@@ -848,15 +921,29 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     p.n = static_cast<uint32_t>(N);
     p.k = static_cast<uint32_t>(K);
     p.k_blocks = ceil_div_u32(K, 64);
-    p.n_tiles = ceil_div_u32(N, 128);
+    const bool pairs = pl.variant == B200_VARIANT_SKINNY_PAIR;
+    p.tile_w = skinny_tile_w(pl, st, N);
+    p.n_tiles = ceil_div_u32(N, p.tile_w);
+    if (pairs) p.n_tiles += p.n_tiles & 1u;  // a pair's second tile may lie past N: it reads zeros and stores nothing
     p.slices = skinny_slices(pl, st, N, K);
     p.kb_per_slice = ceil_div_u32(p.k_blocks, p.slices);
     p.n_pad = static_cast<uint32_t>((N + 31) / 32 * 32);
+    p.prefetch_kb = skinny_prefetch_kb();
+#ifdef B200_TIMELINE
+    p.timeline = g_timeline;
+#endif
     if (static_cast<uint64_t>(p.n_tiles) * p.slices > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
-    int rc = get_tensor_map(st, B, N, K, 128, 64, &p.tm_w);
+    int rc = get_tensor_map(st, B, N, K, p.tile_w, 64, &p.tm_w);
     if (rc != B200_HGEMM_OK) return rc;
-    rc = get_tensor_map(st, A, M, K, static_cast<uint32_t>(pl.bn), 64, &p.tm_x);
+    rc = get_tensor_map(st, A, M, K, static_cast<uint32_t>(pl.bn) / (pairs ? 2u : 1u), 64, &p.tm_x);
     if (rc != B200_HGEMM_OK) return rc;
+    // whole results leave through one TMA store per tile (a plain row-major box of tile_w x bn) when C can
+    // have a tensor map: rows of N halves must be a multiple of 16 bytes
+    p.tma_store = (pl.tma_store && N % 8 == 0 && p.slices == 1) ? 1u : 0u;
+    if (p.tma_store) {
+        rc = get_tensor_map(st, C, M, N, static_cast<uint32_t>(pl.bn), p.tile_w, &p.tm_c, false);
+        if (rc != B200_HGEMM_OK) return rc;
+    }
     if (p.slices > 1) {
         const size_t need = skinny_workspace_bytes(pl, st, N, K);
         uint8_t *ws = nullptr;
@@ -869,12 +956,24 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
         }
         p.partials = reinterpret_cast<float *>(ws);
     }
-    if (pl.bn == 16) {
+    if (pairs) {
+        if (pl.bn == 16) {
+            rc = launch_skinny<16, 6, 2, 2>(st, 21, p, stream);
+        } else if (pl.bn == 32) {
+            rc = launch_skinny<32, 6, 2, 2>(st, 22, p, stream);
+        } else if (pl.bn == 64) {
+            rc = launch_skinny<64, 5, 2, 2>(st, 23, p, stream);
+        } else {
+            rc = launch_skinny<128, 4, 2, 2>(st, 24, p, stream);
+        }
+    } else if (pl.bn == 16) {
         rc = launch_skinny<16, 6, 2>(st, 11, p, stream);
     } else if (pl.bn == 32) {
         rc = launch_skinny<32, 5, 2>(st, 12, p, stream);
-    } else {
+    } else if (pl.bn == 64) {
         rc = launch_skinny<64, 4, 2>(st, 13, p, stream);
+    } else {
+        rc = launch_skinny<128, 3, 2>(st, 14, p, stream);
     }
     if (rc != B200_HGEMM_OK || p.slices == 1) return rc;
     cudaLaunchConfig_t cfg;
@@ -912,7 +1011,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u) {
         return B200_HGEMM_ERR_MISALIGNED;
     }
-    if (pl.variant == B200_VARIANT_SKINNY) {
+    if (pl.variant == B200_VARIANT_SKINNY || pl.variant == B200_VARIANT_SKINNY_PAIR) {
         return run_skinny(st, A, B, C, M, N, K, pl, stream, ws_override, ws_override_bytes,
                           error_word_override ? error_word_override : st.error_word);
     }
@@ -1326,6 +1425,7 @@ static int fused_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_
             pl->bn = 256;
             break;
         case B200_VARIANT_SKINNY:
+        case B200_VARIANT_SKINNY_PAIR:
             pl->variant = B200_VARIANT_CTA1;
             pl->bn = ceil_div_u32(N, 128) * 2 >= sms ? 128 : 64;
             break;
@@ -1384,7 +1484,9 @@ int b200_hgemm_plan_supported(size_t M, size_t N, size_t K, const b200_hgemm_pla
     if (!plan || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
     const int rc = validate_plan(*plan, N, K);
     if (rc != B200_HGEMM_OK) return rc;
-    if (plan->variant == B200_VARIANT_SKINNY && M > static_cast<size_t>(plan->bn)) return B200_HGEMM_ERR_UNSUPPORTED;
+    if ((plan->variant == B200_VARIANT_SKINNY || plan->variant == B200_VARIANT_SKINNY_PAIR) && M > static_cast<size_t>(plan->bn)) {
+        return B200_HGEMM_ERR_UNSUPPORTED;
+    }
     return B200_HGEMM_OK;
 }
 
@@ -1414,8 +1516,8 @@ int b200_hgemm_select_untuned(size_t M, size_t N, size_t K, b200_hgemm_plan *pla
 
 size_t b200_hgemm_workspace_bytes(size_t M, size_t N, size_t K, const b200_hgemm_plan *plan) {
     if (!plan || M == 0 || N == 0 || K == 0) return 0;
-    if (plan->variant == B200_VARIANT_SKINNY) {
-        if (plan->bn != 16 && plan->bn != 32 && plan->bn != 64) return 0;
+    if (plan->variant == B200_VARIANT_SKINNY || plan->variant == B200_VARIANT_SKINNY_PAIR) {
+        if (validate_plan(*plan, N, K) != B200_HGEMM_OK) return 0;
         DeviceState *st = nullptr;
         if (current_state(&st) != B200_HGEMM_OK) {
             cudaGetLastError();

@@ -78,6 +78,29 @@ extern "C" double hgemm_compare_time_loop(hgemm_entry_fn fn, const void *A, cons
     cudaEventDestroy(e1);
     return result;
 }
+
+// The same with the B operand taken in turn from `n_b` buffers (call i uses Bs[i % n_b]): for shapes
+// whose B would otherwise be served from L2 on every call after the first (the decode shapes: B is
+// about as large as L2). `warmup` calls run first, untimed.
+extern "C" double hgemm_compare_time_loop_rotate(hgemm_entry_fn fn, const void *A, const void *const *Bs, int n_b, void *C,
+                                                 size_t M, size_t N, size_t K, int warmup, int iters, void *stream) {
+    if (n_b < 1) return -1.0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return -1.0;
+    double result = -1.0;
+    bool ok = true;
+    int turn = 0;
+    for (int i = 0; i < warmup && ok; ++i, ++turn) ok = fn(A, Bs[turn % n_b], C, M, N, K, stream) == 0;
+    ok = ok && cudaEventRecord(e0, s) == cudaSuccess;
+    for (int i = 0; i < iters && ok; ++i, ++turn) ok = fn(A, Bs[turn % n_b], C, M, N, K, stream) == 0;
+    ok = ok && cudaEventRecord(e1, s) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+    float ms = 0.f;
+    if (ok && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess && iters > 0) result = static_cast<double>(ms) / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return result;
+}
 #else
 void cublasTensorOp(half *A, half *B, half *C, size_t M, size_t N, size_t K) {
     HGEMM_CHECK_CUBLAS_ERROR(gemm_fp16_compute(nullptr, A, B, C, M, N, K));

@@ -190,6 +190,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// Asks for one box to be brought into L2 (no shared-memory destination, no barrier). A hint: data that
+// is rewritten afterwards is simply read again from L2, the point of coherence, by the load that follows.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *tm, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y)
+                 : "memory");
+}
+
 // Pair-CTA form: the destination is this CTA's shared memory, the barrier may live in the
 // peer CTA of the pair (cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap *tm, int32_t x, int32_t y,

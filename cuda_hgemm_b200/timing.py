@@ -100,6 +100,9 @@ def load_compare():
         fn.restype = ctypes.c_int
     lib.hgemm_compare_time_loop.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_size_t] * 3 + [ctypes.c_int] * 2 + [ctypes.c_void_p]
     lib.hgemm_compare_time_loop.restype = ctypes.c_double
+    lib.hgemm_compare_time_loop_rotate.argtypes = ([ctypes.c_void_p] * 2 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                                   ctypes.c_void_p] + [ctypes.c_size_t] * 3 + [ctypes.c_int] * 2 + [ctypes.c_void_p])
+    lib.hgemm_compare_time_loop_rotate.restype = ctypes.c_double
     return lib
 
 
@@ -129,3 +132,18 @@ def cublas_callable(torch, lib, which, A, B, C):
     return call
 
 
+
+
+def time_native_rotate(torch, cmp_lib, entry, A, Bs, C, warmup=50, iters=200):
+    """Mean ms per call of a C-ABI GEMM entry point launched back to back from native code, B taken in turn
+    from the list ``Bs`` (copies of one matrix, together several times the L2) so that no call finds B cached.
+    ``warmup`` untimed calls come first: enough of them to settle the clocks of a kernel of tens of microseconds."""
+    M, K = A.shape
+    N = Bs[0].shape[0]
+    fn_ptr = ctypes.cast(entry, ctypes.c_void_p)
+    ptrs = (ctypes.c_void_p * len(Bs))(*[b.data_ptr() for b in Bs])
+    ms = cmp_lib.hgemm_compare_time_loop_rotate(fn_ptr, A.data_ptr(), ptrs, len(Bs), C.data_ptr(), M, N, K, warmup, iters,
+                                                torch.cuda.current_stream().cuda_stream)
+    if ms <= 0:
+        raise RuntimeError("native timing loop failed")
+    return ms

@@ -55,12 +55,15 @@ enum {
                                    which the library opens after b200_hgemm_enable_multicast(1)
                                    (B200_HGEMM_ERR_UNSUPPORTED otherwise); needs N % 8 == 0; A, B and C must be
                                    allocations of the GPU the call runs on */
-    B200_VARIANT_SKINNY = 5,     /* M <= 64 (decode batches): B streams through the MMA's row operand and C is
-                                   accumulated transposed; plan.bn = rows of A per tile (16, 32 or 64, >= M),
+    B200_VARIANT_SKINNY = 5,     /* M <= 128 (decode batches): B streams through the MMA's row operand and C is
+                                   accumulated transposed; plan.bn = rows of A per tile (16, 32, 64 or 128, >= M),
                                    plan.parts = equal k-ranges per column tile (0 = library's choice), summed
-                                   from an FP32 workspace when there is more than one */
-    B200_VARIANT_HYBRID = 6      /* as STREAMK, but every full wave of tiles (parts tiles each) is computed whole
+                                   from an FP32 workspace when there is more than one; plan.group_m = columns of
+                                   C per tile (a multiple of 8 up to 128; 0 = library's choice) */
+    B200_VARIANT_HYBRID = 6,     /* as STREAMK, but every full wave of tiles (parts tiles each) is computed whole
                                    and only the tiles of the ragged last wave are cut into k-ranges */
+    B200_VARIANT_SKINNY_PAIR = 7 /* as SKINNY on CTA pairs (cta_group::2): two neighbouring column tiles share
+                                   the rows of A, each CTA staging half of them; same plan fields */
 };
 
 /* The dispatch decision for one shape. All fields are filled by b200_hgemm_select(); a

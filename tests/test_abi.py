@@ -102,10 +102,14 @@ def test_plan_selection_covers_the_benchmark_shapes(native_lib):
     skinny = api.select_plan_untuned(48, 4096, 14336)
     assert skinny.variant == _native.VARIANT_SKINNY and skinny.bn == 64
     assert api.workspace_bytes(48, 4096, 14336, skinny) > 0
-    # 65 ... 128 rows keep the 128-row tiles
-    assert api.select_plan_untuned(128, 14336, 4096).variant == _native.VARIANT_CTA1
+    # 65 ... 128 rows against a large B: the same kernel on CTA pairs, k cut where the column tiles are few
+    wide128 = api.select_plan_untuned(128, 14336, 4096)
+    assert (wide128.variant, wide128.bn) == (_native.VARIANT_SKINNY_PAIR, 128)
+    assert api.workspace_bytes(128, 14336, 4096, wide128) == 0
     mid = api.select_plan_untuned(96, 4096, 14336)
-    assert mid.variant == _native.VARIANT_STREAMK and api.workspace_bytes(96, 4096, 14336, mid) > 0
+    assert mid.variant == _native.VARIANT_SKINNY_PAIR and api.workspace_bytes(96, 4096, 14336, mid) > 0
+    # small problems of that height keep the 128-row tiles or k-ranges over them
+    assert api.select_plan_untuned(100, 512, 4096).variant in (_native.VARIANT_CTA1, _native.VARIANT_STREAMK)
     assert api.workspace_bytes(8192, 8192, 8192, big) == 0
     odd = api.select_plan_untuned(48, 40, 100)
     assert odd.variant == _native.VARIANT_SIMT  # K % 8 != 0: no TMA row pitch
@@ -162,10 +166,14 @@ def test_every_plan_the_rules_pick_is_one_the_kernels_can_serve(native_lib):
         if K % 8 != 0:
             assert p.variant == V.VARIANT_SIMT, what
             continue
-        assert p.variant in (V.VARIANT_CTA1, V.VARIANT_CTA2, V.VARIANT_STREAMK, V.VARIANT_CTA2_MCAST, V.VARIANT_SKINNY), what
+        assert p.variant in (V.VARIANT_CTA1, V.VARIANT_CTA2, V.VARIANT_STREAMK, V.VARIANT_CTA2_MCAST, V.VARIANT_SKINNY,
+                             V.VARIANT_SKINNY_PAIR), what
         assert p.parts == 0 and p.grid == 0 and p.group_m == 0, what
         if p.variant == V.VARIANT_SKINNY:
             assert M <= 64 and p.bn in (16, 32, 64) and M <= p.bn and (p.bn == 16 or M > p.bn // 2), what
+            continue
+        if p.variant == V.VARIANT_SKINNY_PAIR:
+            assert 64 < M <= 128 and p.bn == 128 and N >= 2048 and K >= 1024, what
             continue
         assert M > 64, what
         assert p.tma_store == (1 if N % 8 == 0 else 0), what

@@ -276,6 +276,41 @@ def test_short_a_kernel(cuda_device, case):
     # the same plan twice gives the same bits (the k-ranges are summed in a fixed order)
     C2 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_SKINNY, mt, parts=parts))
     assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+    # and so do CTA pairs: the same products in the same order
+    C3 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_SKINNY_PAIR, mt, parts=parts))
+    assert np.array_equal(C.view(np.uint16), C3.view(np.uint16))
+    # plain stores instead of the staged TMA store
+    C4 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_SKINNY, mt, parts=parts, tma_store=0))
+    assert np.array_equal(C.view(np.uint16), C4.view(np.uint16))
+
+
+SHORT_A_WIDTH_CASES = [
+    # M, N, K, rows of A per tile, columns of C per tile (0 = the library's choice), k-ranges
+    (16, 1040, 512, 16, 104, 0),     # ten tiles of 104 columns
+    (16, 1000, 200, 16, 72, 0),      # N not a multiple of the width nor of 8; tails in K
+    (64, 14336, 256, 64, 0, 0),      # the library's own choice for the decode shape: 138 tiles of 104
+    (48, 2048, 1096, 64, 64, 3),     # narrow tiles and k-ranges together
+    (128, 512, 256, 128, 0, 0),      # 128 rows of A per tile
+    (100, 1032, 1096, 128, 0, 0),    # tails in M, N, K
+    (128, 14336, 512, 128, 0, 0),    # 138 tiles of 104 columns
+    (65, 4096, 3584, 128, 0, 0),     # few column tiles: k cut into ranges, FP32 partials summed
+    (128, 777, 320, 128, 88, 5),
+    (8, 136, 64, 16, 8, 0),          # the narrowest tile there is
+]
+
+
+@pytest.mark.parametrize("variant", [_native.VARIANT_SKINNY, _native.VARIANT_SKINNY_PAIR], ids=["single", "pairs"])
+@pytest.mark.parametrize("case", SHORT_A_WIDTH_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-mt{c[3]}-w{c[4]}-p{c[5]}")
+def test_short_a_kernel_tile_widths_and_128_rows(cuda_device, case, variant):
+    """Column tiles narrower than 128 (the TMA box of B has fewer rows than the MMA multiplies), up to 128 rows
+    of A, single CTAs and CTA pairs that share the rows of A."""
+    M, N, K, mt, width, parts = case
+    A, B = make_inputs(M, N, K, seed=33, dist="normal")
+    plan = plan_of(variant, mt, parts=parts, group_m=width)
+    C = run(None, A, B, cuda_device, plan)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"short-A mt={mt} width={width} parts={parts} {(M, N, K)}")
+    C2 = run(None, A, B, cuda_device, plan)
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
 
 
 def test_short_a_kernel_refuses_more_rows_than_its_tile(cuda_device):
