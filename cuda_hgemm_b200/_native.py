@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = (
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
     "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
     "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
-    "b200_debug_wait_expiry_static",
+    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex",
 )
 
 OK = 0
@@ -45,6 +45,8 @@ VARIANT_SKINNY = 5
 VARIANT_HYBRID = 6
 VARIANT_SKINNY_PAIR = 7
 
+C_F16, C_BF16, C_F32 = 0, 1, 2
+
 MULTICAST_OFF, MULTICAST_ON, MULTICAST_LOCKED_OFF = 0, 1, 2
 
 
@@ -59,7 +61,8 @@ class Plan(Structure):
 
 class Epilogue(Structure):
     """``b200_hgemm_epilogue``: C = alpha * A*B^T + beta * c_in + bias."""
-    _fields_ = [("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("bias", c_void_p), ("c_in", c_void_p)]
+    _fields_ = [("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("bias", c_void_p), ("c_in", c_void_p),
+                ("c_type", c_int32)]
 
 
 class HgemmError(RuntimeError):
@@ -91,6 +94,9 @@ def load() -> ctypes.CDLL:
     lib.b200_hgemm_ex.restype = c_int
     lib.b200_hgemm_fused.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, POINTER(Epilogue), c_void_p]
     lib.b200_hgemm_fused.restype = c_int
+    lib.b200_hgemm_fused_ex.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, POINTER(Epilogue),
+                                        POINTER(Plan), c_void_p]
+    lib.b200_hgemm_fused_ex.restype = c_int
     lib.b200_hgemm_host.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]
     lib.b200_hgemm_host.restype = c_int
     lib.b200_hgemm_host_a.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]

@@ -33,11 +33,12 @@ KERNEL_LOG_NAMES = {
 }
 
 
-def _shape_of(A, B, C):
+def _shape_of(A, B, C, c_dtypes=None):
     import torch
 
     for name, t in (("A", A), ("B", B), ("C", C)):
-        if not isinstance(t, torch.Tensor) or t.dtype != torch.float16 or not t.is_cuda or not t.is_contiguous():
+        ok_types = c_dtypes if (name == "C" and c_dtypes) else (torch.float16,)
+        if not isinstance(t, torch.Tensor) or t.dtype not in ok_types or not t.is_cuda or not t.is_contiguous():
             raise TypeError(f"{name} must be a contiguous float16 CUDA tensor")
         if t.dim() != 2:
             raise ValueError(f"{name} must be 2-D")
@@ -109,21 +110,29 @@ def hgemm_ex(A, B, C, plan: Plan):
     return C
 
 
-def hgemm_fused(A, B, C, alpha: float = 1.0, beta: float = 0.0, bias=None, c_in=None):
-    """``C = alpha * A @ B.T + beta * c_in + bias`` in one kernel (C ABI ``b200_hgemm_fused``); ``bias`` has one
-    FP16 value per column of C, ``c_in`` is an FP16 ``[M, N]`` tensor (``C`` itself for an in-place update)."""
+def hgemm_fused(A, B, C, alpha: float = 1.0, beta: float = 0.0, bias=None, c_in=None, plan: Plan = None):
+    """``C = alpha * A @ B.T + beta * c_in + bias`` in one kernel (C ABI ``b200_hgemm_fused``, or
+    ``b200_hgemm_fused_ex`` when a ``plan`` is given). ``C`` may be float16, bfloat16 or float32; ``bias`` has one
+    FP16 value per column of C; ``c_in`` is an ``[M, N]`` tensor of C's dtype (``C`` itself for an in-place update)."""
     import torch
 
-    M, N, K = _shape_of(A, B, C)
+    c_types = {torch.float16: _native.C_F16, torch.bfloat16: _native.C_BF16, torch.float32: _native.C_F32}
+    if not isinstance(C, torch.Tensor) or C.dtype not in c_types or not C.is_cuda or not C.is_contiguous() or C.dim() != 2:
+        raise TypeError("C must be a contiguous 2-D float16, bfloat16 or float32 CUDA tensor")
+    M, N, K = _shape_of(A, B, C, c_dtypes=tuple(c_types))
     if bias is not None and (bias.dtype != torch.float16 or bias.numel() != N or not bias.is_contiguous()):
         raise ValueError("bias must be a contiguous float16 tensor with one value per column of C")
-    if c_in is not None and (c_in.dtype != torch.float16 or tuple(c_in.shape) != (M, N) or not c_in.is_contiguous()):
-        raise ValueError("c_in must be a contiguous float16 [M, N] tensor")
+    if c_in is not None and (c_in.dtype != C.dtype or tuple(c_in.shape) != (M, N) or not c_in.is_contiguous()):
+        raise ValueError("c_in must be a contiguous [M, N] tensor of C's dtype")
     epi = _native.Epilogue(alpha, beta, bias.data_ptr() if bias is not None else None,
-                           c_in.data_ptr() if c_in is not None else None)
+                           c_in.data_ptr() if c_in is not None else None, c_types[C.dtype])
+    lib = _native.load()
     with torch.cuda.device(A.device):
-        check(_native.load().b200_hgemm_fused(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, ctypes.byref(epi),
-                                              _stream_of(A)))
+        if plan is None:
+            check(lib.b200_hgemm_fused(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, ctypes.byref(epi), _stream_of(A)))
+        else:
+            check(lib.b200_hgemm_fused_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, ctypes.byref(epi),
+                                          ctypes.byref(plan), _stream_of(A)))
     return C
 
 

@@ -23,6 +23,8 @@
 // memory and raises an error word the host reads.
 #pragma once
 
+#include <cuda_bf16.h>
+
 #include "ptx_sm100.cuh"
 #include "sched.h"
 
@@ -45,6 +47,14 @@ enum DeviceError : uint32_t {
     kDevWaitTimeout = 1,
 };
 
+// Element type of C (and of c_in) in the kernels instantiated with the fused epilogue; the plain kernels
+// write FP16 only. The values are those of B200_C_* in the public header.
+enum OutType : uint32_t {
+    kOutF16 = 0,
+    kOutBF16 = 1,
+    kOutF32 = 2,
+};
+
 struct alignas(64) GemmParams {
     CUtensorMap tm_a;  // A as {K, M}, box {64, 128}
     CUtensorMap tm_b;  // B as {K, N}, box {64, BN / CG}
@@ -65,7 +75,8 @@ struct alignas(64) GemmParams {
     // fused epilogue (kernels instantiated with EPI only): C = alpha * A*B^T + beta * c_in + bias
     float alpha, beta;
     const __half *bias;  // N values, one per column of C, or nullptr
-    const __half *c_in;  // M x N, row-major, read when beta != 0 (may be C itself), or nullptr
+    const void *c_in;    // M x N of C's element type, row-major, read when beta != 0 (may be C itself), or nullptr
+    uint32_t c_type;     // OutType of C and c_in (kernels with the fused epilogue only; 0 = FP16)
 #ifdef B200_TIMELINE
     unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
 #endif
@@ -168,6 +179,48 @@ __device__ __forceinline__ void store_row_chunk32(__half *c, uint32_t row, uint3
     }
 }
 
+// Two FP32 -> two packed 16-bit values of C's type, round to nearest even.
+__device__ __forceinline__ uint32_t pack2_rn(uint32_t lo_f32_bits, uint32_t hi_f32_bits, uint32_t c_type) {
+    if (c_type == kOutBF16) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(lo_f32_bits), __uint_as_float(hi_f32_bits));
+        return *reinterpret_cast<uint32_t *>(&b);
+    }
+    return pack_half2_rn(lo_f32_bits, hi_f32_bits);
+}
+
+// Element i of a row-major matrix of C's type, as FP32.
+__device__ __forceinline__ float load_c_elem(const void *base, size_t i, uint32_t c_type) {
+    if (c_type == kOutF32) return static_cast<const float *>(base)[i];
+    if (c_type == kOutBF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(base)[i]);
+    return __half2float(static_cast<const __half *>(base)[i]);
+}
+
+__device__ __forceinline__ void store_c_elem(void *base, size_t i, float v, uint32_t c_type) {
+    if (c_type == kOutF32) {
+        static_cast<float *>(base)[i] = v;
+    } else if (c_type == kOutBF16) {
+        static_cast<__nv_bfloat16 *>(base)[i] = __float2bfloat16_rn(v);
+    } else {
+        static_cast<__half *>(base)[i] = __float2half_rn(v);
+    }
+}
+
+// What the fused epilogue needs to know, for kernels that do not carry a whole GemmParams.
+struct EpilogueArgs {
+    float alpha, beta;
+    const __half *bias;
+    const void *c_in;
+    uint32_t c_type;
+};
+
+// v = alpha * v + bias[col] + beta * c_in[row][col] for one element (callers check the bounds).
+__device__ __forceinline__ float fused_value(const EpilogueArgs &e, float acc, size_t row, uint32_t col, uint32_t n) {
+    float v = e.alpha * acc;
+    if (e.bias) v += __half2float(e.bias[col]);
+    if (e.beta != 0.f && e.c_in) v = fmaf(e.beta, load_c_elem(e.c_in, row * n + col, e.c_type), v);
+    return v;
+}
+
 // Fused epilogue on COUNT accumulator columns of one row, in place (FP32 bit patterns):
 // v = alpha * v + bias[col] + beta * c_in[row][col]. Out-of-range rows and columns are left alone
 // (they are clipped when stored).
@@ -176,7 +229,8 @@ __device__ __forceinline__ void fused_epilogue(const GemmParams &p, uint32_t row
     const bool row_ok = row < p.m;
     const bool vec_ok = p.c_vec_ok != 0 && col0 + COUNT <= p.n;
     const __half *bias = p.bias ? p.bias + col0 : nullptr;
-    const __half *cin = (p.beta != 0.f && p.c_in && row_ok) ? p.c_in + static_cast<size_t>(row) * p.n + col0 : nullptr;
+    const bool use_cin = p.beta != 0.f && p.c_in && row_ok;
+    const size_t cin_off = static_cast<size_t>(row) * p.n + col0;
 #pragma unroll
     for (int j = 0; j < COUNT; j += 8) {
         float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -191,14 +245,31 @@ __device__ __forceinline__ void fused_epilogue(const GemmParams &p, uint32_t row
                     add[2 * e + 1] += f.y;
                 }
             }
-            if (cin) {
-                const uint4 c = *reinterpret_cast<const uint4 *>(cin + j);
-                const __half2 *h = reinterpret_cast<const __half2 *>(&c);
+            if (use_cin) {
+                if (p.c_type == kOutF32) {
+                    const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.c_in) + cin_off + j);
+                    const float4 c0 = src[0], c1 = src[1];
+                    add[0] += p.beta * c0.x; add[1] += p.beta * c0.y; add[2] += p.beta * c0.z; add[3] += p.beta * c0.w;
+                    add[4] += p.beta * c1.x; add[5] += p.beta * c1.y; add[6] += p.beta * c1.z; add[7] += p.beta * c1.w;
+                } else {
+                    const uint4 c = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.c_in) + cin_off + j);
+                    if (p.c_type == kOutBF16) {
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&c);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = __half22float2(h[e]);
-                    add[2 * e] += p.beta * f.x;
-                    add[2 * e + 1] += p.beta * f.y;
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(h[e]);
+                            add[2 * e] += p.beta * f.x;
+                            add[2 * e + 1] += p.beta * f.y;
+                        }
+                    } else {
+                        const __half2 *h = reinterpret_cast<const __half2 *>(&c);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __half22float2(h[e]);
+                            add[2 * e] += p.beta * f.x;
+                            add[2 * e + 1] += p.beta * f.y;
+                        }
+                    }
                 }
             }
         } else {
@@ -206,7 +277,7 @@ __device__ __forceinline__ void fused_epilogue(const GemmParams &p, uint32_t row
             for (int e = 0; e < 8; ++e) {
                 if (col0 + j + e < p.n) {
                     if (bias) add[e] += __half2float(bias[j + e]);
-                    if (cin) add[e] += p.beta * __half2float(cin[j + e]);
+                    if (use_cin) add[e] += p.beta * load_c_elem(p.c_in, cin_off + j + e, p.c_type);
                 }
             }
         }
@@ -215,12 +286,45 @@ __device__ __forceinline__ void fused_epilogue(const GemmParams &p, uint32_t row
     }
 }
 
+// 32 FP32 accumulator columns of one row -> C's element type -> global memory (kernels with the fused epilogue).
+__device__ __forceinline__ void store_row_chunk32_typed(void *c, uint32_t c_type, uint32_t row, uint32_t col0, uint32_t m,
+                                                        uint32_t n, bool vec_ok, const uint32_t (&r)[32]) {
+    if (row >= m || col0 >= n) return;
+    const size_t off = static_cast<size_t>(row) * n + col0;
+    if (vec_ok && col0 + 32 <= n) {
+        if (c_type == kOutF32) {
+            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(c) + off);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                     __uint_as_float(r[4 * j + 3]));
+            }
+        } else {
+            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__half *>(c) + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack2_rn(r[8 * j + 0], r[8 * j + 1], c_type);
+                v.y = pack2_rn(r[8 * j + 2], r[8 * j + 3], c_type);
+                v.z = pack2_rn(r[8 * j + 4], r[8 * j + 5], c_type);
+                v.w = pack2_rn(r[8 * j + 6], r[8 * j + 7], c_type);
+                dst[j] = v;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col0 + j < n) store_c_elem(c, off + j, __uint_as_float(r[j]), c_type);
+        }
+    }
+}
+
 // KPS = k-blocks per stage. With KPS = 2, GemmParams::k_blocks and every k index of the work
 // decomposition count pairs of k-blocks (one stage each); a pair that reaches past K reads zeros there.
-// EPI: apply GemmParams' alpha / beta / bias in the epilogue (whole tiles only).
+// EPI: apply GemmParams' alpha / beta / bias in the epilogue and write C in GemmParams::c_type (tiles whose
+// k-range is cut leave FP32 partials as always; streamk_reduce_kernel applies the same epilogue to their sum).
 template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
-    static_assert(!EPI || MODE == kModeTiles, "the fused epilogue is applied to whole tiles");
     using T = KernelTraits<BN, STAGES, CG, KPS>;
     static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
 
@@ -460,13 +564,14 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                             if (lane == 0) tma_store_wait_read<1>();
                             __syncwarp();
                             uint8_t *row_ptr = buf + lane * 128u;
+                            const uint32_t c_type = EPI ? p.c_type : static_cast<uint32_t>(kOutF16);  // FP16 or BF16 here
 #pragma unroll
                             for (uint32_t j = 0; j < 8; ++j) {
                                 uint4 v;
-                                v.x = pack_half2_rn(cur[8 * j + 0], cur[8 * j + 1]);
-                                v.y = pack_half2_rn(cur[8 * j + 2], cur[8 * j + 3]);
-                                v.z = pack_half2_rn(cur[8 * j + 4], cur[8 * j + 5]);
-                                v.w = pack_half2_rn(cur[8 * j + 6], cur[8 * j + 7]);
+                                v.x = pack2_rn(cur[8 * j + 0], cur[8 * j + 1], c_type);
+                                v.y = pack2_rn(cur[8 * j + 2], cur[8 * j + 3], c_type);
+                                v.z = pack2_rn(cur[8 * j + 4], cur[8 * j + 5], c_type);
+                                v.w = pack2_rn(cur[8 * j + 6], cur[8 * j + 7], c_type);
                                 // 128-byte swizzle: 16-byte word j of row r lives at word j ^ (r % 8)
                                 *reinterpret_cast<uint4 *>(row_ptr + ((j ^ (lane & 7u)) << 4)) = v;
                             }
@@ -486,8 +591,12 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         uint32_t r[32];
                         tmem_ld_32x32b_x32(taddr + c * 32u, r);
                         tmem_ld_wait();
-                        if (EPI) fused_epilogue<32>(p, m0 + row_in_tile, n0 + c * 32u, r);
-                        store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
+                        if (EPI) {
+                            fused_epilogue<32>(p, m0 + row_in_tile, n0 + c * 32u, r);
+                            store_row_chunk32_typed(p.c, p.c_type, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
+                        } else {
+                            store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
+                        }
                     }
                 }
                 // accumulator drained: hand it back to the MMA warp
@@ -572,6 +681,8 @@ struct ReduceParams {
     uint32_t dp_tiles;  // tiles the GEMM kernel walked whole; the k-ranges cover tiles [dp_tiles, tiles)
     uint32_t parts;
     uint32_t bn;
+    uint32_t fused;     // 1: apply `epi` to the sums and write C in epi.c_type; 0: plain FP16
+    EpilogueArgs epi;
 };
 
 constexpr int kReduceThreads = 256;
@@ -616,6 +727,14 @@ __global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const Re
             acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
         }
         const uint32_t col = n0 + w * 4u;
+        if (p.fused) {
+            const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+            const size_t row = m0 + r;
+            for (uint32_t e = 0; e < 4 && col + e < p.n; ++e) {
+                store_c_elem(p.c, row * p.n + col + e, fused_value(p.epi, vals[e], row, col + e, p.n), p.epi.c_type);
+            }
+            continue;
+        }
         __half *dst = p.c + static_cast<size_t>(m0 + r) * p.n + col;
         if (vec4_ok && col + 4u <= p.n) {
             uint2 v;

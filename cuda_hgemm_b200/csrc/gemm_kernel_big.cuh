@@ -48,7 +48,9 @@ struct NoMulticastLoad {
     static __device__ __forceinline__ void load(uint32_t, const CUtensorMap *, int32_t, int32_t, uint32_t, uint16_t) {}
 };
 
-template <int GROUP, class MulticastLoad>
+// EPI: apply GemmParams' alpha / beta / bias to each 16-column chunk as it leaves tensor memory and pack C as
+// FP16 or BF16 (GemmParams::c_type).
+template <int GROUP, class MulticastLoad, bool EPI = false>
 __device__ __forceinline__ void hgemm_big_body(const GemmParams &p) {
     static_assert(GROUP == 2 || GROUP == 4, "a work group is one CTA pair or two");
     constexpr int STAGES = kBigStages;
@@ -227,8 +229,14 @@ __device__ __forceinline__ void hgemm_big_body(const GemmParams &p) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar, quad ? pair * 2u : 0u));
                 }
+                if (EPI) {
+                    if (warp_rows_live) fused_epilogue<16>(p, m0 + q * 32u + lane, n0 + s * 16u, cur);
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) packed[s * 8 + j] = pack_half2_rn(cur[2 * j], cur[2 * j + 1]);
+                    for (uint32_t j = 0; j < 8; ++j) packed[s * 8 + j] = pack2_rn(cur[2 * j], cur[2 * j + 1], p.c_type);
+                } else {
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) packed[s * 8 + j] = pack_half2_rn(cur[2 * j], cur[2 * j + 1]);
+                }
             }
 #pragma unroll
             for (uint32_t c = 0; c < BN / 64; ++c) {

@@ -54,6 +54,7 @@ struct alignas(64) SkinnyParams {
     uint32_t n_pad;          // row pitch of the partial results, in floats
     uint32_t tma_store;      // 1: whole results leave through tm_c
     uint32_t prefetch_kb;    // k-blocks of B asked into L2 before waiting for the previous kernel
+    EpilogueArgs epi;        // kernels instantiated with EPI: alpha / beta / bias / c_in and the element type of C
 #ifdef B200_TIMELINE
     unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
 #endif
@@ -77,7 +78,9 @@ struct SkinnyTraits {
     static_assert(STAGES * kStageBytes >= MT * 128 * 2, "the ring must hold one tile of C for the epilogue");
 };
 
-template <int MT, int STAGES, int KPS, int CG = 1>
+// EPI: whole results get alpha * acc + beta * c_in + bias before their one rounding and leave in epi.c_type
+// (FP32 partials of cut k-ranges are left as they are: skinny_reduce_kernel applies the same to their sum).
+template <int MT, int STAGES, int KPS, int CG = 1, bool EPI = false>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_constant__ SkinnyParams p) {
     using T = SkinnyTraits<MT, STAGES, KPS, CG>;
 
@@ -265,7 +268,14 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             // 32 lanes write 32 consecutive halves of one row of the tile
-                            tile_c[(c * 16u + j) * p.tile_w + col_in_tile] = __float2half_rn(__uint_as_float(r[j]));
+                            const uint32_t m = c * 16u + j;
+                            float v = __uint_as_float(r[j]);
+                            if (EPI) {
+                                if (m < p.m && n < p.n) v = fused_value(p.epi, v, m, n, p.n);
+                                store_c_elem(tile_c, m * p.tile_w + col_in_tile, v, p.epi.c_type);  // FP16 or BF16 here
+                            } else {
+                                tile_c[m * p.tile_w + col_in_tile] = __float2half_rn(v);
+                            }
                         }
                     }
                 } else if (col_live) {
@@ -273,8 +283,15 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             const uint32_t m = c * 16u + j;
-                            // 32 lanes write 32 consecutive halves of one row of C
-                            if (m < p.m) p.c[static_cast<size_t>(m) * p.n + n] = __float2half_rn(__uint_as_float(r[j]));
+                            // 32 lanes write 32 consecutive elements of one row of C
+                            if (m < p.m) {
+                                if (EPI) {
+                                    store_c_elem(p.c, static_cast<size_t>(m) * p.n + n,
+                                                 fused_value(p.epi, __uint_as_float(r[j]), m, n, p.n), p.epi.c_type);
+                                } else {
+                                    p.c[static_cast<size_t>(m) * p.n + n] = __float2half_rn(__uint_as_float(r[j]));
+                                }
+                            }
                         }
                     } else {
                         float *ws = p.partials + static_cast<size_t>(slice) * MT * p.n_pad;
@@ -323,9 +340,10 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
 constexpr int kSkinnyReduceThreads = 256;
 
 // C[m][n] = sum over the k-ranges of their FP32 partial results, in range order, rounded to FP16 once.
+// With `fused` the sum gets alpha / beta / bias and leaves in epi.c_type.
 __global__ void __launch_bounds__(kSkinnyReduceThreads) skinny_reduce_kernel(const float *partials, __half *c, uint32_t m,
                                                                             uint32_t n, uint32_t n_pad, uint32_t mt,
-                                                                            uint32_t slices) {
+                                                                            uint32_t slices, uint32_t fused, EpilogueArgs epi) {
     pdl_wait_prior_grids();
     const uint32_t col = blockIdx.x * kSkinnyReduceThreads + threadIdx.x;
     const uint32_t row = blockIdx.y;
@@ -334,7 +352,11 @@ __global__ void __launch_bounds__(kSkinnyReduceThreads) skinny_reduce_kernel(con
     for (uint32_t s = 0; s < slices; ++s) {
         acc += partials[(static_cast<size_t>(s) * mt + row) * n_pad + col];
     }
-    c[static_cast<size_t>(row) * n + col] = __float2half_rn(acc);
+    if (fused) {
+        store_c_elem(c, static_cast<size_t>(row) * n + col, fused_value(epi, acc, row, col, n), epi.c_type);
+    } else {
+        c[static_cast<size_t>(row) * n + col] = __float2half_rn(acc);
+    }
 }
 
 }  // namespace b200

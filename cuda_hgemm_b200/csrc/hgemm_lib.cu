@@ -78,8 +78,8 @@ struct DeviceState {
     size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
     cudaStream_t host_stream[3] = {nullptr, nullptr, nullptr};  // upload, GEMMs, download
     cudaEvent_t host_event[2] = {nullptr, nullptr};
-    bool attr_set[32] = {};
-    int max_clusters[32] = {};  // CTA pairs the device can keep resident at once, per pair kernel
+    bool attr_set[64] = {};
+    int max_clusters[64] = {};  // CTA pairs the device can keep resident at once, per pair kernel
     TensorMapSlot tm_cache[64 * kTensorMapWays];
     uint64_t tm_clock = 0;
 };
@@ -654,10 +654,13 @@ __global__ void __launch_bounds__(kBigThreads, 1) hgemm_tcgen05_big_kernel(const
     hgemm_big_body<2, NoMulticastLoad>(p);
 }
 
-constexpr int kBigAttrSlot = 8;
+__global__ void __launch_bounds__(kBigThreads, 1) hgemm_tcgen05_big_epi_kernel(const __grid_constant__ GemmParams p) {
+    hgemm_big_body<2, NoMulticastLoad, true>(p);
+}
 
-static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
-    auto kern = hgemm_tcgen05_big_kernel;
+static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid, cudaStream_t stream, bool fused = false) {
+    auto kern = fused ? hgemm_tcgen05_big_epi_kernel : hgemm_tcgen05_big_kernel;
+    const int kBigAttrSlot = fused ? 15 : 8;
     if (!st.attr_set[kBigAttrSlot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[kBigAttrSlot]) {
@@ -808,6 +811,19 @@ static int run_simt(const void *A, const void *B, void *C, size_t M, size_t N, s
     return B200_HGEMM_OK;
 }
 
+// The fused epilogue a caller asked for, checked and in the kernels' terms.
+static int epilogue_args(const b200_hgemm_epilogue &epi, EpilogueArgs *out) {
+    if (epi.c_type != B200_C_F16 && epi.c_type != B200_C_BF16 && epi.c_type != B200_C_F32) return B200_HGEMM_ERR_INVALID_ARG;
+    if (epi.beta != 0.f && !epi.c_in) return B200_HGEMM_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(epi.bias) | reinterpret_cast<uintptr_t>(epi.c_in)) & 15u) return B200_HGEMM_ERR_MISALIGNED;
+    out->alpha = epi.alpha;
+    out->beta = epi.beta;
+    out->bias = static_cast<const __half *>(epi.bias);
+    out->c_in = epi.c_in;
+    out->c_type = static_cast<uint32_t>(epi.c_type);
+    return B200_HGEMM_OK;
+}
+
 // ---- short A (M <= 128): B streams through the MMA's row operand (gemm_kernel_skinny.cuh) ----
 // Width of a column tile, in columns of C. Every CTA streams the tile's rows of B over its whole
 // k-range, so the kernel takes as long as its busiest SM: waves x width is what to minimise. 128
@@ -866,10 +882,20 @@ static uint32_t skinny_prefetch_kb() {
     return kb;
 }
 
+template <int MT, int STAGES, int KPS, int CG, bool EPI>
+static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream);
+
+// The kernel for this tile height and CTA grouping, plain or with the fused epilogue (attribute slots 32 up).
 template <int MT, int STAGES, int KPS, int CG = 1>
-static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream) {
+static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool fused) {
+    if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true>(st, attr_slot + 21, p, stream);
+    return launch_skinny_kernel<MT, STAGES, KPS, CG, false>(st, attr_slot, p, stream);
+}
+
+template <int MT, int STAGES, int KPS, int CG, bool EPI>
+static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream) {
     using T = SkinnyTraits<MT, STAGES, KPS, CG>;
-    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS, CG>;
+    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS, CG, EPI>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -911,10 +937,15 @@ static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, 
 
 static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                       const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes,
-                      uint32_t *error_word) {
+                      uint32_t *error_word, const b200_hgemm_epilogue *epi) {
     if (M > static_cast<size_t>(pl.bn)) return B200_HGEMM_ERR_UNSUPPORTED;
     SkinnyParams p;
     memset(&p, 0, sizeof(p));
+    const bool fused = epi != nullptr;
+    if (fused) {
+        const int erc = epilogue_args(*epi, &p.epi);
+        if (erc != B200_HGEMM_OK) return erc;
+    }
     p.c = static_cast<__half *>(C);
     p.error_word = error_word;
     p.m = static_cast<uint32_t>(M);
@@ -939,7 +970,7 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     if (rc != B200_HGEMM_OK) return rc;
     // whole results leave through one TMA store per tile (a plain row-major box of tile_w x bn) when C can
     // have a tensor map: rows of N halves must be a multiple of 16 bytes
-    p.tma_store = (pl.tma_store && N % 8 == 0 && p.slices == 1) ? 1u : 0u;
+    p.tma_store = (pl.tma_store && N % 8 == 0 && p.slices == 1 && p.epi.c_type != kOutF32) ? 1u : 0u;  // FP32 leaves by element
     if (p.tma_store) {
         rc = get_tensor_map(st, C, M, N, static_cast<uint32_t>(pl.bn), p.tile_w, &p.tm_c, false);
         if (rc != B200_HGEMM_OK) return rc;
@@ -958,22 +989,22 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     }
     if (pairs) {
         if (pl.bn == 16) {
-            rc = launch_skinny<16, 6, 2, 2>(st, 21, p, stream);
+            rc = launch_skinny<16, 6, 2, 2>(st, 25, p, stream, fused);
         } else if (pl.bn == 32) {
-            rc = launch_skinny<32, 6, 2, 2>(st, 22, p, stream);
+            rc = launch_skinny<32, 6, 2, 2>(st, 26, p, stream, fused);
         } else if (pl.bn == 64) {
-            rc = launch_skinny<64, 5, 2, 2>(st, 23, p, stream);
+            rc = launch_skinny<64, 5, 2, 2>(st, 27, p, stream, fused);
         } else {
-            rc = launch_skinny<128, 4, 2, 2>(st, 24, p, stream);
+            rc = launch_skinny<128, 4, 2, 2>(st, 28, p, stream, fused);
         }
     } else if (pl.bn == 16) {
-        rc = launch_skinny<16, 6, 2>(st, 11, p, stream);
+        rc = launch_skinny<16, 6, 2>(st, 11, p, stream, fused);
     } else if (pl.bn == 32) {
-        rc = launch_skinny<32, 5, 2>(st, 12, p, stream);
+        rc = launch_skinny<32, 5, 2>(st, 12, p, stream, fused);
     } else if (pl.bn == 64) {
-        rc = launch_skinny<64, 4, 2>(st, 13, p, stream);
+        rc = launch_skinny<64, 4, 2>(st, 13, p, stream, fused);
     } else {
-        rc = launch_skinny<128, 3, 2>(st, 14, p, stream);
+        rc = launch_skinny<128, 3, 2>(st, 14, p, stream, fused);
     }
     if (rc != B200_HGEMM_OK || p.slices == 1) return rc;
     cudaLaunchConfig_t cfg;
@@ -987,7 +1018,7 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     cfg.attrs = &attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     if (!cuda_ok(cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, static_cast<const float *>(p.partials), p.c, p.m, p.n, p.n_pad,
-                                    static_cast<uint32_t>(pl.bn), p.slices),
+                                    static_cast<uint32_t>(pl.bn), p.slices, fused ? 1u : 0u, p.epi),
                  "cudaLaunchKernelEx")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
@@ -1013,7 +1044,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     }
     if (pl.variant == B200_VARIANT_SKINNY || pl.variant == B200_VARIANT_SKINNY_PAIR) {
         return run_skinny(st, A, B, C, M, N, K, pl, stream, ws_override, ws_override_bytes,
-                          error_word_override ? error_word_override : st.error_word);
+                          error_word_override ? error_word_override : st.error_word, epi);
     }
     if (pl.variant == B200_VARIANT_CTA2_MCAST) {
         // the multicast loads may only ever read this GPU's own memory: every operand must be an
@@ -1071,16 +1102,18 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
     p.tma_store = pl.tma_store ? 1u : 0u;
     p.c_vec_ok = (N % 8 == 0) ? 1u : 0u;
+    EpilogueArgs ea;
+    memset(&ea, 0, sizeof(ea));
     if (epi) {
-        // whole-tile kernels only; c_vec_ok also covers the 16-byte loads of bias and c_in
-        if (pl.variant != B200_VARIANT_CTA1 && !(pl.variant == B200_VARIANT_CTA2 && !big)) return B200_HGEMM_ERR_UNSUPPORTED;
-        if (bn == 192) return B200_HGEMM_ERR_UNSUPPORTED;
-        p.alpha = epi->alpha;
-        p.beta = epi->beta;
-        p.bias = static_cast<const __half *>(epi->bias);
-        p.c_in = static_cast<const __half *>(epi->c_in);
-        if (p.beta != 0.f && !p.c_in) return B200_HGEMM_ERR_INVALID_ARG;
-        if ((reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.c_in)) & 15u) return B200_HGEMM_ERR_MISALIGNED;
+        // c_vec_ok also covers the 16-byte loads of bias and c_in
+        if ((rc = epilogue_args(*epi, &ea)) != B200_HGEMM_OK) return rc;
+        if (big && ea.c_type == kOutF32) return B200_HGEMM_ERR_UNSUPPORTED;  // that kernel packs 16-bit outputs only
+        p.alpha = ea.alpha;
+        p.beta = ea.beta;
+        p.bias = ea.bias;
+        p.c_in = ea.c_in;
+        p.c_type = ea.c_type;
+        if (ea.c_type == kOutF32) p.tma_store = 0;  // FP32 rows leave with plain 16-byte stores
     }
 #ifdef B200_TIMELINE
     p.timeline = g_timeline;
@@ -1122,13 +1155,16 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         grid = workers * cg;
     }
 
-    if (epi) {
+    if (epi && !plan_cuts_k(pl)) {
         if (pl.variant == B200_VARIANT_CTA1) {
             if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles, 1, true>(st, 16, p, grid, stream);
+            if (bn == 192) return launch_kernel<192, 4, 1, kModeTiles, 1, true>(st, 21, p, grid, stream);
             if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2, true>(st, 17, p, grid, stream);
             return launch_kernel<64, 4, 1, kModeTiles, 2, true>(st, 18, p, grid, stream);
         }
+        if (big) return launch_big_kernel(st, p, grid, stream, true);
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles, 1, true>(st, 19, p, grid, stream);
+        if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2, true>(st, 22, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2, true>(st, 20, p, grid, stream);
     }
     if (pl.variant == B200_VARIANT_CTA1) {
@@ -1143,7 +1179,15 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);
     }
-    if (bn == 256) {
+    if (epi) {  // whole tiles get the epilogue in the kernel, cut tiles in the reduction below
+        if (bn == 256) {
+            rc = launch_kernel<256, 4, 1, kModeStreamK, 1, true>(st, 23, p, grid, stream);
+        } else if (bn == 128) {
+            rc = launch_kernel<128, 3, 1, kModeStreamK, 2, true>(st, 24, p, grid, stream);
+        } else {
+            rc = launch_kernel<64, 4, 1, kModeStreamK, 2, true>(st, 29, p, grid, stream);
+        }
+    } else if (bn == 256) {
         rc = launch_kernel<256, 4, 1, kModeStreamK>(st, 5, p, grid, stream);
     } else if (bn == 128) {
         rc = launch_kernel<128, 3, 1, kModeStreamK, 2>(st, 6, p, grid, stream);
@@ -1176,6 +1220,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     rp.group_m = p.group_m;
     rp.parts = parts;
     rp.bn = static_cast<uint32_t>(bn);
+    rp.fused = epi ? 1u : 0u;
+    rp.epi = ea;
     // One or two 16-byte words per thread: the sum over ranges is a chain of dependent-latency
     // loads, so the kernel gets its bandwidth from many resident threads, not from long loops.
     const uint32_t words = 128u * static_cast<uint32_t>(bn) / 4u;
@@ -1406,37 +1452,14 @@ int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, siz
     return entry(A, B, C, M, N, K, plan, -1, reinterpret_cast<cudaStream_t>(stream));
 }
 
-// The plan among the whole-tile kernels (the ones that carry the fused epilogue) closest to what
-// the dispatch would run for this shape.
-static int fused_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
+// The dispatch's plan for the shape, as the fused epilogue can run it: every kernel family carries it; the
+// multicast variants run as the same tiles on plain pairs, and FP32 output leaves the 256 x 256-per-CTA
+// arrangement (whose epilogue packs 16-bit values) for 128 x 256 per CTA.
+static int fused_plan(const DeviceState &st, size_t M, size_t N, size_t K, int c_type, b200_hgemm_plan *pl) {
     select_plan(st, M, N, K, pl);
-    const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
-    switch (pl->variant) {
-        case B200_VARIANT_SIMT:
-            return B200_HGEMM_ERR_UNSUPPORTED;  // K % 8 != 0
-        case B200_VARIANT_CTA1:
-            if (pl->bn == 192) pl->bn = 256;
-            break;
-        case B200_VARIANT_CTA2:
-            if (pl->bn != 128) pl->bn = 256;
-            break;
-        case B200_VARIANT_CTA2_MCAST:
-            pl->variant = B200_VARIANT_CTA2;
-            pl->bn = 256;
-            break;
-        case B200_VARIANT_SKINNY:
-        case B200_VARIANT_SKINNY_PAIR:
-            pl->variant = B200_VARIANT_CTA1;
-            pl->bn = ceil_div_u32(N, 128) * 2 >= sms ? 128 : 64;
-            break;
-        default:  // k-ranges: the same tiles, walked whole
-            pl->variant = B200_VARIANT_CTA1;
-            break;
-    }
-    pl->parts = 0;
-    pl->grid = 0;
-    pl->group_m = 0;
-    pl->tma_store = (N % 8 == 0) ? 1 : 0;
+    if (pl->variant == B200_VARIANT_SIMT) return B200_HGEMM_ERR_UNSUPPORTED;  // K % 8 != 0
+    if (pl->variant == B200_VARIANT_CTA2_MCAST) pl->variant = B200_VARIANT_CTA2;
+    if (pl->variant == B200_VARIANT_CTA2 && pl->bn == 512 && c_type == B200_C_F32) pl->bn = 256;
     return B200_HGEMM_OK;
 }
 
@@ -1450,9 +1473,22 @@ int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, 
     if (rc != B200_HGEMM_OK) return rc;
     if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
     b200_hgemm_plan pl;
-    rc = fused_plan(*st, M, N, K, &pl);
+    rc = fused_plan(*st, M, N, K, epilogue->c_type, &pl);
     if (rc != B200_HGEMM_OK) return rc;
     return run_plan(*st, A, B, C, M, N, K, pl, reinterpret_cast<cudaStream_t>(stream), nullptr, 0, nullptr, epilogue);
+}
+
+int b200_hgemm_fused_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_epilogue *epilogue,
+                        const b200_hgemm_plan *plan, b200_stream_t stream) {
+    if (!epilogue || !plan) return B200_HGEMM_ERR_INVALID_ARG;
+    int rc = check_args(A, B, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    if (plan->variant == B200_VARIANT_SIMT || plan->variant == B200_VARIANT_CTA2_MCAST) return B200_HGEMM_ERR_UNSUPPORTED;
+    return run_plan(*st, A, B, C, M, N, K, *plan, reinterpret_cast<cudaStream_t>(stream), nullptr, 0, nullptr, epilogue);
 }
 
 int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan) {

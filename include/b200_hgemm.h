@@ -122,18 +122,29 @@ int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, siz
                   b200_stream_t stream);
 
 /* GEMM with a fused epilogue: C = alpha * (A * B^T) + beta * c_in + bias, everything after the product in
- * FP32 on the accumulator before the one rounding to FP16. The reference fixes alpha = 1, beta = 0
- * (src/cublas_tensor_op.cu:19-20) and has no counterpart; this is the step either side of a GEMM in
- * decode/prefill use. Runs on the whole-tile kernels (single CTAs or pairs, the dispatch's choice mapped
- * onto them); needs K % 8 == 0. */
+ * FP32 on the accumulator before the one rounding to C's element type, which may be FP16, BF16 or FP32.
+ * The reference fixes alpha = 1, beta = 0 and FP16 (src/cublas_tensor_op.cu:19-24) and has no counterpart;
+ * this is the step either side of a GEMM in decode/prefill use. It runs on the kernel the dispatch picks for
+ * the shape (short-A, single-CTA and pair tiles, k-ranges, 256 x 256 outputs per CTA) with two exceptions:
+ * the multicast variants run as the same tiles on plain pairs, and FP32 output is written with plain stores
+ * (the 256 x 256-per-CTA arrangement falls back to 128 x 256 per CTA for it). Needs K % 8 == 0. */
+enum {
+    B200_C_F16 = 0,  /* IEEE binary16, the reference's only output type */
+    B200_C_BF16 = 1,
+    B200_C_F32 = 2
+};
 typedef struct b200_hgemm_epilogue {
     float alpha;
     float beta;
-    const void *bias; /* N halves, one per column of C, 16-byte aligned; or NULL */
-    const void *c_in; /* M x N halves, row-major, 16-byte aligned, read when beta != 0; may be C itself; or NULL */
+    const void *bias; /* N halves (FP16), one per column of C, 16-byte aligned; or NULL */
+    const void *c_in; /* M x N elements of C's type, row-major, 16-byte aligned, read when beta != 0; may be C itself; or NULL */
+    int32_t c_type;   /* B200_C_*: element type of C and of c_in */
 } b200_hgemm_epilogue;
 int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                      const b200_hgemm_epilogue *epilogue, b200_stream_t stream);
+/* The same on an explicit plan (as b200_hgemm_ex). */
+int b200_hgemm_fused_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+                        const b200_hgemm_epilogue *epilogue, const b200_hgemm_plan *plan, b200_stream_t stream);
 
 /* HOST-pointer GEMM: copies A and B to the device, runs b200_hgemm, copies C back and
  * synchronises. This is the path of reference Matrix (src/common/matrix.h:23-35 upload,

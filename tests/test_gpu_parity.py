@@ -558,10 +558,13 @@ FUSED_CASES = [
     (200, 264, 136, -1.25, 0.75, True, False),   # everything, tails in M, N, K
     (200, 1001, 136, 2.0, -0.5, True, False),    # N not a multiple of 8: guarded loads and stores
     (1024, 1536, 512, 1.0, 1.0, False, True),    # C += A * B^T in place
-    (2304, 2304, 256, 0.25, 2.0, True, True),    # pairs (the dispatch's 256 x 192 mapped to 256 x 256)
-    (16, 1024, 2048, 1.5, 0.5, True, False),     # a decode batch: mapped from the short-A kernel to 128-row tiles
-    (96, 4096, 1024, 1.0, 0.5, True, True),      # mapped from k-ranges to whole tiles
+    (2304, 2304, 256, 0.25, 2.0, True, True),    # pairs on 256 x 192
+    (16, 1024, 2048, 1.5, 0.5, True, False),     # a decode batch: the short-A kernel
+    (16, 4096, 14336, 1.0, 1.0, True, True),     # the short-A kernel with k cut into ranges: epilogue in the summing kernel
+    (96, 4096, 1024, 1.0, 0.5, True, True),      # the short-A kernel on CTA pairs
+    (100, 512, 4096, 0.5, 0.5, True, False),     # k-ranges over 128-row tiles
     (4096, 4096, 1536, 1.0, 0.5, True, False),   # many waves of pairs
+    (4096, 4096, 4096, 1.0, -1.0, True, True),   # 256 x 256 outputs per CTA
 ]
 
 
@@ -593,13 +596,88 @@ def test_fused_epilogue(cuda_device, case):
     assert_close_to_oracle(C.cpu().numpy(), ref.astype(np.float32), f"fused {case}")
 
 
-def test_fused_epilogue_with_identity_matches_the_plain_product(cuda_device):
-    A, B = make_inputs(512, 768, 448, seed=63)
+@pytest.mark.parametrize("shape", [(512, 768, 448), (16, 2048, 1024), (128, 4096, 2048), (2560, 2304, 1536)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_fused_epilogue_with_identity_matches_the_plain_product(cuda_device, shape):
+    """alpha = 1, beta = 0, no bias: the same kernel family as the plain entry point, the same bits."""
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=63)
     dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
-    C = poisoned(512, 768, cuda_device).view(512, 768)
+    C = poisoned(M, N, cuda_device).view(M, N)
     api.hgemm_fused(dA, dB, C, 1.0, 0.0)
-    plain = run(api.b200HgemmCta1, A, B, cuda_device)
+    plain = run(api.b200Hgemm, A, B, cuda_device)
     assert np.array_equal(C.cpu().numpy().view(np.uint16), plain.view(np.uint16))
+
+
+FUSED_PLAN_CASES = [
+    # M, N, K, variant, bn, parts, tma_store
+    (1024, 2048, 1024, _native.VARIANT_CTA2, 512, 0, 1),      # 256 x 256 outputs per CTA, several tiles per CTA
+    (600, 776, 136, _native.VARIANT_CTA2, 512, 0, 1),         # the same with tails in M, N and K
+    (384, 512, 320, _native.VARIANT_CTA1, 192, 0, 1),
+    (600, 776, 520, _native.VARIANT_CTA2, 192, 0, 1),
+    (200, 1032, 1096, _native.VARIANT_STREAMK, 128, 33, 1),   # whole and cut tiles in one launch
+    (200, 1032, 1096, _native.VARIANT_STREAMK, 64, 7, 0),
+    (1000, 1032, 1096, _native.VARIANT_HYBRID, 256, 7, 1),
+    (16, 4096, 3584, _native.VARIANT_SKINNY, 16, 3, 1),
+    (40, 1000, 520, _native.VARIANT_SKINNY, 64, 0, 1),        # N % 8 != 0: by element
+    (128, 2048, 1024, _native.VARIANT_SKINNY_PAIR, 128, 0, 1),
+    (65, 1032, 1096, _native.VARIANT_SKINNY_PAIR, 128, 2, 1),
+]
+
+
+@pytest.mark.parametrize("c_dtype", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("case", FUSED_PLAN_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-v{c[3]}-bn{c[4]}-p{c[5]}")
+def test_fused_epilogue_on_every_kernel_family_and_output_type(cuda_device, case, c_dtype):
+    """alpha, beta * c_in and bias on an explicit plan, C (and c_in) as FP16, BF16 or FP32."""
+    import torch
+
+    M, N, K, variant, bn, parts, tma_store = case
+    dtype = getattr(torch, c_dtype)
+    A, B = make_inputs(M, N, K, seed=66)
+    rng = np.random.default_rng(67)
+    alpha, beta = 0.75, -0.5
+    c_in = torch.from_numpy(rng.uniform(-4, 4, size=(M, N)).astype(np.float32)).to(dtype)
+    bias = rng.uniform(-2, 2, size=(N,)).astype(np.float16)
+    ref = (alpha * oracle.gemm_f32(A, B) + np.float32(beta) * c_in.float().numpy() + bias.astype(np.float32)[None, :])
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    C = torch.full((M, N), float("nan"), dtype=dtype, device=cuda_device)
+    plan = plan_of(variant, bn, parts=parts, tma_store=tma_store if N % 8 == 0 else 0)
+    if variant == _native.VARIANT_CTA2 and bn == 512 and c_dtype == "float32":
+        with pytest.raises(_native.HgemmError) as e:
+            api.hgemm_fused(dA, dB, C, alpha, beta, to_dev(bias, cuda_device), c_in.to(cuda_device), plan=plan)
+        assert e.value.status == _native.ERR_UNSUPPORTED
+        return
+    api.hgemm_fused(dA, dB, C, alpha, beta, to_dev(bias, cuda_device), c_in.to(cuda_device), plan=plan)
+    torch.cuda.synchronize(cuda_device)
+    assert api.last_device_error() == 0
+    got = C.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    if c_dtype == "float16":
+        assert_close_to_oracle(C.cpu().numpy(), ref.astype(np.float32), f"fused {case}")
+        return
+    # FP32 output keeps the accumulator: only the order of summation differs from the oracle's; BF16 rounds once to 8 bits
+    tol = 2e-5 if c_dtype == "float32" else 2.0 ** -8
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err <= tol, f"{case} {c_dtype}: max-norm relative error {err:.3e}"
+
+
+def test_fused_epilogue_through_the_dispatch_with_other_output_types(cuda_device):
+    """FP32 output on a shape whose plan is 256 x 256 outputs per CTA falls back to 128 x 256; BF16 stays."""
+    import torch
+
+    M = N = K = 4096
+    A, B = make_inputs(M, N, K, seed=68)
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    rows = [0, 255, 256, 2049, M - 1]
+    ref = np.stack([oracle.gemm_f32_rows(A, B, r, 1)[0] for r in rows])
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 2.0 ** -8)):
+        C = torch.full((M, N), float("nan"), dtype=dtype, device=cuda_device)
+        api.hgemm_fused(dA, dB, C, 1.0, 0.0)
+        torch.cuda.synchronize(cuda_device)
+        assert torch.isfinite(C).all()
+        got = C[rows].float().cpu().numpy()
+        assert np.abs(got - ref).max() / np.abs(ref).max() <= tol, dtype
+    assert api.last_device_error() == 0
 
 
 def test_fused_epilogue_error_codes(cuda_device):
@@ -620,7 +698,7 @@ def test_fused_epilogue_error_codes(cuda_device):
     with pytest.raises(_native.HgemmError) as e:
         api.hgemm_fused(to_dev(A2, cuda_device), to_dev(B2, cuda_device), C2, 2.0, 0.0)
     assert e.value.status == _native.ERR_UNSUPPORTED
-    epi = _native.Epilogue(1.0, 0.0, dA.data_ptr() + 2, None)  # bias not 16-byte aligned
+    epi = _native.Epilogue(1.0, 0.0, dA.data_ptr() + 2, None, _native.C_F16)  # bias not 16-byte aligned
     assert lib.b200_hgemm_fused(dA.data_ptr(), dB.data_ptr(), C.data_ptr(), 128, 128, 128, ctypes.byref(epi), None) == _native.ERR_MISALIGNED
     torch.cuda.synchronize(cuda_device)
 
