@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = (
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
     "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
     "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
-    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex",
+    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched",
 )
 
 OK = 0
@@ -97,6 +97,8 @@ def load() -> ctypes.CDLL:
     lib.b200_hgemm_fused_ex.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, POINTER(Epilogue),
                                         POINTER(Plan), c_void_p]
     lib.b200_hgemm_fused_ex.restype = c_int
+    lib.b200_hgemm_batched.argtypes = [c_void_p, c_void_p, c_void_p] + [c_size_t] * 7 + [c_void_p]
+    lib.b200_hgemm_batched.restype = c_int
     lib.b200_hgemm_host.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]
     lib.b200_hgemm_host.restype = c_int
     lib.b200_hgemm_host_a.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]

@@ -136,6 +136,31 @@ def hgemm_fused(A, B, C, alpha: float = 1.0, beta: float = 0.0, bias=None, c_in=
     return C
 
 
+def hgemm_batched(A, B, C):
+    """``C[i] = A[i] @ B[i].T`` for stacks ``A [batch, M, K]``, ``B [batch, N, K]`` (or one ``[N, K]`` matrix for all),
+    ``C [batch, M, N]`` (C ABI ``b200_hgemm_batched``). The innermost two dimensions must be contiguous; the
+    stack dimension may have any stride that is a multiple of 8 elements."""
+    import torch
+
+    for name, t in (("A", A), ("B", B), ("C", C)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.float16 or not t.is_cuda:
+            raise TypeError(f"{name} must be a float16 CUDA tensor")
+    if A.dim() != 3 or C.dim() != 3 or B.dim() not in (2, 3):
+        raise ValueError("A and C must be [batch, rows, cols]; B [batch, N, K] or [N, K]")
+    batch, M, K = A.shape
+    N = B.shape[-2]
+    if B.shape[-1] != K or tuple(C.shape) != (batch, M, N) or (B.dim() == 3 and B.shape[0] != batch):
+        raise ValueError("shape mismatch")
+    for name, t in (("A", A), ("B", B), ("C", C)):
+        if t.stride(-1) != 1 or t.stride(-2) != t.shape[-1]:
+            raise ValueError(f"the matrices of {name} must be contiguous")
+    stride_b = B.stride(0) if B.dim() == 3 else 0
+    with torch.cuda.device(A.device):
+        check(_native.load().b200_hgemm_batched(A.data_ptr(), B.data_ptr(), C.data_ptr(), int(M), int(N), int(K), int(batch),
+                                                int(A.stride(0)), int(stride_b), int(C.stride(0)), _stream_of(A)))
+    return C
+
+
 def hgemm_host(A_host, B_host, C_host):
     """HOST tensors in, HOST tensor out (C ABI ``b200_hgemm_host``): uploads, multiplies, downloads, synchronises."""
     import torch

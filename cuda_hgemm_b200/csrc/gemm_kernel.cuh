@@ -36,6 +36,11 @@ constexpr int kThreads = 192;     // 6 warps
 constexpr int kEpiThreads = 128;  // warps 2..5
 constexpr uint32_t kStagingBytes = 4u * 2u * 4096u;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
 
+// Bits of the kernels' FLAVOR template parameter.
+enum GemmFlavor : int {
+    kFlavorBatched = 1,  // operands are stacks of matrices: three-dimensional tensor maps, tile -> (matrix, tile)
+};
+
 enum GemmMode : int {
     kModeTiles = 0,    // every CTA walks whole tiles, strided by the grid
     kModeStreamK = 1,  // every CTA owns a contiguous range of (tile, k-block) units
@@ -77,6 +82,13 @@ struct alignas(64) GemmParams {
     const __half *bias;  // N values, one per column of C, or nullptr
     const void *c_in;    // M x N of C's element type, row-major, read when beta != 0 (may be C itself), or nullptr
     uint32_t c_type;     // OutType of C and c_in (kernels with the fused epilogue only; 0 = FP16)
+    // Tail of a launch with larger tiles (whole-tile mode only; tail_sm = 0: off). This launch's tile u is part
+    // u % (tail_sm * tail_sn) of the larger tile tail_first + u / (tail_sm * tail_sn), which is located with
+    // the larger tiles' own geometry and split tail_sm x tail_sn ways.
+    uint32_t tail_first, tail_sm, tail_sn, tail_m_blocks, tail_n_blocks, tail_group_m;
+    // Batched kernels (FLAVOR & kFlavorBatched): `tiles` counts the tiles of all matrices, m_blocks x n_blocks
+    // of them per matrix; the tensor maps are {columns, rows, matrices}.
+    uint64_t batch_stride_c;  // elements between consecutive matrices of C (plain-store path)
 #ifdef B200_TIMELINE
     unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
 #endif
@@ -155,6 +167,17 @@ struct WorkWalker<kModeStreamK> {
         return true;
     }
 };
+
+// Linear tile id of this launch -> block coordinates in this launch's own tile size.
+__device__ __forceinline__ TileCoord locate_tile(const GemmParams &p, uint32_t tile) {
+    if (p.tail_sm == 0) return tile_coord(tile, p.m_blocks, p.n_blocks, p.group_m);
+    const uint32_t per = p.tail_sm * p.tail_sn;
+    const uint32_t part = tile % per;
+    TileCoord c = tile_coord(p.tail_first + tile / per, p.tail_m_blocks, p.tail_n_blocks, p.tail_group_m);
+    c.m_blk = c.m_blk * p.tail_sm + part % p.tail_sm;
+    c.n_blk = c.n_blk * p.tail_sn + part / p.tail_sm;
+    return c;
+}
 
 // 32 FP32 accumulator columns of one row -> FP16 -> global memory.
 __device__ __forceinline__ void store_row_chunk32(__half *c, uint32_t row, uint32_t col0, uint32_t m, uint32_t n,
@@ -323,8 +346,10 @@ __device__ __forceinline__ void store_row_chunk32_typed(void *c, uint32_t c_type
 // decomposition count pairs of k-blocks (one stage each); a pair that reaches past K reads zeros there.
 // EPI: apply GemmParams' alpha / beta / bias in the epilogue and write C in GemmParams::c_type (tiles whose
 // k-range is cut leave FP32 partials as always; streamk_reduce_kernel applies the same epilogue to their sum).
-template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false>
+template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false, int FLAVOR = 0>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+    constexpr bool BATCHED = (FLAVOR & kFlavorBatched) != 0;
+    static_assert(!BATCHED || (MODE == kModeTiles && !EPI), "stacks of matrices are multiplied in whole tiles, plain epilogue");
     using T = KernelTraits<BN, STAGES, CG, KPS>;
     static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
 
@@ -408,7 +433,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
 #endif
             pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
             while (ok && work.next(seg)) {
-                const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
+                uint32_t zt = seg.tile;
+                int32_t z = 0;  // which matrix of the stack
+                if (BATCHED) {
+                    z = static_cast<int32_t>(zt / (p.m_blocks * p.n_blocks));
+                    zt -= static_cast<uint32_t>(z) * p.m_blocks * p.n_blocks;
+                }
+                const TileCoord tc = locate_tile(p, zt);
                 const int32_t row_a = static_cast<int32_t>((tc.m_blk * CG + cta_rank) * kBM);
                 const int32_t row_b = static_cast<int32_t>(tc.n_blk * BN + cta_rank * T::kBRows);
                 for (uint32_t kb = seg.kb0; kb < seg.kb1; ++kb) {
@@ -423,8 +454,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         for (uint32_t j = 0; j < KPS; ++j) {
                             const uint32_t sa = slot + j * T::kBlockBytes;
                             const int32_t kx = static_cast<int32_t>((kb * KPS + j) * kBK);  // past K: zero fill
-                            tma_load_2d(sa, &p.tm_a, kx, row_a, full_bar + 8u * stage);
-                            tma_load_2d(sa + T::kABytes, &p.tm_b, kx, row_b, full_bar + 8u * stage);
+                            if (BATCHED) {
+                                tma_load_3d(sa, &p.tm_a, kx, row_a, z, full_bar + 8u * stage);
+                                tma_load_3d(sa + T::kABytes, &p.tm_b, kx, row_b, z, full_bar + 8u * stage);
+                            } else {
+                                tma_load_2d(sa, &p.tm_a, kx, row_a, full_bar + 8u * stage);
+                                tma_load_2d(sa + T::kABytes, &p.tm_b, kx, row_b, full_bar + 8u * stage);
+                            }
                         }
                     } else {
                         // Both CTAs' copies complete on the leader's barrier; the leader alone
@@ -435,8 +471,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         for (uint32_t j = 0; j < KPS; ++j) {
                             const uint32_t sa = slot + j * T::kBlockBytes;
                             const int32_t kx = static_cast<int32_t>((kb * KPS + j) * kBK);
-                            tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
-                            tma_load_2d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, leader_bar);
+                            if (BATCHED) {
+                                tma_load_3d_pair(sa, &p.tm_a, kx, row_a, z, leader_bar);
+                                tma_load_3d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, z, leader_bar);
+                            } else {
+                                tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
+                                tma_load_2d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, leader_bar);
+                            }
                         }
                     }
                     if (++stage == STAGES) {
@@ -522,7 +563,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         while (work.next(seg)) {
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;
-            const TileCoord tc = tile_coord(seg.tile, p.m_blocks, p.n_blocks, p.group_m);
+            uint32_t zt = seg.tile;
+            int32_t z = 0;
+            if (BATCHED) {
+                z = static_cast<int32_t>(zt / (p.m_blocks * p.n_blocks));
+                zt -= static_cast<uint32_t>(z) * p.m_blocks * p.n_blocks;
+            }
+            const TileCoord tc = locate_tile(p, zt);
             const uint32_t m0 = (tc.m_blk * CG + cta_rank) * kBM;
             const uint32_t n0 = tc.n_blk * BN;
             // one lane per warp polls the barrier; the other 31 park at the warp barrier
@@ -578,8 +625,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                             fence_proxy_async_smem();
                             __syncwarp();
                             if (lane == 0) {
-                                tma_store_2d(&p.tm_c, my_staging + (store_buf & 1u) * 4096u,
-                                             static_cast<int32_t>(n0 + c * 64u), static_cast<int32_t>(m0 + q * 32u));
+                                if (BATCHED) {
+                                    tma_store_3d(&p.tm_c, my_staging + (store_buf & 1u) * 4096u,
+                                                 static_cast<int32_t>(n0 + c * 64u), static_cast<int32_t>(m0 + q * 32u), z);
+                                } else {
+                                    tma_store_2d(&p.tm_c, my_staging + (store_buf & 1u) * 4096u,
+                                                 static_cast<int32_t>(n0 + c * 64u), static_cast<int32_t>(m0 + q * 32u));
+                                }
                                 tma_store_commit();
                             }
                             ++store_buf;
@@ -595,7 +647,8 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                             fused_epilogue<32>(p, m0 + row_in_tile, n0 + c * 32u, r);
                             store_row_chunk32_typed(p.c, p.c_type, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
                         } else {
-                            store_row_chunk32(p.c, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
+                            __half *c_mat = BATCHED ? p.c + static_cast<size_t>(z) * p.batch_stride_c : p.c;
+                            store_row_chunk32(c_mat, m0 + row_in_tile, n0 + c * 32u, p.m, p.n, p.c_vec_ok != 0, r);
                         }
                     }
                 }

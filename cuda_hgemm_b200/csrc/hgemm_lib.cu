@@ -39,9 +39,10 @@ struct TensorMapKey {
     uint64_t rows, cols;
     uint32_t box_rows, box_cols;
     bool swizzle;
+    uint64_t batch, batch_stride;  // stacks of matrices: how many, and elements from one to the next (1, 0: a single matrix)
     bool operator==(const TensorMapKey &o) const {
         return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
-               swizzle == o.swizzle;
+               swizzle == o.swizzle && batch == o.batch && batch_stride == o.batch_stride;
     }
 };
 
@@ -166,10 +167,11 @@ static int current_state(DeviceState **out) {
 // tiles, without. Out-of-range elements read as zero and are dropped on store. The cache is 4-way
 // set-associative (64 sets): a handful of operands in rotation never evict each other.
 static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                          uint32_t box_cols, CUtensorMap *out, bool swizzle = true) {
-    TensorMapKey key{ptr, rows, cols, box_rows, box_cols, swizzle};
+                          uint32_t box_cols, CUtensorMap *out, bool swizzle = true, uint64_t batch = 1, uint64_t batch_stride = 0) {
+    TensorMapKey key{ptr, rows, cols, box_rows, box_cols, swizzle, batch, batch_stride};
     size_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
-    h ^= rows * 0xC2B2AE3D27D4EB4Full + cols * 0x165667B19E3779F9ull + box_rows * 131u + box_cols + (swizzle ? 0u : 77u);
+    h ^= rows * 0xC2B2AE3D27D4EB4Full + cols * 0x165667B19E3779F9ull + box_rows * 131u + box_cols + (swizzle ? 0u : 77u) +
+         batch * 0x9E3779B1ull + batch_stride * 0x85EBCA77ull;
     const size_t set = ((h >> 20) & 63u) * kTensorMapWays;
     std::lock_guard<std::mutex> lock(st.mu);
     TensorMapSlot *slot = nullptr;
@@ -185,11 +187,13 @@ static int get_tensor_map(DeviceState &st, const void *ptr, uint64_t rows, uint6
     }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return B200_HGEMM_ERR_CUDA;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * sizeof(__half)};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t elem_strides[2] = {1, 1};
-    CUresult r = enc(&slot->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box,
+    // a stack of matrices is a third dimension; a stack of one with stride 0 stays two-dimensional
+    const bool stacked = batch > 1 || batch_stride != 0;
+    cuuint64_t dims[3] = {cols, rows, batch};
+    cuuint64_t strides[2] = {cols * sizeof(__half), (batch_stride ? batch_stride : rows * cols) * sizeof(__half)};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t elem_strides[3] = {1, 1, 1};
+    CUresult r = enc(&slot->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, stacked ? 3 : 2, const_cast<void *>(ptr), dims, strides, box,
                      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -517,7 +521,13 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
             const uint64_t tiles_big = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 256);
             const uint64_t tiles_mc = static_cast<uint64_t>(ceil_div_u32(M, 512)) * ceil_div_u32(N, 512);
             const double f256 = fill(pairs256, pair_slots, 256.0 * 256.0);
-            const double fbig = fill(tiles_big, pair_slots, 512.0 * 256.0);
+            // left-over tiles that fit one wave as 256 x 256 halves run on the 128 x 256-per-CTA kernel behind the
+            // full waves (launch_big_with_tail): a little over half a wave's time instead of a whole one
+            const uint64_t big_rest = tiles_big % pair_slots;
+            const bool big_tail = tiles_big >= pair_slots && big_rest != 0 && 2 * big_rest <= pair_slots;
+            const double big_waves = big_tail ? static_cast<double>(tiles_big / pair_slots) + 0.55 : waves(tiles_big, pair_slots);
+            const double fbig = static_cast<double>(M) * static_cast<double>(N) /
+                                (big_waves * static_cast<double>(pair_slots) * 512.0 * 256.0);
             const double fmc = mc_launch_fn(512) ? fill(tiles_mc, sms / 4, 512.0 * 512.0) : 0.0;
             // what the larger tiles gain at equal fill grows with the length of the run (measured:
             // pairs +0.5 % at 4096^3, +4 % at 8192^3, +7 % at 16384^3; groups of four 2 % more)
@@ -586,10 +596,10 @@ static bool pdl_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false>
+template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false, int FLAVOR = 0>
 static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, uint32_t grid, cudaStream_t stream) {
     using T = KernelTraits<BN, STAGES, CG, KPS>;
-    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE, KPS, EPI>;
+    auto kern = hgemm_tcgen05_kernel<BN, STAGES, CG, MODE, KPS, EPI, FLAVOR>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -658,25 +668,22 @@ __global__ void __launch_bounds__(kBigThreads, 1) hgemm_tcgen05_big_epi_kernel(c
     hgemm_big_body<2, NoMulticastLoad, true>(p);
 }
 
-static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid, cudaStream_t stream, bool fused = false) {
+// Launch configuration of the kernel with 256 x 256 outputs per CTA (shared-memory opt-in done once).
+static int big_kernel_config(DeviceState &st, bool fused, cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs) {
     auto kern = fused ? hgemm_tcgen05_big_epi_kernel : hgemm_tcgen05_big_kernel;
-    const int kBigAttrSlot = fused ? 15 : 8;
-    if (!st.attr_set[kBigAttrSlot]) {
+    const int slot = fused ? 15 : 8;
+    if (!st.attr_set[slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
-        if (!st.attr_set[kBigAttrSlot]) {
+        if (!st.attr_set[slot]) {
             if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBigSmemBytes), "cudaFuncSetAttribute")) {
                 return B200_HGEMM_ERR_CUDA;
             }
-            st.attr_set[kBigAttrSlot] = true;
+            st.attr_set[slot] = true;
         }
     }
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kBigThreads, 1, 1);
-    cfg.dynamicSmemBytes = kBigSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attrs[2];
+    memset(cfg, 0, sizeof(*cfg));
+    cfg->blockDim = dim3(kBigThreads, 1, 1);
+    cfg->dynamicSmemBytes = kBigSmemBytes;
     int n_attrs = 0;
     if (pdl_enabled()) {
         attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -688,21 +695,44 @@ static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid
     attrs[n_attrs].val.clusterDim.y = 1;
     attrs[n_attrs].val.clusterDim.z = 1;
     ++n_attrs;
-    cfg.attrs = attrs;
-    cfg.numAttrs = n_attrs;
-    if (st.max_clusters[kBigAttrSlot] == 0) {
+    cfg->attrs = attrs;
+    cfg->numAttrs = n_attrs;
+    return B200_HGEMM_OK;
+}
+
+// CTA pairs of that kernel the device keeps resident at once (74 on a B200), asked for once.
+static int big_kernel_pair_slots(DeviceState &st, bool fused, uint32_t *slots) {
+    const int slot = fused ? 15 : 8;
+    if (st.max_clusters[slot] == 0) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attrs[2];
+        const int rc = big_kernel_config(st, fused, &cfg, attrs);
+        if (rc != B200_HGEMM_OK) return rc;
+        cfg.gridDim = dim3(2u * static_cast<uint32_t>(st.sm_count > 1 ? st.sm_count / 2 : 1), 1, 1);
         int n = 0;
+        auto kern = fused ? hgemm_tcgen05_big_epi_kernel : hgemm_tcgen05_big_kernel;
         if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
             cudaGetLastError();
             return B200_HGEMM_ERR_CUDA;
         }
         std::lock_guard<std::mutex> lock(st.mu);
-        st.max_clusters[kBigAttrSlot] = n;
+        st.max_clusters[slot] = n;
     }
-    if (grid / 2 > static_cast<uint32_t>(st.max_clusters[kBigAttrSlot])) {
-        grid = 2u * static_cast<uint32_t>(st.max_clusters[kBigAttrSlot]);
-        cfg.gridDim = dim3(grid, 1, 1);
-    }
+    *slots = static_cast<uint32_t>(st.max_clusters[slot]);
+    return B200_HGEMM_OK;
+}
+
+static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid, cudaStream_t stream, bool fused = false) {
+    auto kern = fused ? hgemm_tcgen05_big_epi_kernel : hgemm_tcgen05_big_kernel;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attrs[2];
+    int rc = big_kernel_config(st, fused, &cfg, attrs);
+    if (rc != B200_HGEMM_OK) return rc;
+    uint32_t slots = 0;
+    if ((rc = big_kernel_pair_slots(st, fused, &slots)) != B200_HGEMM_OK) return rc;
+    if (grid / 2 > slots) grid = 2u * slots;  // a persistent grid must be fully resident
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.stream = stream;
     if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, p), "cudaLaunchKernelEx")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
@@ -1033,6 +1063,40 @@ static int check_args(const void *A, const void *B, const void *C, size_t M, siz
     return B200_HGEMM_OK;
 }
 
+// 512 x 256 tiles on CTA pairs, and what is left of them after the full waves.
+//
+// With T tiles on S resident pairs the last wave holds T % S tiles and costs as much as a full one. When
+// those left-over tiles, cut into two 256 x 256 halves each, fit one wave of the 128 x 256-per-CTA pair
+// kernel (2 * (T % S) <= S), that kernel takes them in a second launch right behind the first: half a
+// wave's time instead of a whole one. A row slab of 2048 x 16384 (one of eight GPUs' share of 16384^3)
+// has 256 tiles on 74 pairs: 3 full waves and 34 tiles, i.e. 3.5 waves' time instead of 4. The second
+// launch reads the same tensor maps (its boxes are the same) and finds its tiles through the larger
+// tiles' raster (GemmParams::tail_*), so both launches together write every element of C exactly once.
+static int launch_big_with_tail(DeviceState &st, const GemmParams &p, uint32_t grid, cudaStream_t stream, bool fused,
+                                bool fixed_grid) {
+    uint32_t slots = 0;
+    int rc = big_kernel_pair_slots(st, fused, &slots);
+    if (rc != B200_HGEMM_OK) return rc;
+    const uint32_t full = (p.tiles / slots) * slots, rest = p.tiles - full;
+    static const bool tail_off = (getenv("B200_HGEMM_NO_TAIL_SPLIT") != nullptr);
+    if (tail_off || fixed_grid || full == 0 || rest == 0 || 2u * rest > slots) return launch_big_kernel(st, p, grid, stream, fused);
+    GemmParams head = p;
+    head.tiles = full;
+    if ((rc = launch_big_kernel(st, head, grid, stream, fused)) != B200_HGEMM_OK) return rc;
+    GemmParams tail = p;
+    tail.tail_first = full;
+    tail.tail_sm = 2;
+    tail.tail_sn = 1;
+    tail.tail_m_blocks = p.m_blocks;
+    tail.tail_n_blocks = p.n_blocks;
+    tail.tail_group_m = p.group_m;
+    tail.m_blocks = ceil_div_u32(p.m, 256);
+    tail.tiles = 2u * rest;
+    const uint32_t tail_grid = 2u * tail.tiles;
+    if (fused) return launch_kernel<256, 6, 2, kModeTiles, 1, true>(st, 19, tail, tail_grid, stream);
+    return launch_kernel<256, 6, 2, kModeTiles>(st, 3, tail, tail_grid, stream);
+}
+
 static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                     const b200_hgemm_plan &pl, cudaStream_t stream, void *ws_override, size_t ws_override_bytes,
                     uint32_t *error_word_override = nullptr, const b200_hgemm_epilogue *epi = nullptr) {
@@ -1162,7 +1226,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
             if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2, true>(st, 17, p, grid, stream);
             return launch_kernel<64, 4, 1, kModeTiles, 2, true>(st, 18, p, grid, stream);
         }
-        if (big) return launch_big_kernel(st, p, grid, stream, true);
+        if (big) return launch_big_with_tail(st, p, grid, stream, true, pl.grid > 0);
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles, 1, true>(st, 19, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2, true>(st, 22, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2, true>(st, 20, p, grid, stream);
@@ -1173,7 +1237,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2>(st, 1, p, grid, stream);
         return launch_kernel<64, 4, 1, kModeTiles, 2>(st, 2, p, grid, stream);
     }
-    if (big) return launch_big_kernel(st, p, grid, stream);
+    if (big) return launch_big_with_tail(st, p, grid, stream, false, pl.grid > 0);
     if (pl.variant == B200_VARIANT_CTA2) {
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
@@ -1444,6 +1508,88 @@ int b200_hgemm_streamk_static(const void *A, const void *B, void *C, size_t M, s
 
 int b200_hgemm_simt(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
     return entry(A, B, C, M, N, K, nullptr, B200_VARIANT_SIMT, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---- stacks of matrices -------------------------------------------------------------------
+// One launch for `batch` products of the same shape: the whole-tile kernels with three-dimensional
+// tensor maps ({columns, rows, matrices}) and tile ids that run over all matrices, so that small
+// products fill the GPU together. The tile is chosen by the shape of one product and by how many
+// tiles the stack has in total.
+static int run_batched(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, size_t batch,
+                       size_t stride_a, size_t stride_b, size_t stride_c, cudaStream_t stream) {
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u) {
+        return B200_HGEMM_ERR_MISALIGNED;
+    }
+    if ((stride_a | stride_b | stride_c) % 8 != 0) return B200_HGEMM_ERR_MISALIGNED;  // every matrix 16-byte aligned
+    const uint32_t sms = st.sm_count > 0 ? static_cast<uint32_t>(st.sm_count) : 148u;
+    const uint64_t m_blocks128 = ceil_div_u32(M, 128);
+    // pairs on 256 x 256 when one product alone has rows for them and the stack fills the pairs twice over;
+    // else single CTAs on the widest tile that still gives every SM one
+    const uint64_t pair_tiles = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 256) * batch;
+    int cg = 1, bn = 256;
+    if (M > 128 && N > 128 && pair_tiles >= sms) {
+        cg = 2;
+    } else {
+        while (bn > 64 && (N <= static_cast<size_t>(bn) / 2 || m_blocks128 * ceil_div_u32(N, bn) * batch < sms)) bn /= 2;
+    }
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.c = static_cast<__half *>(C);
+    p.error_word = st.error_word;
+    p.m = static_cast<uint32_t>(M);
+    p.n = static_cast<uint32_t>(N);
+    p.k = static_cast<uint32_t>(K);
+    p.m_blocks = ceil_div_u32(M, 128u * cg);
+    p.n_blocks = ceil_div_u32(N, bn);
+    const uint32_t kps = (cg == 1 && bn != 256) ? 2u : 1u;
+    p.k_blocks = ceil_div_u32(K, 64u * kps);
+    const uint64_t tiles = static_cast<uint64_t>(p.m_blocks) * p.n_blocks * batch;
+    if (tiles > 0x7fffffffull || batch > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
+    p.tiles = static_cast<uint32_t>(tiles);
+    p.group_m = p.m_blocks < 16u ? p.m_blocks : 16u;
+    p.tma_store = (N % 8 == 0) ? 1u : 0u;
+    p.c_vec_ok = p.tma_store;
+    p.batch_stride_c = stride_c;
+    int rc = get_tensor_map(st, A, M, K, 128, 64, &p.tm_a, true, batch, stride_a);
+    if (rc != B200_HGEMM_OK) return rc;
+    if ((rc = get_tensor_map(st, B, N, K, static_cast<uint32_t>(bn / cg), 64, &p.tm_b, true, batch, stride_b)) != B200_HGEMM_OK) return rc;
+    if (p.tma_store && (rc = get_tensor_map(st, C, M, N, 32, 64, &p.tm_c, true, batch, stride_c)) != B200_HGEMM_OK) return rc;
+    const uint32_t max_workers = static_cast<uint32_t>(st.sm_count) / cg;
+    const uint32_t grid = (p.tiles < max_workers ? p.tiles : max_workers) * cg;
+    if (cg == 2) return launch_kernel<256, 6, 2, kModeTiles, 1, false, kFlavorBatched>(st, 50, p, grid, stream);
+    if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles, 1, false, kFlavorBatched>(st, 51, p, grid, stream);
+    if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2, false, kFlavorBatched>(st, 52, p, grid, stream);
+    return launch_kernel<64, 4, 1, kModeTiles, 2, false, kFlavorBatched>(st, 53, p, grid, stream);
+}
+
+int b200_hgemm_batched(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, size_t batch, size_t stride_a,
+                       size_t stride_b, size_t stride_c, b200_stream_t stream) {
+    if (batch == 0) return B200_HGEMM_ERR_INVALID_ARG;
+    int rc = check_args(A, B, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    // matrices of a stack may share B (stride 0) but must not overlap otherwise
+    if (stride_a < M * K || stride_c < M * N || (stride_b != 0 && stride_b < N * K)) {
+        if (batch > 1) return B200_HGEMM_ERR_INVALID_ARG;
+    }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (batch == 1) return entry(A, B, C, M, N, K, nullptr, -1, s);
+    // one B for the whole stack and A, C densely stacked: that is one product with batch * M rows
+    if (stride_b == 0 && stride_a == M * K && stride_c == M * N) return entry(A, B, C, batch * M, N, K, nullptr, -1, s);
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    if (K % 8 != 0 || stride_b == 0) {
+        // no tensor map for these rows (K % 8 != 0), or a shared B under A and C that are not densely stacked:
+        // one product after the other on the stream
+        for (size_t i = 0; i < batch; ++i) {
+            rc = entry(static_cast<const __half *>(A) + i * stride_a, static_cast<const __half *>(B) + i * stride_b,
+                       static_cast<__half *>(C) + i * stride_c, M, N, K, nullptr, -1, s);
+            if (rc != B200_HGEMM_OK) return rc;
+        }
+        return B200_HGEMM_OK;
+    }
+    return run_batched(*st, A, B, C, M, N, K, batch, stride_a, stride_b, stride_c, s);
 }
 
 int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, const b200_hgemm_plan *plan,

@@ -218,6 +218,33 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *tm, uint32_t sme
                  : "memory");
 }
 
+// Three-dimensional forms for batched operands viewed as {columns, rows, matrices}: z picks the matrix.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap *tm, int32_t x, int32_t y, int32_t z,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap *tm, int32_t x, int32_t y, int32_t z,
+                                                 uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
+        "%3, %4}], [%5];"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(cluster_bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, uint32_t smem_src, int32_t x, int32_t y, int32_t z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

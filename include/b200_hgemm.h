@@ -146,6 +146,15 @@ int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, 
 int b200_hgemm_fused_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                         const b200_hgemm_epilogue *epilogue, const b200_hgemm_plan *plan, b200_stream_t stream);
 
+/* `batch` products of one shape in one call: C_i = A_i * B_i with A_i = A + i * stride_a (strides in elements,
+ * multiples of 8; matrices must not overlap), likewise B_i and C_i; stride_b = 0 multiplies every A_i by the
+ * same B. The reference has no counterpart (no batch, no strides: src/main.cu:11, src/cublas_tensor_op.cu:22-24).
+ * Stacks run as ONE launch of the whole-tile kernels over three-dimensional tensor maps, so that many small
+ * products fill the GPU together; a shared B under densely stacked A and C is simply one product of
+ * batch * M rows; what fits neither (K % 8 != 0, a shared B with gaps between the A_i) runs product by product. */
+int b200_hgemm_batched(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, size_t batch,
+                       size_t stride_a, size_t stride_b, size_t stride_c, b200_stream_t stream);
+
 /* HOST-pointer GEMM: copies A and B to the device, runs b200_hgemm, copies C back and
  * synchronises. This is the path of reference Matrix (src/common/matrix.h:23-35 upload,
  * :83-85 moveToHost) + one kernel call, behind one entry point. Returns after C_host is complete. */

@@ -162,6 +162,8 @@ BIG_TILE_SHAPES = [
     (2560, 2304, 512),   # several tiles per worker: tensor memory handed back and forth
     (6144, 5120, 576),   # more tiles than workers on every arrangement
     (520, 264, 8200),    # long k, 129 k-blocks
+    (1300, 6656, 200),   # 78 pair tiles: one full wave of 74, the other four as eight 256 x 256 halves behind it; ragged M
+    (2048, 16384, 320),  # one of eight row slabs of 16384^2: three full waves and 34 tiles as 68 halves
 ]
 
 
@@ -613,6 +615,7 @@ FUSED_PLAN_CASES = [
     # M, N, K, variant, bn, parts, tma_store
     (1024, 2048, 1024, _native.VARIANT_CTA2, 512, 0, 1),      # 256 x 256 outputs per CTA, several tiles per CTA
     (600, 776, 136, _native.VARIANT_CTA2, 512, 0, 1),         # the same with tails in M, N and K
+    (1300, 6656, 200, _native.VARIANT_CTA2, 512, 0, 1),       # a full wave and a tail of half tiles on the other pair kernel
     (384, 512, 320, _native.VARIANT_CTA1, 192, 0, 1),
     (600, 776, 520, _native.VARIANT_CTA2, 192, 0, 1),
     (200, 1032, 1096, _native.VARIANT_STREAMK, 128, 33, 1),   # whole and cut tiles in one launch
@@ -945,3 +948,63 @@ def test_decode_shapes_at_full_size(cuda_device, M, NK):
     assert api.last_device_error() == 0
     ref = oracle.gemm_f32(dA.cpu().numpy(), dB.cpu().numpy())
     assert_close_to_oracle(C.cpu().numpy(), ref, f"decode {M}x{N}x{K} plan {api.select_plan(M, N, K).as_dict()}")
+
+
+# ---- stacks of matrices ---------------------------------------------------------------------
+BATCHED_CASES = [
+    # batch, M, N, K, gap in elements between consecutive matrices (0 = dense), B shared?
+    (5, 200, 264, 136, 0, False),      # tails in M, N and K
+    (64, 128, 128, 64, 0, False),      # many one-tile products, one k-block each
+    (40, 512, 512, 128, 0, False),     # enough 256 x 256 tiles for CTA pairs
+    (7, 96, 1000, 520, 4096, False),   # gaps between the matrices
+    (3, 100, 100, 64, 8, False),       # N % 8 != 0: plain stores
+    (6, 48, 512, 256, 0, True),        # one B for the whole stack, A and C dense: one product of batch * M rows
+    (4, 64, 256, 128, 1024, True),     # one B, gaps in A and C: product by product
+    (3, 40, 48, 100, 0, False),        # K % 8 != 0: product by product on the CUDA-core kernel
+    (1, 256, 256, 256, 0, False),
+]
+
+
+@pytest.mark.parametrize("case", BATCHED_CASES, ids=lambda c: f"b{c[0]}-" + "x".join(map(str, c[1:4])) + f"-gap{c[4]}" + ("-sharedB" if c[5] else ""))
+def test_batched_products(cuda_device, case):
+    """b200_hgemm_batched: every matrix of the stack against the oracle; the gaps between matrices stay untouched."""
+    import torch
+
+    batch, M, N, K, gap, shared_b = case
+    rng = np.random.default_rng(71)
+    A = rng.uniform(-1, 1, size=(batch, M, K)).astype(np.float16)
+    B = rng.uniform(-1, 1, size=((1 if shared_b else batch), N, K)).astype(np.float16)
+
+    def stack(x, rows, cols, fill):
+        flat = torch.full((x.shape[0] * (rows * cols + gap),), fill, dtype=torch.float16, device=cuda_device)
+        view = torch.as_strided(flat, (x.shape[0], rows, cols), (rows * cols + gap, cols, 1))
+        view.copy_(torch.from_numpy(x).to(cuda_device))
+        return flat, view
+
+    _, dA = stack(A, M, K, 0.0)
+    dB = torch.from_numpy(B[0]).to(cuda_device) if shared_b else stack(B, N, K, 0.0)[1]
+    c_flat, dC = stack(np.zeros((batch, M, N), dtype=np.float16), M, N, float("nan"))
+    dC.fill_(float("nan"))
+    api.hgemm_batched(dA, dB, dC)
+    torch.cuda.synchronize(cuda_device)
+    assert api.last_device_error() == 0
+    got = dC.cpu().numpy()
+    for i in range(batch):
+        assert_close_to_oracle(got[i], oracle.gemm_f32(A[i], B[0 if shared_b else i]), f"batched {case} matrix {i}")
+    if gap:
+        gaps = torch.as_strided(c_flat, (batch, gap), (M * N + gap, 1), storage_offset=M * N)
+        assert torch.isnan(gaps).all(), "the call wrote between the matrices of C"
+
+
+def test_batched_products_refuse_overlapping_or_misaligned_stacks(cuda_device):
+    import torch
+
+    lib = _native.load()
+    buf = torch.zeros(1 << 20, dtype=torch.float16, device=cuda_device)
+    p = buf.data_ptr()
+    M = N = K = 64
+    dense = M * K
+    assert lib.b200_hgemm_batched(p, p, p, M, N, K, 0, dense, dense, dense, None) == _native.ERR_INVALID_ARG
+    assert lib.b200_hgemm_batched(p, p, p, M, N, K, 4, dense - 8, dense, dense, None) == _native.ERR_INVALID_ARG   # A_i overlap
+    assert lib.b200_hgemm_batched(p, p, p, M, N, K, 4, dense, dense, dense + 4, None) == _native.ERR_MISALIGNED    # C_i off 16 bytes
+    torch.cuda.synchronize()
