@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = (
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
     "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
     "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
-    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched",
+    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched", "b200_hgemm_bkn",
 )
 
 OK = 0
@@ -86,7 +86,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIB_PATH))
     gemm_args = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p]
     for name in ("b200_hgemm", "b200_hgemm_cta1", "b200_hgemm_cta2", "b200_hgemm_splitk", "b200_hgemm_streamk",
-                 "b200_hgemm_simt", "b200_hgemm_streamk_static"):
+                 "b200_hgemm_simt", "b200_hgemm_streamk_static", "b200_hgemm_bkn"):
         fn = getattr(lib, name)
         fn.argtypes = gemm_args
         fn.restype = c_int

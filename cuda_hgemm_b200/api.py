@@ -136,6 +136,22 @@ def hgemm_fused(A, B, C, alpha: float = 1.0, beta: float = 0.0, bias=None, c_in=
     return C
 
 
+def hgemm_bkn(A, B_kn, C):
+    """``C = A @ B_kn`` with ``B_kn`` stored ``[K, N]`` row-major (C ABI ``b200_hgemm_bkn``): no transpose is made."""
+    import torch
+
+    for name, t in (("A", A), ("B_kn", B_kn), ("C", C)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.float16 or not t.is_cuda or not t.is_contiguous() or t.dim() != 2:
+            raise TypeError(f"{name} must be a contiguous 2-D float16 CUDA tensor")
+    M, K = A.shape
+    Kb, N = B_kn.shape
+    if Kb != K or tuple(C.shape) != (M, N):
+        raise ValueError("shape mismatch")
+    with torch.cuda.device(A.device):
+        check(_native.load().b200_hgemm_bkn(A.data_ptr(), B_kn.data_ptr(), C.data_ptr(), int(M), int(N), int(K), _stream_of(A)))
+    return C
+
+
 def hgemm_batched(A, B, C):
     """``C[i] = A[i] @ B[i].T`` for stacks ``A [batch, M, K]``, ``B [batch, N, K]`` (or one ``[N, K]`` matrix for all),
     ``C [batch, M, N]`` (C ABI ``b200_hgemm_batched``). The innermost two dimensions must be contiguous; the

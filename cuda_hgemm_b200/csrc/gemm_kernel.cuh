@@ -39,6 +39,8 @@ constexpr uint32_t kStagingBytes = 4u * 2u * 4096u;  // 4 epilogue warps x 2 buf
 // Bits of the kernels' FLAVOR template parameter.
 enum GemmFlavor : int {
     kFlavorBatched = 1,  // operands are stacks of matrices: three-dimensional tensor maps, tile -> (matrix, tile)
+    kFlavorBkn = 2,      // B is stored K x N row-major (N contiguous): tm_b is {N, K} with box {64, 64}; the B slab of
+                         // a stage is BN / CG / 64 such boxes, an MN-major operand of the MMA
 };
 
 enum GemmMode : int {
@@ -349,6 +351,8 @@ __device__ __forceinline__ void store_row_chunk32_typed(void *c, uint32_t c_type
 template <int BN, int STAGES, int CG, int MODE, int KPS = 1, bool EPI = false, int FLAVOR = 0>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     constexpr bool BATCHED = (FLAVOR & kFlavorBatched) != 0;
+    constexpr bool BKN = (FLAVOR & kFlavorBkn) != 0;
+    static_assert(!BKN || (!BATCHED && BN % (64 * CG) == 0), "K x N row-major B: whole 64-column boxes per CTA, single matrices");
     static_assert(!BATCHED || (MODE == kModeTiles && !EPI), "stacks of matrices are multiplied in whole tiles, plain epilogue");
     using T = KernelTraits<BN, STAGES, CG, KPS>;
     static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
@@ -454,7 +458,14 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         for (uint32_t j = 0; j < KPS; ++j) {
                             const uint32_t sa = slot + j * T::kBlockBytes;
                             const int32_t kx = static_cast<int32_t>((kb * KPS + j) * kBK);  // past K: zero fill
-                            if (BATCHED) {
+                            if (BKN) {
+                                tma_load_2d(sa, &p.tm_a, kx, row_a, full_bar + 8u * stage);
+#pragma unroll
+                                for (uint32_t g = 0; g < T::kBRows / 64u; ++g) {  // x = column of B (of C), y = k
+                                    tma_load_2d(sa + T::kABytes + g * 8192u, &p.tm_b, row_b + static_cast<int32_t>(g * 64u), kx,
+                                                full_bar + 8u * stage);
+                                }
+                            } else if (BATCHED) {
                                 tma_load_3d(sa, &p.tm_a, kx, row_a, z, full_bar + 8u * stage);
                                 tma_load_3d(sa + T::kABytes, &p.tm_b, kx, row_b, z, full_bar + 8u * stage);
                             } else {
@@ -471,7 +482,14 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                         for (uint32_t j = 0; j < KPS; ++j) {
                             const uint32_t sa = slot + j * T::kBlockBytes;
                             const int32_t kx = static_cast<int32_t>((kb * KPS + j) * kBK);
-                            if (BATCHED) {
+                            if (BKN) {
+                                tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
+#pragma unroll
+                                for (uint32_t g = 0; g < T::kBRows / 64u; ++g) {
+                                    tma_load_2d_pair(sa + T::kABytes + g * 8192u, &p.tm_b, row_b + static_cast<int32_t>(g * 64u), kx,
+                                                     leader_bar);
+                                }
+                            } else if (BATCHED) {
                                 tma_load_3d_pair(sa, &p.tm_a, kx, row_a, z, leader_bar);
                                 tma_load_3d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, z, leader_bar);
                             } else {
@@ -498,7 +516,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc = umma_idesc_f16_f32(kBM * CG, BN);
+            constexpr uint32_t idesc = BKN ? umma_idesc_f16_f32_b_mn(kBM * CG, BN) : umma_idesc_f16_f32(kBM * CG, BN);
             WorkWalker<MODE> work(p, worker, workers);
             Segment seg;
             uint32_t stage = 0, phase = 0, it = 0;
@@ -522,11 +540,14 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
 #pragma unroll
                     for (uint32_t j = 0; j < KPS; ++j) {
                         const uint64_t da = umma_smem_desc_sw128(slot + j * T::kBlockBytes);
-                        const uint64_t db = umma_smem_desc_sw128(slot + j * T::kBlockBytes + T::kABytes);
+                        const uint64_t db = BKN ? umma_smem_desc_sw128_mn(slot + j * T::kBlockBytes + T::kABytes, 8192u)
+                                                : umma_smem_desc_sw128(slot + j * T::kBlockBytes + T::kABytes);
 #pragma unroll
                         for (uint32_t k = 0; k < kBK / 16; ++k) {
-                            // 16 halves = 32 bytes along K inside the swizzle atom -> +2 in the address field
-                            umma_f16<CG>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > seg.kb0 || j > 0 || k > 0) ? 1u : 0u);
+                            // 16 halves = 32 bytes along K inside the swizzle atom -> +2 in the address field; for
+                            // the MN-major B, 16 rows of k = two atoms of 1024 bytes -> +128
+                            umma_f16<CG>(d_tmem, da + 2u * k, db + (BKN ? 128u : 2u) * k, idesc,
+                                         (kb > seg.kb0 || j > 0 || k > 0) ? 1u : 0u);
                         }
                     }
                     if (CG == 1) {

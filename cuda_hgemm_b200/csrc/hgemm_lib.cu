@@ -1562,6 +1562,69 @@ static int run_batched(DeviceState &st, const void *A, const void *B, void *C, s
     return launch_kernel<64, 4, 1, kModeTiles, 2, false, kFlavorBatched>(st, 53, p, grid, stream);
 }
 
+// ---- B stored K x N row-major -----------------------------------------------------------------
+// The whole-tile kernels with B as an MN-major operand of the MMA (FLAVOR kFlavorBkn): the tile is the
+// dispatch's choice for the shape mapped onto single CTAs of 64 / 128 / 256 columns or pairs on 256 x 128 /
+// 256 x 256.
+static int run_bkn(DeviceState &st, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, cudaStream_t stream) {
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u) {
+        return B200_HGEMM_ERR_MISALIGNED;
+    }
+    if (K % 8 != 0 || N % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // row pitches of A (K halves) and of B, C (N halves)
+    b200_hgemm_plan pl;
+    select_plan(st, M, N, K, &pl, false);
+    int cg = 1, bn = 256;
+    if (pl.variant == B200_VARIANT_CTA2 || pl.variant == B200_VARIANT_CTA2_MCAST) {
+        cg = 2;
+        bn = pl.bn == 128 ? 128 : 256;
+    } else if (pl.variant == B200_VARIANT_CTA1 || plan_cuts_k(pl)) {
+        bn = pl.bn == 192 ? 256 : pl.bn;
+    } else {  // decode-like shapes: narrow single-CTA tiles spread N over the SMs
+        bn = ceil_div_u32(N, 128) * 2 >= static_cast<uint32_t>(st.sm_count) ? 128 : 64;
+    }
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.c = static_cast<__half *>(C);
+    p.error_word = st.error_word;
+    p.m = static_cast<uint32_t>(M);
+    p.n = static_cast<uint32_t>(N);
+    p.k = static_cast<uint32_t>(K);
+    p.m_blocks = ceil_div_u32(M, 128u * cg);
+    p.n_blocks = ceil_div_u32(N, bn);
+    const uint32_t kps = ((cg == 1 && bn != 256) || (cg == 2 && bn == 128)) ? 2u : 1u;
+    p.k_blocks = ceil_div_u32(K, 64u * kps);
+    const uint64_t tiles = static_cast<uint64_t>(p.m_blocks) * p.n_blocks;
+    if (tiles > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
+    p.tiles = static_cast<uint32_t>(tiles);
+    p.group_m = cg == 2 ? 8u : 16u;
+    if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
+    p.tma_store = 1;
+    p.c_vec_ok = 1;
+    int rc = get_tensor_map(st, A, M, K, 128, 64, &p.tm_a);
+    if (rc != B200_HGEMM_OK) return rc;
+    if ((rc = get_tensor_map(st, B, K, N, 64, 64, &p.tm_b)) != B200_HGEMM_OK) return rc;  // K rows of N halves, boxes of 64 x 64
+    if ((rc = get_tensor_map(st, C, M, N, 32, 64, &p.tm_c)) != B200_HGEMM_OK) return rc;
+    const uint32_t max_workers = static_cast<uint32_t>(st.sm_count) / cg;
+    const uint32_t grid = (p.tiles < max_workers ? p.tiles : max_workers) * cg;
+    if (cg == 2) {
+        if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles, 1, false, kFlavorBkn>(st, 54, p, grid, stream);
+        return launch_kernel<128, 4, 2, kModeTiles, 2, false, kFlavorBkn>(st, 55, p, grid, stream);
+    }
+    if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles, 1, false, kFlavorBkn>(st, 56, p, grid, stream);
+    if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2, false, kFlavorBkn>(st, 57, p, grid, stream);
+    return launch_kernel<64, 4, 1, kModeTiles, 2, false, kFlavorBkn>(st, 58, p, grid, stream);
+}
+
+int b200_hgemm_bkn(const void *A, const void *B_kn, void *C, size_t M, size_t N, size_t K, b200_stream_t stream) {
+    int rc = check_args(A, B_kn, C, M, N, K);
+    if (rc != B200_HGEMM_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = current_state(&st);
+    if (rc != B200_HGEMM_OK) return rc;
+    if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
+    return run_bkn(*st, A, B_kn, C, M, N, K, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int b200_hgemm_batched(const void *A, const void *B, void *C, size_t M, size_t N, size_t K, size_t batch, size_t stride_a,
                        size_t stride_b, size_t stride_c, b200_stream_t stream) {
     if (batch == 0) return B200_HGEMM_ERR_INVALID_ARG;

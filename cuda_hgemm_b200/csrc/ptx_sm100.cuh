@@ -317,6 +317,21 @@ __host__ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_
     return d;
 }
 
+// The same for an MN-major operand: 64 consecutive elements along the operand's row index are contiguous
+// (one 128-byte line) and consecutive k sit 128 bytes apart, as TMA writes a box of {64 columns, 64 rows} of
+// a K x N row-major matrix. An atom is 8 k-rows of 128 bytes; atoms follow each other every 1024 bytes
+// along k (the stride field) and every `mn_stride_bytes` along the row index (the leading field), which is
+// the size of one such box. Stepping 16 along K (two atoms) adds 2048 bytes = 128 to the address field.
+__host__ __device__ __forceinline__ uint64_t umma_smem_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_stride_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((mn_stride_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
 // Instruction descriptor for kind::f16: FP16 A and B (both K-major), FP32 accumulate.
 //   bits [4,6)   D format (1 = F32)
 //   bits [7,10)  A format (0 = F16)      bits [10,13) B format (0 = F16)
@@ -324,6 +339,10 @@ __host__ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_
 //   bits [17,23) N >> 3                  bits [24,29) M >> 4
 __host__ __device__ constexpr uint32_t umma_idesc_f16_f32(uint32_t m, uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// The same with the B operand MN-major (bit 16).
+__host__ __device__ constexpr uint32_t umma_idesc_f16_f32_b_mn(uint32_t m, uint32_t n) {
+    return umma_idesc_f16_f32(m, n) | (1u << 16);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.

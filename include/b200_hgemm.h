@@ -146,6 +146,13 @@ int b200_hgemm_fused(const void *A, const void *B, void *C, size_t M, size_t N, 
 int b200_hgemm_fused_ex(const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
                         const b200_hgemm_epilogue *epilogue, const b200_hgemm_plan *plan, b200_stream_t stream);
 
+/* The same product with B stored the other way round: B_kn is K rows of N contiguous halves (row-major K x N,
+ * element (k, n) at B_kn[k*N + n]), as frameworks keep a weight matrix that is applied as x @ W. The reference
+ * only has the K-contiguous form (src/common/tester.h:117-119, src/cublas_tensor_op.cu:22-24: OP_T on B). No copy
+ * or transpose is made: TMA stages boxes of 64 k x 64 n and the MMA reads them as an MN-major operand. Runs on
+ * the whole-tile kernels (single CTAs and CTA pairs); needs K % 8 == 0 and N % 8 == 0. */
+int b200_hgemm_bkn(const void *A, const void *B_kn, void *C, size_t M, size_t N, size_t K, b200_stream_t stream);
+
 /* `batch` products of one shape in one call: C_i = A_i * B_i with A_i = A + i * stride_a (strides in elements,
  * multiples of 8; matrices must not overlap), likewise B_i and C_i; stride_b = 0 multiplies every A_i by the
  * same B. The reference has no counterpart (no batch, no strides: src/main.cu:11, src/cublas_tensor_op.cu:22-24).

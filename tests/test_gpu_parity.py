@@ -1008,3 +1008,38 @@ def test_batched_products_refuse_overlapping_or_misaligned_stacks(cuda_device):
     assert lib.b200_hgemm_batched(p, p, p, M, N, K, 4, dense - 8, dense, dense, None) == _native.ERR_INVALID_ARG   # A_i overlap
     assert lib.b200_hgemm_batched(p, p, p, M, N, K, 4, dense, dense, dense + 4, None) == _native.ERR_MISALIGNED    # C_i off 16 bytes
     torch.cuda.synchronize()
+
+
+# ---- B stored K x N row-major -----------------------------------------------------------------
+@pytest.mark.parametrize("shape", [
+    (128, 64, 64), (128, 256, 64), (128, 256, 128), (256, 256, 256), (384, 512, 320), (200, 264, 136), (16, 1024, 512),
+    (100, 14336, 256), (1024, 1024, 1024), (2304, 2560, 512), (4096, 4096, 1024), (520, 264, 8200),
+], ids=lambda s: "x".join(map(str, s)))
+def test_b_stored_k_by_n_row_major(cuda_device, shape):
+    """b200_hgemm_bkn: B as K rows of N halves, read by the MMA as an MN-major operand; the same bits as the
+    K-contiguous form on the transposed copy when both run the same tiles, the oracle's tolerance always."""
+    import torch
+
+    M, N, K = shape
+    A, B = make_inputs(M, N, K, seed=81)          # B is [N, K]
+    B_kn = np.ascontiguousarray(B.T)              # the same matrix stored [K, N]
+    dA, dB = to_dev(A, cuda_device), to_dev(B_kn, cuda_device)
+    flat = poisoned(M, N, cuda_device, extra_rows=4)
+    C = flat[: M * N].view(M, N)
+    api.hgemm_bkn(dA, dB, C)
+    torch.cuda.synchronize(cuda_device)
+    assert api.last_device_error() == 0
+    assert (flat[M * N:].view(torch.int16).cpu().numpy() == POISON).all()
+    assert_close_to_oracle(C.cpu().numpy(), oracle.gemm_f32(A, B), f"B as K x N {shape}")
+
+
+def test_b_stored_k_by_n_refuses_row_pitches_tma_cannot_take(cuda_device):
+    import torch
+
+    lib = _native.load()
+    buf = torch.zeros(1 << 16, dtype=torch.float16, device=cuda_device)
+    p = buf.data_ptr()
+    assert lib.b200_hgemm_bkn(p, p, p, 64, 60, 64, None) == _native.ERR_UNSUPPORTED
+    assert lib.b200_hgemm_bkn(p, p, p, 64, 64, 60, None) == _native.ERR_UNSUPPORTED
+    assert lib.b200_hgemm_bkn(p, p + 2, p, 64, 64, 64, None) == _native.ERR_MISALIGNED
+    torch.cuda.synchronize()
