@@ -53,7 +53,7 @@ MULTICAST_OFF, MULTICAST_ON, MULTICAST_LOCKED_OFF = 0, 1, 2
 class Plan(Structure):
     """Mirror of ``b200_hgemm_plan``."""
     _fields_ = [("variant", c_int32), ("bn", c_int32), ("parts", c_int32), ("group_m", c_int32),
-                ("tma_store", c_int32), ("grid", c_int32)]
+                ("tma_store", c_int32), ("grid", c_int32), ("stages", c_int32)]
 
     def as_dict(self):
         return {name: int(getattr(self, name)) for name, _ in self._fields_}

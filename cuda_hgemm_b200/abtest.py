@@ -9,7 +9,7 @@ does instead (a short run after an idle pause, before the power cap bites).
     python -m cuda_hgemm_b200.abtest --shape 8192x8192x8192 \
         --plans auto,cta2:256,cta1:256:g16,cta1:128,streamk:128,mcast:256
 
-A plan is ``variant:bn[:gN][:pN][:nt]`` with variant one of cta1, cta2, streamk, hybrid, mcast, skinny, simt;
+A plan is ``variant:bn[:gN][:pN][:sN][:nt]`` with variant one of cta1, cta2, streamk, hybrid, mcast, skinny, simt;
 ``gN`` sets the rasterisation band height, ``pN`` the number of stream-k ranges, ``nt`` turns the
 TMA-store epilogue off. ``auto`` is the library's own choice.
 """
@@ -38,6 +38,8 @@ def parse_plan(text: str) -> _native.Plan:
             plan.group_m = int(extra[1:])
         elif extra.startswith("p"):
             plan.parts = int(extra[1:])
+        elif extra.startswith("s"):
+            plan.stages = int(extra[1:])
         elif extra == "nt":
             plan.tma_store = 0
         else:

@@ -335,7 +335,14 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
     const bool short_a = pl.variant == B200_VARIANT_SKINNY || pl.variant == B200_VARIANT_SKINNY_PAIR;
     if (pl.tma_store && N % 8 != 0 && !short_a) return B200_HGEMM_ERR_UNSUPPORTED;  // (the short-A kernels then store by element)
-    if (pl.parts < 0 || pl.group_m < 0 || pl.grid < 0) return B200_HGEMM_ERR_INVALID_ARG;
+    if (pl.parts < 0 || pl.group_m < 0 || pl.grid < 0 || pl.stages < 0) return B200_HGEMM_ERR_INVALID_ARG;
+    if (pl.stages != 0) {
+        // ring depths other than the default exist for the whole-tile kernels only: the default or one or two less
+        const int def = pl.variant == B200_VARIANT_CTA1 ? (pl.bn == 128 ? 3 : pl.bn == 192 ? 0 : 4)
+                        : pl.variant == B200_VARIANT_CTA2 ? (pl.bn == 256 ? 6 : pl.bn == 128 ? 4 : 0) : 0;
+        const int least = (pl.variant == B200_VARIANT_CTA2 && pl.bn == 256) ? 4 : def - 1;
+        if (def == 0 || pl.stages > def || pl.stages < least) return B200_HGEMM_ERR_UNSUPPORTED;
+    }
     return B200_HGEMM_OK;
 }
 
@@ -367,7 +374,7 @@ static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, 
 // ------------------------------------------------------------------------------------------
 // tuned plans: shapes whose best plan was measured (autotune.py) override the rules below
 // ------------------------------------------------------------------------------------------
-// A text file, one line per shape: "M N K variant bn parts group_m tma_store"; '#' starts a comment.
+// A text file, one line per shape: "M N K variant bn parts group_m tma_store [stages]"; '#' starts a comment.
 // It is read once, from B200_HGEMM_PLAN_TABLE if that is set, else from plan_table.txt in the
 // directory above the one this library lies in (the package directory); B200_HGEMM_NO_PLAN_TABLE
 // turns it off; b200_hgemm_load_plan_table() replaces it at run time. An entry that the
@@ -389,8 +396,8 @@ static int read_plan_table(const char *path, std::vector<TunedPlan> *out) {
         char *hash = strchr(line, '#');
         if (hash) *hash = 0;
         unsigned long long m, n, k;
-        int variant, bn, parts, group_m, tma_store;
-        if (sscanf(line, "%llu %llu %llu %d %d %d %d %d", &m, &n, &k, &variant, &bn, &parts, &group_m, &tma_store) != 8) continue;
+        int variant, bn, parts, group_m, tma_store, stages = 0;
+        if (sscanf(line, "%llu %llu %llu %d %d %d %d %d %d", &m, &n, &k, &variant, &bn, &parts, &group_m, &tma_store, &stages) < 8) continue;
         TunedPlan t;
         t.m = m;
         t.n = n;
@@ -401,6 +408,7 @@ static int read_plan_table(const char *path, std::vector<TunedPlan> *out) {
         t.plan.parts = parts;
         t.plan.group_m = group_m;
         t.plan.tma_store = tma_store;
+        t.plan.stages = stages;
         out->push_back(t);
         ++entries;
     }
@@ -1232,6 +1240,10 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         return launch_kernel<128, 4, 2, kModeTiles, 2, true>(st, 20, p, grid, stream);
     }
     if (pl.variant == B200_VARIANT_CTA1) {
+        // a plan may ask for a shallower ring than the default (plan.stages; the autotuner's knob)
+        if (bn == 256 && pl.stages == 3) return launch_kernel<256, 3, 1, kModeTiles>(st, 59, p, grid, stream);
+        if (bn == 128 && pl.stages == 2) return launch_kernel<128, 2, 1, kModeTiles, 2>(st, 60, p, grid, stream);
+        if (bn == 64 && pl.stages == 3) return launch_kernel<64, 3, 1, kModeTiles, 2>(st, 61, p, grid, stream);
         if (bn == 256) return launch_kernel<256, 4, 1, kModeTiles>(st, 0, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 4, 1, kModeTiles>(st, 9, p, grid, stream);
         if (bn == 128) return launch_kernel<128, 3, 1, kModeTiles, 2>(st, 1, p, grid, stream);
@@ -1239,6 +1251,9 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     }
     if (big) return launch_big_with_tail(st, p, grid, stream, false, pl.grid > 0);
     if (pl.variant == B200_VARIANT_CTA2) {
+        if (bn == 256 && pl.stages == 4) return launch_kernel<256, 4, 2, kModeTiles>(st, 62, p, grid, stream);
+        if (bn == 256 && pl.stages == 5) return launch_kernel<256, 5, 2, kModeTiles>(st, 63, p, grid, stream);
+        if (bn == 128 && pl.stages == 3) return launch_kernel<128, 3, 2, kModeTiles, 2>(st, 30, p, grid, stream);
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);

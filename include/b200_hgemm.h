@@ -78,6 +78,9 @@ typedef struct b200_hgemm_plan {
     int32_t group_m;   /* rasterisation band height in row blocks; 0 = library default */
     int32_t tma_store; /* 1: epilogue writes C with TMA stores (needs N % 8 == 0); 0: plain stores */
     int32_t grid;      /* CTA1/CTA2: CTAs launched (0 = min(tiles, SMs)); informational for STREAMK */
+    int32_t stages;    /* CTA1/CTA2: depth of the operand ring; 0 = the kernel's default (its deepest). Shallower
+                        * rings exist for measurements and the autotuner: CTA1 bn 256: 3, bn 128: 2, bn 64: 3;
+                        * CTA2 bn 256: 4 or 5, bn 128: 3; anything else is B200_HGEMM_ERR_UNSUPPORTED */
 } b200_hgemm_plan;
 
 /* ---- compute entry points: each replaces one reference HGEMM_FUNC symbol ----------------
@@ -179,7 +182,7 @@ int b200_hgemm_host_a(const void *A_host, const void *B_device, void *C_host, si
 int b200_hgemm_select(size_t M, size_t N, size_t K, b200_hgemm_plan *plan);
 
 /* Tuned plans. b200_hgemm_select() (and so b200_hgemm) first looks the shape up in a table of measured
- * plans, a text file with one "M N K variant bn parts group_m tma_store" line per shape that
+ * plans, a text file with one "M N K variant bn parts group_m tma_store [stages]" line per shape that
  * `python -m cuda_hgemm_b200.autotune` writes: B200_HGEMM_PLAN_TABLE if set, else plan_table.txt in the
  * directory above the library's; B200_HGEMM_NO_PLAN_TABLE=1 disables it. This call replaces the table at run
  * time (NULL: empty table) and returns the number of entries read, or a negative status.

@@ -153,6 +153,29 @@ def test_cluster_multicast_pairs(cuda_device, multicast_on, shape):
     assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
 
 
+@pytest.mark.parametrize("variant,bn,stages", [
+    (_native.VARIANT_CTA1, 256, 3), (_native.VARIANT_CTA1, 128, 2), (_native.VARIANT_CTA1, 64, 3),
+    (_native.VARIANT_CTA2, 256, 4), (_native.VARIANT_CTA2, 256, 5), (_native.VARIANT_CTA2, 128, 3),
+], ids=lambda v: str(v))
+def test_shallower_operand_rings(cuda_device, variant, bn, stages):
+    """plan.stages: the whole-tile kernels with a ring one or two stages short of their default; same bits."""
+    import torch
+
+    M, N, K = 600, 776, 1096   # 18 k-blocks: several trips round every ring; tails in M, N and K
+    A, B = make_inputs(M, N, K, seed=14)
+    plan = plan_of(variant, bn)
+    plan.stages = stages
+    C = run(None, A, B, cuda_device, plan)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"variant {variant} bn {bn} stages {stages}")
+    assert np.array_equal(C.view(np.uint16), run(None, A, B, cuda_device, plan_of(variant, bn)).view(np.uint16))
+    lib = _native.load()
+    bad = plan_of(variant, bn)
+    bad.stages = 9
+    dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
+    dC = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+    assert lib.b200_hgemm_ex(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), M, N, K, ctypes.byref(bad), None) == _native.ERR_UNSUPPORTED
+
+
 BIG_TILE_SHAPES = [
     (512, 256, 64),      # one pair tile, one k-block
     (512, 512, 256),     # one tile for a group of four, the ring of 4 stages exactly once
