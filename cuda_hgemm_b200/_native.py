@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = (
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
     "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
     "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
-    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched", "b200_hgemm_bkn",
+    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched", "b200_hgemm_bkn", "b200_hgemm_host_a_after",
 )
 
 OK = 0
@@ -44,6 +44,7 @@ VARIANT_CTA2_MCAST = 4
 VARIANT_SKINNY = 5
 VARIANT_HYBRID = 6
 VARIANT_SKINNY_PAIR = 7
+VARIANT_HYBRID_PAIR = 8
 
 C_F16, C_BF16, C_F32 = 0, 1, 2
 
@@ -103,6 +104,8 @@ def load() -> ctypes.CDLL:
     lib.b200_hgemm_host.restype = c_int
     lib.b200_hgemm_host_a.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]
     lib.b200_hgemm_host_a.restype = c_int
+    lib.b200_hgemm_host_a_after.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p]
+    lib.b200_hgemm_host_a_after.restype = c_int
     lib.b200_hgemm_select.argtypes = [c_size_t, c_size_t, c_size_t, POINTER(Plan)]
     lib.b200_hgemm_select.restype = c_int
     lib.b200_hgemm_select_untuned.argtypes = [c_size_t, c_size_t, c_size_t, POINTER(Plan)]

@@ -24,7 +24,7 @@ from . import _native, api
 from .timing import cublas_callable, load_compare, time_burst, time_graph, time_launches
 
 VARIANTS = {"cta1": _native.VARIANT_CTA1, "cta2": _native.VARIANT_CTA2, "streamk": _native.VARIANT_STREAMK,
-            "simt": _native.VARIANT_SIMT, "mcast": _native.VARIANT_CTA2_MCAST, "skinny": _native.VARIANT_SKINNY, "skinny2": _native.VARIANT_SKINNY_PAIR, "hybrid": _native.VARIANT_HYBRID}
+            "simt": _native.VARIANT_SIMT, "mcast": _native.VARIANT_CTA2_MCAST, "skinny": _native.VARIANT_SKINNY, "skinny2": _native.VARIANT_SKINNY_PAIR, "hybrid2": _native.VARIANT_HYBRID_PAIR, "hybrid": _native.VARIANT_HYBRID}
 
 
 def parse_plan(text: str) -> _native.Plan:

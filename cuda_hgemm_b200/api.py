@@ -192,9 +192,11 @@ def hgemm_host(A_host, B_host, C_host):
     return C_host
 
 
-def hgemm_host_a(A_host, B_dev, C_host):
+def hgemm_host_a(A_host, B_dev, C_host, upload_after=None, gemm_after=None):
     """HOST ``A`` in, HOST ``C`` out, ``B`` already on the GPU (C ABI ``b200_hgemm_host_a``); the current stream's
-    work on ``B_dev`` must be complete (this call synchronises that stream first)."""
+    work on ``B_dev`` must be complete (this call synchronises that stream first). With ``upload_after`` /
+    ``gemm_after`` (``torch.cuda.Event`` objects already recorded; C ABI ``b200_hgemm_host_a_after``) nothing is
+    synchronised up front: A's uploads start behind the first event and the multiplies behind the second."""
     import torch
 
     for name, t in (("A", A_host), ("C", C_host)):
@@ -207,8 +209,14 @@ def hgemm_host_a(A_host, B_dev, C_host):
     if Kb != K or tuple(C_host.shape) != (M, N):
         raise ValueError("shape mismatch")
     with torch.cuda.device(B_dev.device):
-        torch.cuda.current_stream().synchronize()
-        check(_native.load().b200_hgemm_host_a(A_host.data_ptr(), B_dev.data_ptr(), C_host.data_ptr(), int(M), int(N), int(K)))
+        if upload_after is None and gemm_after is None:
+            torch.cuda.current_stream().synchronize()
+            check(_native.load().b200_hgemm_host_a(A_host.data_ptr(), B_dev.data_ptr(), C_host.data_ptr(), int(M), int(N), int(K)))
+        else:
+            check(_native.load().b200_hgemm_host_a_after(
+                A_host.data_ptr(), B_dev.data_ptr(), C_host.data_ptr(), int(M), int(N), int(K),
+                upload_after.cuda_event if upload_after is not None else None,
+                gemm_after.cuda_event if gemm_after is not None else None))
     return C_host
 
 

@@ -355,7 +355,6 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     static_assert(!BKN || (!BATCHED && BN % (64 * CG) == 0), "K x N row-major B: whole 64-column boxes per CTA, single matrices");
     static_assert(!BATCHED || (MODE == kModeTiles && !EPI), "stacks of matrices are multiplied in whole tiles, plain epilogue");
     using T = KernelTraits<BN, STAGES, CG, KPS>;
-    static_assert(!(MODE == kModeStreamK && CG != 1), "split k-ranges are implemented for single-CTA tiles");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -685,8 +684,9 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 }
             } else {
                 // ---- this tile's k-range is shared with other workers: publish an FP32 partial
+                // (a pair's slot holds 256 x BN values; each CTA writes the half that belongs to its 128 rows)
                 const uint32_t slot = partial_slot(worker, p.sk_parts, p.tiles - p.dp_tiles, p.k_blocks, seg.tile - p.dp_tiles);
-                float4 *ws = p.partials + static_cast<size_t>(slot) * (kBM * BN / 4);
+                float4 *ws = p.partials + (static_cast<size_t>(slot) * CG + cta_rank) * (kBM * BN / 4);
                 const bool row_live = (m0 + row_in_tile) < p.m;
 #pragma unroll 1
                 for (uint32_t c = 0; c < BN / 32; ++c) {
@@ -705,7 +705,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 }
                 tcgen05_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar + 8u * acc);
+                if (lane == 0) {
+                    if (CG == 1) {
+                        mbar_arrive(tempty_bar + 8u * acc);
+                    } else {
+                        mbar_arrive_cluster(map_to_cta(tempty_bar + 8u * acc, 0));
+                    }
+                }
 
                 // the partial tiles of all ranges are summed by streamk_reduce_kernel, launched next
             }
@@ -755,6 +761,7 @@ struct ReduceParams {
     uint32_t dp_tiles;  // tiles the GEMM kernel walked whole; the k-ranges cover tiles [dp_tiles, tiles)
     uint32_t parts;
     uint32_t bn;
+    uint32_t cg;        // 1: tiles of 128 rows; 2: pair tiles of 256 rows (each slot holds the two CTAs' halves one after the other)
     uint32_t fused;     // 1: apply `epi` to the sums and write C in epi.c_type; 0: plain FP16
     EpilogueArgs epi;
 };
@@ -773,7 +780,9 @@ __global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const Re
     if (part_first == part_last) return;
 
     const TileCoord tc = tile_coord(tile, p.m_blocks, p.n_blocks, p.group_m);
-    const uint32_t m0 = tc.m_blk * kBM, n0 = tc.n_blk * p.bn;
+    const uint32_t half = blockIdx.z;  // which CTA's 128 rows of a pair tile (always 0 for single-CTA tiles)
+    const uint32_t m0 = (tc.m_blk * p.cg + half) * kBM, n0 = tc.n_blk * p.bn;
+    if (m0 >= p.m) return;
     const uint32_t rows_live = (p.m - m0) < static_cast<uint32_t>(kBM) ? (p.m - m0) : kBM;
     const uint32_t cols_left = p.n - n0;
     const uint32_t words_per_row = ((cols_left < p.bn ? cols_left : p.bn) + 3u) / 4u;
@@ -788,16 +797,16 @@ __global__ void __launch_bounds__(kReduceThreads) streamk_reduce_kernel(const Re
     for (uint32_t i = blockIdx.x * kReduceThreads + threadIdx.x; i < total_words; i += gridDim.x * kReduceThreads) {
         const uint32_t w = i / rows_live, r = i - w * rows_live;
         const size_t off = static_cast<size_t>(w) * kBM + r;
-        float4 acc = ld_cg_f4(p.partials + static_cast<size_t>(slot_first) * slot_words + off);
+        float4 acc = ld_cg_f4(p.partials + (static_cast<size_t>(slot_first) * p.cg + half) * slot_words + off);
         uint32_t k = 1;
         for (; k + 1 < n_parts; k += 2) {  // two loads in flight per step
-            const float4 v0 = ld_cg_f4(p.partials + static_cast<size_t>(2u * (part_first + k)) * slot_words + off);
-            const float4 v1 = ld_cg_f4(p.partials + static_cast<size_t>(2u * (part_first + k + 1)) * slot_words + off);
+            const float4 v0 = ld_cg_f4(p.partials + (static_cast<size_t>(2u * (part_first + k)) * p.cg + half) * slot_words + off);
+            const float4 v1 = ld_cg_f4(p.partials + (static_cast<size_t>(2u * (part_first + k + 1)) * p.cg + half) * slot_words + off);
             acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
             acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
         }
         if (k < n_parts) {
-            const float4 v0 = ld_cg_f4(p.partials + static_cast<size_t>(2u * (part_first + k)) * slot_words + off);
+            const float4 v0 = ld_cg_f4(p.partials + (static_cast<size_t>(2u * (part_first + k)) * p.cg + half) * slot_words + off);
             acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
         }
         const uint32_t col = n0 + w * 4u;

@@ -300,9 +300,15 @@ static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) {
     return static_cast<uint32_t>((a + b - 1) / b);
 }
 
-// STREAMK and HYBRID run the same kernel; HYBRID walks the full waves of tiles whole first.
+// STREAMK and HYBRID run the same kernel; HYBRID walks the full waves of tiles whole first. HYBRID_PAIR is
+// HYBRID on CTA pairs (256-row tiles).
 static bool plan_cuts_k(const b200_hgemm_plan &pl) {
-    return pl.variant == B200_VARIANT_STREAMK || pl.variant == B200_VARIANT_HYBRID;
+    return pl.variant == B200_VARIANT_STREAMK || pl.variant == B200_VARIANT_HYBRID || pl.variant == B200_VARIANT_HYBRID_PAIR;
+}
+
+// CTAs that work on one tile together.
+static int plan_cg(const b200_hgemm_plan &pl) {
+    return (pl.variant == B200_VARIANT_CTA2 || pl.variant == B200_VARIANT_HYBRID_PAIR) ? 2 : 1;
 }
 
 static bool plan_is_tensor(const b200_hgemm_plan &pl) {
@@ -332,6 +338,7 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
         return B200_HGEMM_ERR_UNSUPPORTED;
     }
     if (pl.variant == B200_VARIANT_CTA2 && pl.bn == 64) return B200_HGEMM_ERR_UNSUPPORTED;
+    if (pl.variant == B200_VARIANT_HYBRID_PAIR && pl.bn != 128 && pl.bn != 256) return B200_HGEMM_ERR_UNSUPPORTED;
     if (K % 8 != 0) return B200_HGEMM_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
     const bool short_a = pl.variant == B200_VARIANT_SKINNY || pl.variant == B200_VARIANT_SKINNY_PAIR;
     if (pl.tma_store && N % 8 != 0 && !short_a) return B200_HGEMM_ERR_UNSUPPORTED;  // (the short-A kernels then store by element)
@@ -354,6 +361,7 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
 // and the M = 128 decode shape from 3.8 to 4.2 TB/s. The kernels count k in stages, so everything
 // that cuts k-ranges (stream-k ranges, workspace sizes) counts the same units.
 static uint32_t plan_kps(const b200_hgemm_plan &pl) {
+    if (pl.variant == B200_VARIANT_HYBRID_PAIR) return pl.bn == 128 ? 2u : 1u;
     if (pl.variant == B200_VARIANT_CTA1 || plan_cuts_k(pl)) return (pl.bn == 128 || pl.bn == 64) ? 2u : 1u;
     if (pl.variant == B200_VARIANT_CTA2) return (pl.bn == 128 || pl.bn == 192) ? 2u : 1u;
     return 1u;
@@ -365,7 +373,7 @@ static uint32_t plan_k_units(const b200_hgemm_plan &pl, size_t K) {
 
 static uint32_t streamk_parts(const b200_hgemm_plan &pl, const DeviceState &st, uint32_t tiles, uint32_t k_blocks) {
     uint64_t units = static_cast<uint64_t>(tiles) * k_blocks;
-    uint64_t parts = pl.parts > 0 ? static_cast<uint64_t>(pl.parts) : static_cast<uint64_t>(st.sm_count);
+    uint64_t parts = pl.parts > 0 ? static_cast<uint64_t>(pl.parts) : static_cast<uint64_t>(st.sm_count / plan_cg(pl));
     if (parts > units) parts = units;
     if (parts < 1) parts = 1;
     return static_cast<uint32_t>(parts);
@@ -654,7 +662,8 @@ static int launch_kernel(DeviceState &st, int attr_slot, const GemmParams &p, ui
             std::lock_guard<std::mutex> lock(st.mu);
             st.max_clusters[attr_slot] = n;
         }
-        if (grid / 2 > static_cast<uint32_t>(st.max_clusters[attr_slot])) {
+        // (k-ranges are handed out by CTA index: that grid is launched as it is; none of its CTAs waits for another)
+        if (MODE == kModeTiles && grid / 2 > static_cast<uint32_t>(st.max_clusters[attr_slot])) {
             grid = 2u * static_cast<uint32_t>(st.max_clusters[attr_slot]);
             cfg.gridDim = dim3(grid, 1, 1);
         }
@@ -751,9 +760,10 @@ static int launch_big_kernel(DeviceState &st, const GemmParams &p, uint32_t grid
 
 static size_t plan_workspace_bytes(const DeviceState &st, size_t M, size_t N, size_t K, const b200_hgemm_plan &pl) {
     if (!plan_cuts_k(pl)) return 0;
-    const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, pl.bn);
+    const uint32_t cg = static_cast<uint32_t>(plan_cg(pl));
+    const uint32_t tiles = ceil_div_u32(M, 128u * cg) * ceil_div_u32(N, pl.bn);
     const uint32_t parts = streamk_parts(pl, st, tiles, plan_k_units(pl, K));
-    return kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * pl.bn * sizeof(float));
+    return kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * cg * pl.bn * sizeof(float));
 }
 
 constexpr size_t kMaxStreamWorkspaces = 64;
@@ -1153,7 +1163,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return B200_HGEMM_OK;
     }
-    const int cg = (pl.variant == B200_VARIANT_CTA2) ? 2 : 1;
+    const int cg = plan_cg(pl);
     const bool big = pl.variant == B200_VARIANT_CTA2 && pl.bn == 512;  // 512 x 256 per pair
     const int bn = big ? 256 : pl.bn;
 
@@ -1205,10 +1215,10 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (p.tiles > kMaxCountedTiles) return B200_HGEMM_ERR_UNSUPPORTED;
         const uint32_t parts = streamk_parts(pl, st, p.tiles, p.k_blocks);
         // HYBRID: every full wave of tiles is walked whole; only the rest is cut into k-ranges
-        if (pl.variant == B200_VARIANT_HYBRID) p.dp_tiles = (p.tiles / parts) * parts;
+        if (pl.variant == B200_VARIANT_HYBRID || pl.variant == B200_VARIANT_HYBRID_PAIR) p.dp_tiles = (p.tiles / parts) * parts;
         const uint64_t cut_units = static_cast<uint64_t>(p.tiles - p.dp_tiles) * p.k_blocks;
         p.sk_parts = cut_units < parts ? static_cast<uint32_t>(cut_units) : parts;  // no empty k-range
-        const size_t need = kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * bn * sizeof(float));
+        const size_t need = kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * cg * bn * sizeof(float));
         uint8_t *ws = nullptr;
         if (ws_override) {
             if (ws_override_bytes < need) return B200_HGEMM_ERR_WORKSPACE;
@@ -1218,7 +1228,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
             if (rc != B200_HGEMM_OK) return rc;
         }
         p.partials = reinterpret_cast<float4 *>(ws + kCounterBytes);
-        grid = parts;
+        grid = parts * cg;
     } else {
         const uint32_t max_workers = (cg == 2) ? static_cast<uint32_t>(st.sm_count / 2) : static_cast<uint32_t>(st.sm_count);
         uint32_t workers = pl.grid > 0 ? static_cast<uint32_t>(pl.grid) / cg : max_workers;
@@ -1258,7 +1268,14 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);
     }
-    if (epi) {  // whole tiles get the epilogue in the kernel, cut tiles in the reduction below
+    if (pl.variant == B200_VARIANT_HYBRID_PAIR) {
+        if (epi) return B200_HGEMM_ERR_UNSUPPORTED;
+        if (bn == 256) {
+            rc = launch_kernel<256, 6, 2, kModeStreamK>(st, 31, p, grid, stream);
+        } else {
+            rc = launch_kernel<128, 4, 2, kModeStreamK, 2>(st, 36, p, grid, stream);
+        }
+    } else if (epi) {  // whole tiles get the epilogue in the kernel, cut tiles in the reduction below
         if (bn == 256) {
             rc = launch_kernel<256, 4, 1, kModeStreamK, 1, true>(st, 23, p, grid, stream);
         } else if (bn == 128) {
@@ -1299,6 +1316,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     rp.group_m = p.group_m;
     rp.parts = parts;
     rp.bn = static_cast<uint32_t>(bn);
+    rp.cg = static_cast<uint32_t>(cg);
     rp.fused = epi ? 1u : 0u;
     rp.epi = ea;
     // One or two 16-byte words per thread: the sum over ranges is a chain of dependent-latency
@@ -1308,7 +1326,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     if (chunks < 1) chunks = 1;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(chunks, cut_tiles, 1);
+    cfg.gridDim = dim3(chunks, cut_tiles, static_cast<unsigned>(cg));
     cfg.blockDim = dim3(kReduceThreads, 1, 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr;
@@ -1682,7 +1700,7 @@ int b200_hgemm_ex(const void *A, const void *B, void *C, size_t M, size_t N, siz
 static int fused_plan(const DeviceState &st, size_t M, size_t N, size_t K, int c_type, b200_hgemm_plan *pl) {
     select_plan(st, M, N, K, pl);
     if (pl->variant == B200_VARIANT_SIMT) return B200_HGEMM_ERR_UNSUPPORTED;  // K % 8 != 0
-    if (pl->variant == B200_VARIANT_CTA2_MCAST) pl->variant = B200_VARIANT_CTA2;
+    if (pl->variant == B200_VARIANT_CTA2_MCAST || pl->variant == B200_VARIANT_HYBRID_PAIR) pl->variant = B200_VARIANT_CTA2;
     if (pl->variant == B200_VARIANT_CTA2 && pl->bn == 512 && c_type == B200_C_F32) pl->bn = 256;
     return B200_HGEMM_OK;
 }
@@ -1916,7 +1934,11 @@ static int grow(void **ptr, size_t *have, size_t need) {
 }
 
 // A and C on the host; B on the host (b_on_device = false: uploaded first) or already on the device.
-static int host_pipeline(const void *A_host, const void *B_any, void *C_host, size_t M, size_t N, size_t K, bool b_on_device) {
+// upload_after / gemm_after (b_on_device only, either may be null): events the caller recorded; A's first upload
+// waits for the one, the first multiply for the other, so that the uploads of A can run while B is still being
+// completed on the device (e.g. by an exchange between GPUs).
+static int host_pipeline(const void *A_host, const void *B_any, void *C_host, size_t M, size_t N, size_t K, bool b_on_device,
+                         cudaEvent_t upload_after = nullptr, cudaEvent_t gemm_after = nullptr) {
     const void *B_host = B_any;
     int rc = check_args(A_host, B_any, C_host, M, N, K);
     if (rc != B200_HGEMM_OK) return rc;
@@ -1965,6 +1987,8 @@ static int host_pipeline(const void *A_host, const void *B_any, void *C_host, si
         if (!cuda_ok(cudaMemcpyAsync(st->host_b, B_host, b_bytes, cudaMemcpyHostToDevice, s_up), "cudaMemcpyAsync")) return B200_HGEMM_ERR_CUDA;
         b_dev = st->host_b;
     }
+    if (upload_after && !cuda_ok(cudaStreamWaitEvent(s_up, upload_after, 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
+    if (gemm_after && !cuda_ok(cudaStreamWaitEvent(s_run, gemm_after, 0), "cudaStreamWaitEvent")) return B200_HGEMM_ERR_CUDA;
     size_t slabs = 1;
     if (M >= 2048 && M % 128 == 0) {
         slabs = M >= 16384 ? 16 : M >= 8192 ? 8 : 4;
@@ -2007,6 +2031,13 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
 int b200_hgemm_host_a(const void *A_host, const void *B_device, void *C_host, size_t M, size_t N, size_t K) {
     if (reinterpret_cast<uintptr_t>(B_device) & 15u) return B200_HGEMM_ERR_MISALIGNED;
     return host_pipeline(A_host, B_device, C_host, M, N, K, true);
+}
+
+int b200_hgemm_host_a_after(const void *A_host, const void *B_device, void *C_host, size_t M, size_t N, size_t K,
+                            b200_event_t upload_after, b200_event_t gemm_after) {
+    if (reinterpret_cast<uintptr_t>(B_device) & 15u) return B200_HGEMM_ERR_MISALIGNED;
+    return host_pipeline(A_host, B_device, C_host, M, N, K, true, reinterpret_cast<cudaEvent_t>(upload_after),
+                         reinterpret_cast<cudaEvent_t>(gemm_after));
 }
 
 // ---- several GPUs from one process ----------------------------------------------------------

@@ -161,8 +161,14 @@ def slab_hgemm_host(A_host_slab, B_host, C_host_slab, B_dev, group=None):
     rank = dist.get_rank(group)
     lo, hi = share_of_b(B_host.shape[0], rank, world)
     B_dev[lo:hi].copy_(B_host[lo:hi], non_blocking=True)
+    share_up = torch.cuda.Event()
+    share_up.record()                      # this rank's share of B is on its way over the host link
     exchange_b(B_dev, rank, world, group)
+    b_complete = torch.cuda.Event()
+    b_complete.record()                    # ... and behind this, all of B is on the device
     if A_host_slab.shape[0] == 0:
         torch.cuda.current_stream().synchronize()
         return C_host_slab
-    return api.hgemm_host_a(A_host_slab, B_dev, C_host_slab)
+    # the rows of A follow the share of B over the host link while the other shares arrive over NVLink;
+    # the multiplies wait for the exchange
+    return api.hgemm_host_a(A_host_slab, B_dev, C_host_slab, upload_after=share_up, gemm_after=b_complete)

@@ -1,7 +1,7 @@
 """Regenerates the Nsight Compute summaries under ``profiles/``: one command per capture, one markdown file each.
 
     python -m cuda_hgemm_b200.profile --list
-    python -m cuda_hgemm_b200.profile [--only NAME[,NAME...]] [--out profiles] [--raw DIR]
+    python -m cuda_hgemm_b200.profile [--only NAME[,NAME...]] [--out profiles] [--raw DIR] [--summarise-only]
 
 The counterpart of the reference's profiling wrapper (reference run_sample.sh:23-27, one ``ncu`` line kept in a
 comment there). Every capture runs its target once WITHOUT ncu first and goes on only if that exits 0; ncu then
@@ -141,14 +141,9 @@ def summarise_launch_list(title, plain_cmd, ncu_cmd, launches):
     return "\n".join(out) + "\n"
 
 
-def run_capture(name, out_dir: Path, raw_dir: Path) -> int:
+def run_capture(name, out_dir: Path, raw_dir: Path, summarise_only: bool = False) -> int:
     title, target, regex, skip, count, shape = CAPTURES[name]
     raw_dir.mkdir(parents=True, exist_ok=True)
-    plain = subprocess.run(target, cwd=ROOT, capture_output=True, text=True)
-    (raw_dir / f"{name}.plain.log").write_text(plain.stdout + plain.stderr)
-    if plain.returncode != 0:
-        print(f"{name}: the target exits {plain.returncode} without ncu; not profiled", file=sys.stderr)
-        return 1
     csv_path = raw_dir / f"{name}.csv"
     metrics = "gpu__time_duration.sum" if regex is None else METRICS
     ncu_cmd = ["ncu", "--metrics", metrics, "--clock-control", "none"]
@@ -156,11 +151,21 @@ def run_capture(name, out_dir: Path, raw_dir: Path) -> int:
         ncu_cmd += ["-k", f"regex:{regex}", "-s", str(skip)]
     ncu_cmd += ["-c", str(count), "--csv", "--log-file", str(csv_path.relative_to(ROOT) if csv_path.is_relative_to(ROOT) else csv_path)]
     ncu_cmd += target
-    prof = subprocess.run(ncu_cmd, cwd=ROOT, capture_output=True, text=True)
-    (raw_dir / f"{name}.ncu.log").write_text(prof.stdout + prof.stderr)
-    if prof.returncode != 0 or not csv_path.exists():
-        print(f"{name}: ncu exits {prof.returncode}: {(prof.stdout + prof.stderr)[-300:]}", file=sys.stderr)
-        return 1
+    if summarise_only:
+        if not csv_path.exists():
+            print(f"{name}: no {csv_path} to summarise", file=sys.stderr)
+            return 1
+    else:
+        plain = subprocess.run(target, cwd=ROOT, capture_output=True, text=True)
+        (raw_dir / f"{name}.plain.log").write_text(plain.stdout + plain.stderr)
+        if plain.returncode != 0:
+            print(f"{name}: the target exits {plain.returncode} without ncu; not profiled", file=sys.stderr)
+            return 1
+        prof = subprocess.run(ncu_cmd, cwd=ROOT, capture_output=True, text=True)
+        (raw_dir / f"{name}.ncu.log").write_text(prof.stdout + prof.stderr)
+        if prof.returncode != 0 or not csv_path.exists():
+            print(f"{name}: ncu exits {prof.returncode}: {(prof.stdout + prof.stderr)[-300:]}", file=sys.stderr)
+            return 1
     launches = parse_ncu_csv(csv_path)
     shown_target = ["python" if t == sys.executable else t for t in target]
     shown_ncu = ["python" if t == sys.executable else t for t in ncu_cmd]
@@ -181,6 +186,8 @@ def main(argv=None) -> int:
     ap.add_argument("--only", default="", help="comma-separated capture names (default: all)")
     ap.add_argument("--out", default=str(ROOT / "profiles"))
     ap.add_argument("--raw", default=str(ROOT / "gpurun_out" / "ncu_raw"), help="where the CSV files and logs go (scratch)")
+    ap.add_argument("--summarise-only", action="store_true",
+                    help="rewrite the summaries from the CSV files an earlier run left under --raw (e.g. captured on another machine)")
     args = ap.parse_args(argv)
     if args.list:
         for name, (title, *_rest) in CAPTURES.items():
@@ -190,7 +197,7 @@ def main(argv=None) -> int:
     unknown = [n for n in names if n not in CAPTURES]
     if unknown:
         ap.error(f"unknown capture(s): {', '.join(unknown)}")
-    failures = sum(run_capture(n, Path(args.out), Path(args.raw)) for n in names)
+    failures = sum(run_capture(n, Path(args.out), Path(args.raw), args.summarise_only) for n in names)
     return 1 if failures else 0
 
 

@@ -31,6 +31,8 @@ extern "C" {
 
 /* Same type as cudaStream_t / CUstream; spelled out so that C callers need no CUDA headers. */
 typedef struct CUstream_st *b200_stream_t;
+/* Same type as cudaEvent_t / CUevent. */
+typedef struct CUevent_st *b200_event_t;
 
 enum {
     B200_HGEMM_OK = 0,
@@ -62,8 +64,11 @@ enum {
                                    C per tile (a multiple of 8 up to 128; 0 = library's choice) */
     B200_VARIANT_HYBRID = 6,     /* as STREAMK, but every full wave of tiles (parts tiles each) is computed whole
                                    and only the tiles of the ragged last wave are cut into k-ranges */
-    B200_VARIANT_SKINNY_PAIR = 7 /* as SKINNY on CTA pairs (cta_group::2): two neighbouring column tiles share
-                                   the rows of A, each CTA staging half of them; same plan fields */
+    B200_VARIANT_SKINNY_PAIR = 7, /* as SKINNY on CTA pairs (cta_group::2): two neighbouring column tiles share
+                                    the rows of A, each CTA staging half of them; same plan fields */
+    B200_VARIANT_HYBRID_PAIR = 8  /* as HYBRID on CTA pairs: 256 x bn tiles (bn 128 or 256), the full waves whole, the
+                                    tiles of the ragged last wave cut into k-ranges over all pairs (parts = pairs
+                                    launched; 0 = one per two SMs) and summed from the FP32 workspace */
 };
 
 /* The dispatch decision for one shape. All fields are filled by b200_hgemm_select(); a
@@ -175,6 +180,14 @@ int b200_hgemm_host(const void *A_host, const void *B_host, void *C_host, size_t
  * exchanged between the GPUs instead of every GPU pulling all of B over its own host link. Work queued on other
  * streams that produces B must have completed (or the caller must have synchronised) before the call. */
 int b200_hgemm_host_a(const void *A_host, const void *B_device, void *C_host, size_t M, size_t N, size_t K);
+
+/* The same for a B that is still being completed on the device when the call is made: the first upload of A waits
+ * for the event `upload_after`, the first multiply for `gemm_after` (CUDA events the caller has recorded; either may
+ * be NULL). With several GPUs a rank records `upload_after` behind the upload of its share of B and `gemm_after`
+ * behind the exchange of the shares, and its rows of A travel over the host link while the other shares arrive
+ * over NVLink. */
+int b200_hgemm_host_a_after(const void *A_host, const void *B_device, void *C_host, size_t M, size_t N, size_t K,
+                            b200_event_t upload_after, b200_event_t gemm_after);
 
 /* ---- planning, workspace, status ------------------------------------------------------- */
 

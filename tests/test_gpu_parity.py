@@ -376,6 +376,31 @@ def test_whole_tiles_then_k_ranges(cuda_device, case):
     assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
 
 
+HYBRID_PAIR_CASES = [
+    # M, N, K, bn, parts (0 = one per two SMs)
+    (2304, 2304, 512, 256, 0),    # 81 pair tiles: 74 whole, 7 cut into k-ranges over all pairs
+    (2304, 2304, 512, 128, 0),    # 162 tiles of 256 x 128: two whole per pair, 14 cut; two k-blocks per stage
+    (1792, 1792, 1096, 256, 0),   # 49 tiles on 74 pairs: nothing whole, every tile cut
+    (1000, 1032, 1096, 256, 7),   # tails everywhere; 20 tiles on 7 pairs: 14 whole, 6 cut
+    (1000, 1032, 1096, 128, 5),
+    (300, 520, 8200, 256, 33),    # fewer tiles than pairs, long k
+    (1280, 2560, 320, 256, 10),   # 50 tiles on 10 pairs: nothing left to cut
+    (3840, 3840, 256, 256, 74),   # 3 cut tiles of 4 k-blocks: fewer units than pairs
+]
+
+
+@pytest.mark.parametrize("case", HYBRID_PAIR_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-bn{c[3]}-p{c[4]}")
+def test_whole_pair_tiles_then_k_ranges(cuda_device, case):
+    """HYBRID_PAIR: full waves of 256-row pair tiles computed whole, the ragged rest cut into k-ranges and summed."""
+    M, N, K, bn, parts = case
+    A, B = make_inputs(M, N, K, seed=43)
+    plan = plan_of(_native.VARIANT_HYBRID_PAIR, bn, parts=parts, tma_store=1 if N % 8 == 0 else 0)
+    C = run(None, A, B, cuda_device, plan)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"hybrid pairs bn={bn} parts={parts} {(M, N, K)}")
+    C2 = run(None, A, B, cuda_device, plan)
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
 @pytest.mark.parametrize("M", [16, 32, 64, 128])
 def test_skinny_decode_shapes(cuda_device, M):
     # decode-like: activations ~ N(0,1), weights ~ N(0, 1/K); N and K scaled down 4x from 14336 x 4096
@@ -516,6 +541,29 @@ def test_host_entry_point_with_b_resident_on_the_device(cuda_device):
         assert_close_to_oracle(hC.numpy(), oracle.gemm_f32(A, B), f"host A, resident B {M}x{N}x{K}")
         api.hgemm_host(hA, torch.from_numpy(B).pin_memory(), hC2)
         assert np.array_equal(hC.numpy().view(np.uint16), hC2.numpy().view(np.uint16))
+
+
+def test_host_entry_point_that_waits_for_b_on_events(cuda_device):
+    """b200_hgemm_host_a_after: B is still being written on another stream when the call is made; the uploads of
+    A wait for one event, the multiplies for the other."""
+    import torch
+
+    M, N, K = 2048 + 512, 520, 264
+    A, B = make_inputs(M, N, K, seed=15)
+    hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+    hC = torch.full((M, N), float("nan"), dtype=torch.float16).pin_memory()
+    dB = torch.zeros((N, K), dtype=torch.float16, device=cuda_device)
+    side = torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(side):
+        started = torch.cuda.Event()
+        started.record()
+        torch.cuda._sleep(20_000_000)          # B arrives late: about 10 ms of spinning first
+        dB.copy_(hB, non_blocking=True)
+        complete = torch.cuda.Event()
+        complete.record()
+    api.hgemm_host_a(hA, dB, hC, upload_after=started, gemm_after=complete)
+    assert_close_to_oracle(hC.numpy(), oracle.gemm_f32(A, B), "host A behind events")
+    side.synchronize()
 
 
 def _single_process_group_case(devices, M, N, K):
