@@ -32,7 +32,7 @@ namespace b200 {
 constexpr int kMaxDevices = 64;
 constexpr size_t kMaxOwnedWorkspace = size_t(1) << 30;  // the library never grows its own workspace past 1 GiB
 constexpr size_t kCounterBytes = 64 * 1024;             // reserved header at the front of the workspace (no kernel uses it now)
-constexpr uint32_t kMaxCountedTiles = kCounterBytes / 4;  // most tiles a stream-k launch accepts (the reduce kernel's grid.y)
+constexpr uint32_t kMaxCountedTiles = kCounterBytes / 4;  // most tiles the allocation-free stream-k entry point accepts
 
 struct TensorMapKey {
     const void *ptr;
@@ -1212,10 +1212,10 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
 
     uint32_t grid = 0;
     if (plan_cuts_k(pl)) {
-        if (p.tiles > kMaxCountedTiles) return B200_HGEMM_ERR_UNSUPPORTED;
         const uint32_t parts = streamk_parts(pl, st, p.tiles, p.k_blocks);
         // HYBRID: every full wave of tiles is walked whole; only the rest is cut into k-ranges
         if (pl.variant == B200_VARIANT_HYBRID || pl.variant == B200_VARIANT_HYBRID_PAIR) p.dp_tiles = (p.tiles / parts) * parts;
+        if (p.tiles - p.dp_tiles > 65535u) return B200_HGEMM_ERR_UNSUPPORTED;  // the summing kernel's grid has one row per cut tile
         const uint64_t cut_units = static_cast<uint64_t>(p.tiles - p.dp_tiles) * p.k_blocks;
         p.sk_parts = cut_units < parts ? static_cast<uint32_t>(cut_units) : parts;  // no empty k-range
         const size_t need = kCounterBytes + static_cast<size_t>(parts) * 2u * (128u * cg * bn * sizeof(float));
@@ -1466,7 +1466,15 @@ int b200_hgemm_splitk(const void *A, const void *B, void *C, size_t M, size_t N,
     if (!st->sm100) return B200_HGEMM_ERR_NO_SM100;
     b200_hgemm_plan pl;
     select_plan(*st, M, N, K, &pl);
-    if (pl.variant != B200_VARIANT_SIMT) {
+    const uint64_t tiles128 = static_cast<uint64_t>(ceil_div_u32(M, 128)) * ceil_div_u32(N, 128);
+    if (pl.variant != B200_VARIANT_SIMT && tiles128 >= static_cast<uint64_t>(st->sm_count)) {
+        // every SM has a tile of its own already: one slice per tile, i.e. whole 128 x 128 tiles and no workspace
+        // (two slices of a 16384^2 output would want 4 GiB of partial tiles)
+        memset(&pl, 0, sizeof(pl));
+        pl.variant = B200_VARIANT_CTA1;
+        pl.bn = 128;
+        pl.tma_store = (N % 8 == 0) ? 1 : 0;
+    } else if (pl.variant != B200_VARIANT_SIMT) {
         pl.variant = B200_VARIANT_STREAMK;
         pl.bn = 128;
         const uint32_t tiles = ceil_div_u32(M, 128) * ceil_div_u32(N, 128);

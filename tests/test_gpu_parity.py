@@ -118,7 +118,9 @@ def test_single_cta_tiles(cuda_device, shape, bn, tma_store):
 
 
 @pytest.mark.parametrize("bn", [128, 192, 256])
-@pytest.mark.parametrize("shape", [(256, 256, 64), (256, 512, 320), (512, 2048, 1024), (328, 264, 136), (2048, 2048, 512)],
+@pytest.mark.parametrize("shape", [(256, 256, 64), (256, 512, 320), (512, 2048, 1024), (328, 264, 136), (2048, 2048, 512),
+                                   (3840, 3840, 192),   # 225 tiles of 256 x 256 on 74 pairs: several tiles per pair
+                                   (1300, 3320, 136)],  # 78 such tiles, ragged in M, N and K
                          ids=lambda s: "x".join(map(str, s)))
 def test_cta_pair_tiles(cuda_device, shape, bn):
     M, N, K = shape
@@ -687,6 +689,7 @@ FUSED_PLAN_CASES = [
     (1024, 2048, 1024, _native.VARIANT_CTA2, 512, 0, 1),      # 256 x 256 outputs per CTA, several tiles per CTA
     (600, 776, 136, _native.VARIANT_CTA2, 512, 0, 1),         # the same with tails in M, N and K
     (1300, 6656, 200, _native.VARIANT_CTA2, 512, 0, 1),       # a full wave and a tail of half tiles on the other pair kernel
+    (1300, 3320, 136, _native.VARIANT_CTA2, 256, 0, 1),       # more 256 x 256 tiles than pairs, ragged in M, N and K
     (384, 512, 320, _native.VARIANT_CTA1, 192, 0, 1),
     (600, 776, 520, _native.VARIANT_CTA2, 192, 0, 1),
     (200, 1032, 1096, _native.VARIANT_STREAMK, 128, 33, 1),   # whole and cut tiles in one launch
