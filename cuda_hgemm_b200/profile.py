@@ -44,11 +44,12 @@ CAPTURES = OrderedDict([
     ("cublas_fp32_compute_square16384", (
         "cuBLAS cublasGemmEx, FP32 compute, at M=N=K=16384 (the comparison)",
         TARGET + ["--shape", "16384x16384x16384", "--plan", "cta2:512", "--launches", "1", "--cublas", "fp32"],
-        "nvjet|cutlass|gemm", 0, 1, (16384, 16384, 16384))),
+        "nvjet|cutlass", 0, 1, (16384, 16384, 16384))),
     ("hgemm_tcgen05_big_prefill", (
-        "the dispatch's plan at the prefill shape M=8192, N=28672, K=8192",
+        "pairs on 512 x 256 tiles at the prefill shape M=8192, N=28672, K=8192 (24 full waves; the 16 left-over tiles run as "
+        "32 halves on the 128 x 256-per-CTA pair kernel right behind, not captured here)",
         TARGET + ["--shape", "8192x28672x8192", "--dist", "normal", "--launches", "4"],
-        "hgemm_tcgen05", 1, 3, (8192, 28672, 8192))),
+        "hgemm_tcgen05_big", 1, 3, (8192, 28672, 8192))),
     ("hgemm_skinny_skinny16", (
         "the short-A kernel at the decode shape M=16, N=14336, K=4096 (B cycled through 7 copies)",
         TARGET + ["--shape", "16x14336x4096", "--dist", "normal", "--b-copies", "7", "--launches", "10"],
