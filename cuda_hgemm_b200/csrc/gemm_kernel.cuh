@@ -110,7 +110,8 @@ struct alignas(64) GemmParams {
 template <int BN, int STAGES, int CG, int KPS = 1>
 struct KernelTraits {
     static_assert(KPS == 1 || KPS == 2, "a stage holds one or two 64-wide k-blocks");
-    static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN must be a multiple of 64 up to 256");
+    static_assert(BN == 64 || BN == 128 || BN == 160 || BN == 192 || BN == 224 || BN == 256, "tile widths the kernels are built for");
+    static_assert((BN / CG) % 8 == 0 && BN % 32 == 0, "whole swizzle atoms per CTA, whole 32-column epilogue chunks");
     static_assert(CG == 1 || CG == 2, "CG is the CTA-pair size");
     static constexpr uint32_t kARows = kBM;
     static constexpr uint32_t kBRows = BN / CG;
@@ -119,6 +120,7 @@ struct KernelTraits {
     static constexpr uint32_t kBlockBytes = kABytes + kBBytes;   // one k-block of A and B
     static constexpr uint32_t kStageBytes = KPS * kBlockBytes;  // [A0][B0] or [A0][B0][A1][B1]
     static constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;  // two accumulators; power of two
+    static constexpr uint32_t kAccStride = kTmemCols / 2;  // the second accumulator starts half way (BN columns for the widths that are powers of two times 64)
     static constexpr uint32_t kBarrierBytes = 256;
     static constexpr uint32_t kSmemBytes = 1024 + STAGES * kStageBytes + kStagingBytes + kBarrierBytes;
     static_assert((kBlockBytes % 1024) == 0, "operand slabs must keep 1024-byte alignment");
@@ -525,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 const uint32_t acc_phase = (it >> 1) & 1u;
                 if (!mbar_wait(tempty_bar + 8u * acc, acc_phase ^ 1u, abort_flag)) break;
                 tcgen05_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t d_tmem = tmem_base + acc * T::kAccStride;
                 for (uint32_t kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!mbar_wait(full_bar + 8u * stage, phase, abort_flag)) {
                         ok = false;
@@ -601,7 +603,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
 #ifdef B200_TIMELINE
             if (epi_tid == 0) B200_STAMP(it == 0 ? 6 : 7);
 #endif
-            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * T::kAccStride;
             const uint32_t row_in_tile = q * 32u + lane;
             const bool whole_tile = (MODE == kModeTiles) || (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
 
@@ -655,6 +657,18 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                                 tma_store_commit();
                             }
                             ++store_buf;
+                        }
+                    }
+                    if (BN % 64 == 32) {
+                        // a tile 160 or 224 columns wide ends in half a chunk: its 32 columns leave with plain 16-byte stores
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(taddr + kChunks * 64u, r);
+                        tmem_ld_wait();
+                        if (EPI) {
+                            fused_epilogue<32>(p, m0 + row_in_tile, n0 + kChunks * 64u, r);
+                            store_row_chunk32_typed(p.c, p.c_type, m0 + row_in_tile, n0 + kChunks * 64u, p.m, p.n, p.c_vec_ok != 0, r);
+                        } else {
+                            store_row_chunk32(p.c, m0 + row_in_tile, n0 + kChunks * 64u, p.m, p.n, p.c_vec_ok != 0, r);
                         }
                     }
                 } else {

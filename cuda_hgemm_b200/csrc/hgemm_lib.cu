@@ -334,6 +334,9 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     } else if (pl.bn == 192) {
         // whole tiles only: between 128 and 256 for shapes whose tile count would leave a wave ragged
         if (plan_cuts_k(pl)) return B200_HGEMM_ERR_UNSUPPORTED;
+    } else if (pl.bn == 160 || pl.bn == 224) {
+        // two more widths for the same purpose, on CTA pairs only
+        if (pl.variant != B200_VARIANT_CTA2) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) {
         return B200_HGEMM_ERR_UNSUPPORTED;
     }
@@ -363,7 +366,7 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
 static uint32_t plan_kps(const b200_hgemm_plan &pl) {
     if (pl.variant == B200_VARIANT_HYBRID_PAIR) return pl.bn == 128 ? 2u : 1u;
     if (pl.variant == B200_VARIANT_CTA1 || plan_cuts_k(pl)) return (pl.bn == 128 || pl.bn == 64) ? 2u : 1u;
-    if (pl.variant == B200_VARIANT_CTA2) return (pl.bn == 128 || pl.bn == 192) ? 2u : 1u;
+    if (pl.variant == B200_VARIANT_CTA2) return (pl.bn == 128 || pl.bn == 160 || pl.bn == 192 || pl.bn == 224) ? 2u : 1u;
     return 1u;
 }
 
@@ -466,7 +469,7 @@ static bool tuned_plan(size_t M, size_t N, size_t K, b200_hgemm_plan *pl) {
 //    k - 256 x 256 outputs per CTA (pairs on 512 x 256, groups of four on 512 x 512 with A multicast),
 //    whichever fills its waves best after what the larger tiles gain under the power cap;
 //  * in between: the candidate with the smallest estimated time among single-CTA tiles of three
-//    widths, pairs on 256 x 256 and 256 x 192, and stream-k.
+//    widths, pairs on 256 x 256, 256 x 224 and 256 x 192, and stream-k.
 static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b200_hgemm_plan *pl, bool use_table = true) {
     memset(pl, 0, sizeof(*pl));
     if (K % 8 != 0) {
@@ -575,22 +578,36 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     // (about 4 TB/s for this pattern): with full-height tiles that costs more than a ragged last
     // wave does, so stream-k only wins here when the tiles are few and k is long
     auto partial_us = [&](int bn) { return 2.0 * sms * 2.0 * (128.0 * bn * 4.0) / 4.0e6; };
-    constexpr int kCands = 7;
+    constexpr int kCands = 8;
     const uint64_t pairs192 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 192);
+    const uint64_t pairs224 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 224);
+    // Waves of pair tiles, the last one counted by how full it is: behind at least one full wave a nearly empty
+    // wave costs about three quarters of a full one (its tiles have L2 and the memory system to themselves).
+    // Measured in the driver's burst protocol at 2304 ... 3840: pairs on 256 x 224 beat 256 x 256 at 2816^3
+    // (1260 against 1163 TFLOP/s) and 3328^3 (1300 against 1245), 256 x 192 wins 2304^3 and 2560^3, and 256 x 160
+    // (built, a plan option) wins nowhere.
+    auto pair_waves = [&](uint64_t tiles) {
+        if (tiles <= pair_slots) return 1.0;
+        const uint64_t rest = tiles % pair_slots;
+        if (rest == 0) return static_cast<double>(tiles / pair_slots);
+        return static_cast<double>(tiles / pair_slots) + 0.75 + 0.25 * static_cast<double>(rest) / static_cast<double>(pair_slots);
+    };
     Candidate cands[kCands] = {
         {B200_VARIANT_CTA1, 256, waves(tiles256, sms) * kb * 0.35 + 2.0},
         {B200_VARIANT_CTA1, 128, waves(tiles128, sms) * kb * 0.33 + 1.5},
         {B200_VARIANT_CTA1, 64, waves(tiles64, sms) * kb * 0.30 + 1.2},
         // pairs: less L2 traffic per k-block than single CTAs, a costlier launch (measured: single
         // CTAs ahead at 1792 and 2048, pairs from 2304 up)
-        {B200_VARIANT_CTA2, 256, waves(pairs256, pair_slots) * kb * 0.335 + 2.5},
+        {B200_VARIANT_CTA2, 256, pair_waves(pairs256) * kb * 0.335 + 2.5},
         {B200_VARIANT_STREAMK, 256, static_cast<double>(tiles256) * kb / sms * 0.35 + 4.0 + partial_us(256)},
         {B200_VARIANT_STREAMK, 128, static_cast<double>(tiles128) * kb / sms * 0.33 + 4.0 + partial_us(128)},
         // pairs on 256 x 192 tiles (two k-blocks per stage): three quarters of the time of a 256-wide tile,
         // so two ragged waves of them beat two ragged waves of those (measured: 2304^3 950 against 810
         // TFLOP/s, 2560^3 1160 against 990; no gain where 256-wide tiles fit one wave, as at 1792^3)
-        {B200_VARIANT_CTA2, 192, pairs256 > pair_slots ? waves(pairs192, pair_slots) * kb * 0.27 + 2.5 : 1e30},
+        {B200_VARIANT_CTA2, 192, pairs256 > pair_slots ? pair_waves(pairs192) * kb * 0.27 + 2.5 : 1e30},
+        {B200_VARIANT_CTA2, 224, pairs256 > pair_slots ? pair_waves(pairs224) * kb * 0.308 + 2.5 : 1e30},
     };
+    if (M % 256 != 0) cands[7].us *= 1.0 + 128.0 / static_cast<double>(M);
     if (M % 256 != 0) cands[6].us *= 1.0 + 128.0 / static_cast<double>(M);
     if (M % 256 != 0) cands[3].us *= 1.0 + 128.0 / static_cast<double>(M);  // the pair's second CTA idles on the last rows
     if (k_blocks < 16) cands[4].us = cands[5].us = 1e30;                    // too little k to split
@@ -1247,6 +1264,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (big) return launch_big_with_tail(st, p, grid, stream, true, pl.grid > 0);
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles, 1, true>(st, 19, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2, true>(st, 22, p, grid, stream);
+        if (bn == 160) return launch_kernel<160, 3, 2, kModeTiles, 2, true>(st, 39, p, grid, stream);
+        if (bn == 224) return launch_kernel<224, 3, 2, kModeTiles, 2, true>(st, 40, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2, true>(st, 20, p, grid, stream);
     }
     if (pl.variant == B200_VARIANT_CTA1) {
@@ -1266,6 +1285,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 128 && pl.stages == 3) return launch_kernel<128, 3, 2, kModeTiles, 2>(st, 30, p, grid, stream);
         if (bn == 256) return launch_kernel<256, 6, 2, kModeTiles>(st, 3, p, grid, stream);
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
+        if (bn == 160) return launch_kernel<160, 3, 2, kModeTiles, 2>(st, 37, p, grid, stream);
+        if (bn == 224) return launch_kernel<224, 3, 2, kModeTiles, 2>(st, 38, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);
     }
     if (pl.variant == B200_VARIANT_HYBRID_PAIR) {
