@@ -166,6 +166,7 @@ NCU_TRAFFIC_BYTES = {
     ((16384, 16384, 16384), _native.VARIANT_CTA2_MCAST, 512): 7.49e9,  # profiles/hgemm_tcgen05_mc512_square16384.md
     ((16384, 16384, 16384), _native.VARIANT_CTA2, 512): 7.80e9,        # profiles/hgemm_tcgen05_big_square16384.md
     ((16384, 16384, 16384), _native.VARIANT_CTA2, 256): 16.5e9,        # profiles/hgemm_tcgen05_big_vs_cublas_square16384.md
+    ((8192, 28672, 8192), _native.VARIANT_CTA2, 512): 4.26e9,          # profiles/hgemm_tcgen05_big_prefill.md
     ((8192, 8192, 8192), _native.VARIANT_CTA2_MCAST, 512): 0.936e9,    # profiles/hgemm_tcgen05_mc512_square8192.md
     ((8192, 8192, 8192), _native.VARIANT_CTA2, 256): 1.118e9,          # profiles/hgemm_tcgen05_cta2_square8192.md
     ((16, 14336, 4096), _native.VARIANT_SKINNY, 16): 121.3e6,          # profiles/hgemm_skinny_skinny16.md
