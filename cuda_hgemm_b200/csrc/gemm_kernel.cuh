@@ -88,18 +88,22 @@ struct alignas(64) GemmParams {
     // u % (tail_sm * tail_sn) of the larger tile tail_first + u / (tail_sm * tail_sn), which is located with
     // the larger tiles' own geometry and split tail_sm x tail_sn ways.
     uint32_t tail_first, tail_sm, tail_sn, tail_m_blocks, tail_n_blocks, tail_group_m;
+    Raster raster;  // tile id -> block coordinates of this launch (of the larger tiles' raster when tail_sm != 0)
     // Batched kernels (FLAVOR & kFlavorBatched): `tiles` counts the tiles of all matrices, m_blocks x n_blocks
     // of them per matrix; the tensor maps are {columns, rows, matrices}.
     uint64_t batch_stride_c;  // elements between consecutive matrices of C (plain-store path)
 #ifdef B200_TIMELINE
-    unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
+    unsigned long long *timeline;  // profiling builds only: per CTA 16 stamps of %globaltimer, then the same 16 of the SM's cycle counter
 #endif
 };
 
 #ifdef B200_TIMELINE
 #define B200_STAMP(slot)                                                                                  \
     do {                                                                                                  \
-        if (p.timeline) p.timeline[blockIdx.x * 16 + (slot)] = global_timer_ns();                         \
+        if (p.timeline) {                                                                                 \
+            p.timeline[blockIdx.x * 32 + (slot)] = global_timer_ns();                                     \
+            p.timeline[blockIdx.x * 32 + 16 + (slot)] = static_cast<unsigned long long>(clock64());       \
+        }                                                                                                 \
     } while (0)
 #else
 #define B200_STAMP(slot) \
@@ -174,10 +178,10 @@ struct WorkWalker<kModeStreamK> {
 
 // Linear tile id of this launch -> block coordinates in this launch's own tile size.
 __device__ __forceinline__ TileCoord locate_tile(const GemmParams &p, uint32_t tile) {
-    if (p.tail_sm == 0) return tile_coord(tile, p.m_blocks, p.n_blocks, p.group_m);
+    if (p.tail_sm == 0) return tile_coord_fast(tile, p.raster);
     const uint32_t per = p.tail_sm * p.tail_sn;
     const uint32_t part = tile % per;
-    TileCoord c = tile_coord(p.tail_first + tile / per, p.tail_m_blocks, p.tail_n_blocks, p.tail_group_m);
+    TileCoord c = tile_coord_fast(p.tail_first + tile / per, p.raster);
     c.m_blk = c.m_blk * p.tail_sm + part % p.tail_sm;
     c.n_blk = c.n_blk * p.tail_sn + part / p.tail_sm;
     return c;
@@ -402,6 +406,16 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         tma_prefetch_desc(&p.tm_b);
         if (p.tma_store) tma_prefetch_desc(&p.tm_c);
     }
+    if (warp == 3 && lane == 0) {
+        // The kernel's parameters sit in constant memory and nothing on this SM has read them yet: the producer's
+        // first tile would pay one cache miss after the other for them (measured: 1175 cycles from the dependency
+        // wait to its first load at 256^3, most of it here). An idle epilogue lane reads them now, while the
+        // barriers are set up, so that the producer finds them cached.
+        const uint32_t touch = p.tiles + p.k_blocks + p.m_blocks + p.n_blocks + p.group_m + p.dp_tiles + p.sk_parts + p.tail_sm +
+                               p.m + p.n + p.tma_store + p.raster.n_blocks + p.raster.tall_tiles + p.raster.tall_span.mul +
+                               p.raster.short_span.mul + p.raster.tall_rows.mul + p.raster.short_rows.sh2;
+        asm volatile("" ::"r"(touch));
+    }
     if (warp == 1) {
         tmem_alloc<CG>(smem_u32(const_cast<uint32_t *>(tmem_slot)), T::kTmemCols);
         tmem_relinquish<CG>();
@@ -433,10 +447,13 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
             Segment seg;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            uint32_t filled = 0;  // stages filled so far, counted up to STAGES: the first trip round the ring finds every stage free
 #ifdef B200_TIMELINE
             bool stamped_first_load = false;
 #endif
+            B200_STAMP(11);
             pdl_wait_prior_grids();  // A and B may have been written by the previous kernel
+            B200_STAMP(12);
             while (ok && work.next(seg)) {
                 uint32_t zt = seg.tile;
                 int32_t z = 0;  // which matrix of the stack
@@ -447,11 +464,22 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                 const TileCoord tc = locate_tile(p, zt);
                 const int32_t row_a = static_cast<int32_t>((tc.m_blk * CG + cta_rank) * kBM);
                 const int32_t row_b = static_cast<int32_t>(tc.n_blk * BN + cta_rank * T::kBRows);
+#ifdef B200_TIMELINE
+                if (!stamped_first_load) {
+                    asm volatile("" ::"r"(row_a), "r"(row_b));
+                    B200_STAMP(14);
+                }
+#endif
                 for (uint32_t kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    if (!mbar_wait(empty_bar + 8u * stage, phase ^ 1u, abort_flag)) {
+                    if (filled < static_cast<uint32_t>(STAGES)) {
+                        ++filled;
+                    } else if (!mbar_wait(empty_bar + 8u * stage, phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
+#ifdef B200_TIMELINE
+                    if (!stamped_first_load) B200_STAMP(13);
+#endif
                     const uint32_t slot = base + stage * T::kStageBytes;
                     if (CG == 1) {
                         mbar_arrive_expect_tx(full_bar + 8u * stage, T::kStageBytes);

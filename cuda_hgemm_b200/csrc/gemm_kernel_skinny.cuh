@@ -56,7 +56,7 @@ struct alignas(64) SkinnyParams {
     uint32_t prefetch_kb;    // k-blocks of B asked into L2 before waiting for the previous kernel
     EpilogueArgs epi;        // kernels instantiated with EPI: alpha / beta / bias / c_in and the element type of C
 #ifdef B200_TIMELINE
-    unsigned long long *timeline;  // profiling builds only: 16 stamps per CTA
+    unsigned long long *timeline;  // profiling builds only: 32 words per CTA (see GemmParams::timeline)
 #endif
 };
 

@@ -1199,6 +1199,7 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
     p.tiles = static_cast<uint32_t>(tiles64);
     p.group_m = pl.group_m > 0 ? static_cast<uint32_t>(pl.group_m) : (big ? 6u : cg == 2 ? 8u : 16u);
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
+    p.raster = make_raster(p.m_blocks, p.n_blocks, p.group_m);
     p.tma_store = pl.tma_store ? 1u : 0u;
     p.c_vec_ok = (N % 8 == 0) ? 1u : 0u;
     EpilogueArgs ea;
@@ -1609,6 +1610,7 @@ static int run_batched(DeviceState &st, const void *A, const void *B, void *C, s
     if (tiles > 0x7fffffffull || batch > 0x7fffffffull) return B200_HGEMM_ERR_UNSUPPORTED;
     p.tiles = static_cast<uint32_t>(tiles);
     p.group_m = p.m_blocks < 16u ? p.m_blocks : 16u;
+    p.raster = make_raster(p.m_blocks, p.n_blocks, p.group_m);
     p.tma_store = (N % 8 == 0) ? 1u : 0u;
     p.c_vec_ok = p.tma_store;
     p.batch_stride_c = stride_c;
@@ -1660,6 +1662,7 @@ static int run_bkn(DeviceState &st, const void *A, const void *B, void *C, size_
     p.tiles = static_cast<uint32_t>(tiles);
     p.group_m = cg == 2 ? 8u : 16u;
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
+    p.raster = make_raster(p.m_blocks, p.n_blocks, p.group_m);
     p.tma_store = 1;
     p.c_vec_ok = 1;
     int rc = get_tensor_map(st, A, M, K, 128, 64, &p.tm_a);
@@ -2271,6 +2274,18 @@ void b200_sched_tile_coord(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, 
     TileCoord c = tile_coord(tile, m_blocks, n_blocks, group_m);
     *m_blk = c.m_blk;
     *n_blk = c.n_blk;
+}
+
+void b200_sched_tile_coord_fast(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
+                                uint32_t *n_blk) {
+    const Raster r = make_raster(m_blocks, n_blocks, group_m);
+    TileCoord c = tile_coord_fast(tile, r);
+    *m_blk = c.m_blk;
+    *n_blk = c.n_blk;
+}
+
+uint32_t b200_debug_fast_div(uint32_t n, uint32_t d) {
+    return fast_div(n, make_fast_div(d));
 }
 
 uint32_t b200_sched_segments(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *out,

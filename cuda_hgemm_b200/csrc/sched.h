@@ -53,6 +53,82 @@ B200_HD TileCoord tile_coord(uint32_t t, uint32_t m_blocks, uint32_t n_blocks, u
     return c;
 }
 
+// Division of a 32-bit number by a divisor that is fixed for a whole launch, as a multiplication and two shifts
+// (Granlund and Montgomery, "Division by invariant integers using multiplication"): the host computes the
+// constants once, the kernels divide in a handful of cycles where the hardware's own division of two run-time
+// values costs a couple of hundred -- which is what locating a tile used to cost the thread that issues the
+// first loads of a kernel.
+struct FastDiv {
+    uint32_t divisor, mul, sh1, sh2;
+};
+
+inline FastDiv make_fast_div(uint32_t d) {
+    FastDiv f;
+    f.divisor = d < 1 ? 1u : d;
+    uint32_t l = 0;
+    while ((static_cast<uint64_t>(1) << l) < f.divisor) ++l;  // ceil(log2 d)
+    f.mul = static_cast<uint32_t>(((static_cast<uint64_t>(1) << 32) * ((static_cast<uint64_t>(1) << l) - f.divisor)) / f.divisor + 1);
+    f.sh1 = l < 1 ? l : 1u;
+    f.sh2 = l > 0 ? l - 1 : 0u;
+    return f;
+}
+
+B200_HD uint32_t fast_div(uint32_t n, const FastDiv &f) {
+#if defined(__CUDA_ARCH__)
+    const uint32_t t = __umulhi(f.mul, n);
+#else
+    const uint32_t t = static_cast<uint32_t>((static_cast<uint64_t>(f.mul) * n) >> 32);
+#endif
+    return (t + ((n - t) >> f.sh1)) >> f.sh2;
+}
+
+// tile_coord with everything that depends on the launch alone worked out beforehand.
+struct Raster {
+    uint32_t n_blocks, extra, base, tall_tiles;
+    FastDiv tall_span, short_span, tall_rows, short_rows;  // (rows of a band) x n_blocks, and rows of a band
+};
+
+inline Raster make_raster(uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m) {
+    Raster r;
+    if (group_m < 1) group_m = 1;
+    if (m_blocks < 1) m_blocks = 1;
+    if (n_blocks < 1) n_blocks = 1;
+    const uint32_t bands = (m_blocks + group_m - 1) / group_m;
+    r.n_blocks = n_blocks;
+    r.base = m_blocks / bands;
+    r.extra = m_blocks % bands;
+    r.tall_tiles = r.extra * (r.base + 1) * n_blocks;
+    r.tall_span = make_fast_div((r.base + 1) * n_blocks);
+    r.short_span = make_fast_div((r.base < 1 ? 1u : r.base) * n_blocks);
+    r.tall_rows = make_fast_div(r.base + 1);
+    r.short_rows = make_fast_div(r.base < 1 ? 1u : r.base);
+    return r;
+}
+
+// Same result as tile_coord(t, m_blocks, n_blocks, group_m) for the launch `r` was made for.
+B200_HD TileCoord tile_coord_fast(uint32_t t, const Raster &r) {
+    uint32_t band, first_m, rows_here, rem, n;
+    if (t < r.tall_tiles) {
+        rows_here = r.base + 1;
+        band = fast_div(t, r.tall_span);
+        first_m = band * rows_here;
+        rem = t - band * rows_here * r.n_blocks;
+        n = fast_div(rem, r.tall_rows);
+    } else {
+        rows_here = r.base;
+        const uint32_t u = t - r.tall_tiles;
+        const uint32_t b = fast_div(u, r.short_span);
+        band = r.extra + b;
+        first_m = r.extra * (r.base + 1) + b * rows_here;
+        rem = u - b * rows_here * r.n_blocks;
+        n = fast_div(rem, r.short_rows);
+    }
+    TileCoord c;
+    c.m_blk = first_m + (rem - n * rows_here);
+    c.n_blk = (band & 1u) ? (r.n_blocks - 1u - n) : n;
+    return c;
+}
+
 // One contiguous piece of work: k-blocks [kb0, kb1) of output tile `tile`.
 struct Segment {
     uint32_t tile;

@@ -21,7 +21,10 @@ from .abtest import parse_plan
 
 STAMPS = ("launch", "set-up done", "first load issued", "producer done", "first MMA", "last MMA issued",
           "epilogue: first tile ready", "epilogue: last tile ready", "epilogue: stores issued",
-          "epilogue: stores read out", "exit")
+          "epilogue: stores read out", "exit", "producer: before the dependency wait", "producer: after the dependency wait",
+          "producer: first stage free", "producer: first tile located")
+# the order in which one CTA passes the stamps (for the cycle counts between consecutive ones)
+ORDER = (0, 1, 11, 12, 14, 13, 2, 4, 3, 5, 6, 8, 9, 10)
 
 
 def run_case(torch, lib, text, device, B_copies=1):
@@ -35,7 +38,7 @@ def run_case(torch, lib, text, device, B_copies=1):
     a = torch.randn(M, K, device=device).half()
     bs = [torch.randn(N, K, device=device).half() for _ in range(B_copies)]
     c = torch.empty(M, N, device=device, dtype=torch.float16)
-    stamps = torch.zeros(8192 * 16, dtype=torch.int64, device=device)
+    stamps = torch.zeros(8192 * 32, dtype=torch.int64, device=device)
     s = torch.cuda.current_stream().cuda_stream
 
     def call(b):
@@ -49,8 +52,9 @@ def run_case(torch, lib, text, device, B_copies=1):
     call(bs[3 % len(bs)])
     torch.cuda.synchronize()
     lib.b200_debug_set_timeline(None)
-    t = stamps.cpu().numpy().reshape(-1, 16)
-    t = t[t[:, 0] > 0].astype("float64")
+    both = stamps.cpu().numpy().reshape(-1, 32)
+    both = both[both[:, 0] > 0].astype("float64")
+    t, cyc = both[:, :16], both[:, 16:]
     t0 = t[:, 0].min()
     rows = []
     for i, name in enumerate(STAMPS):
@@ -59,7 +63,14 @@ def run_case(torch, lib, text, device, B_copies=1):
         if len(col):
             r = sorted((col - t0) / 1e3)
             rows.append((name, r[0], r[len(r) // 2], r[-1]))
-    return {"case": text, "shape": (M, N, K), "plan": plan.as_dict(), "ctas": int(len(t)), "rows": rows}
+    # SM cycles between consecutive stamps of the same CTA (the global timer ticks every 0.256 us only); stamps
+    # taken by different warps of the CTA still share the SM's counter
+    steps = []
+    seen = [i for i in ORDER if (cyc[:, i] > 0).all()]
+    for a, b in zip(seen, seen[1:]):
+        d = sorted(cyc[:, b] - cyc[:, a])
+        steps.append((STAMPS[a], STAMPS[b], d[len(d) // 2]))
+    return {"case": text, "shape": (M, N, K), "plan": plan.as_dict(), "ctas": int(len(t)), "rows": rows, "steps": steps}
 
 
 def main(argv=None) -> int:
@@ -86,6 +97,9 @@ def main(argv=None) -> int:
         out.append("|---|---|---|---|")
         for name, lo, med, hi in r["rows"]:
             out.append(f"| {name} | {lo:.2f} | {med:.2f} | {hi:.2f} |")
+        out.append("")
+        out.append("SM cycles from one stamp to the next (median over the CTAs): " +
+                   "; ".join(f"{a} -> {b}: {int(c)}" for a, b, c in r["steps"]))
         out.append("")
     text = "\n".join(out)
     print(text)

@@ -285,6 +285,11 @@ int b200_partition_slab(size_t M, int n, int index, size_t *row0, size_t *rows);
 /* Tile rasterisation: linear tile id -> (m_blk, n_blk). */
 void b200_sched_tile_coord(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
                            uint32_t *n_blk);
+/* The same through the kernels' own path: the launch's raster constants worked out once, divisions by
+ * multiplication (must agree with b200_sched_tile_coord everywhere). And that division on its own: n / d, d >= 1. */
+void b200_sched_tile_coord_fast(uint32_t tile, uint32_t m_blocks, uint32_t n_blocks, uint32_t group_m, uint32_t *m_blk,
+                                uint32_t *n_blk);
+uint32_t b200_debug_fast_div(uint32_t n, uint32_t d);
 /* Stream-K: writes up to `cap` segments {tile, kb0, kb1} of part `part` to out[3*i..]; returns the count. */
 uint32_t b200_sched_segments(uint32_t part, uint32_t parts, uint32_t tiles, uint32_t k_blocks, uint32_t *out,
                              uint32_t cap);

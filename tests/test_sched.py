@@ -125,3 +125,36 @@ def test_whole_tiles_then_k_ranges_cover_every_unit_once(native_lib, tiles, k_bl
                     key = (dp_tiles + tile, kb)
                     seen[key] = seen.get(key, 0) + 1
     assert len(seen) == tiles * k_blocks and set(seen.values()) == {1}
+
+
+def test_division_by_multiplication_is_exact(native_lib):
+    """The kernels divide by launch constants with a multiplication and two shifts: exact for every 32-bit pair."""
+    import numpy as np
+
+    rng = np.random.default_rng(5)
+    cases = [(0, 1), (1, 1), (2 ** 32 - 1, 1), (2 ** 32 - 1, 2 ** 32 - 1), (2 ** 32 - 1, 2), (2 ** 31, 3), (12345, 2 ** 31)]
+    cases += [(int(rng.integers(0, 2 ** 32)), int(rng.integers(1, 2 ** 32))) for _ in range(2000)]
+    cases += [(int(rng.integers(0, 2 ** 32)), int(rng.integers(1, 5000))) for _ in range(4000)]
+    cases += [(d * q + r, d) for d in (1, 2, 3, 7, 74, 148, 255, 256, 257, 65535, 65536) for q in (0, 1, 999, 16777215 // d)
+              for r in (0, d - 1)]
+    for n, d in cases:
+        n &= 0xFFFFFFFF
+        assert native_lib.b200_debug_fast_div(n, d) == n // d, (n, d)
+
+
+def test_fast_tile_raster_agrees_with_the_plain_one(native_lib):
+    import ctypes
+
+    import numpy as np
+
+    rng = np.random.default_rng(6)
+    m, n = ctypes.c_uint32(), ctypes.c_uint32()
+    m2, n2 = ctypes.c_uint32(), ctypes.c_uint32()
+    geometries = [(1, 1, 1), (1, 7, 4), (9, 9, 8), (59, 3, 8), (64, 64, 6), (128, 2, 16), (4, 64, 6), (15, 15, 8), (3, 500, 1)]
+    geometries += [(int(rng.integers(1, 200)), int(rng.integers(1, 200)), int(rng.integers(1, 40))) for _ in range(60)]
+    for mb, nb, g in geometries:
+        tiles = mb * nb
+        for t in sorted(set([0, tiles - 1] + [int(x) for x in rng.integers(0, tiles, size=min(tiles, 200))])):
+            native_lib.b200_sched_tile_coord(t, mb, nb, min(g, mb), ctypes.byref(m), ctypes.byref(n))
+            native_lib.b200_sched_tile_coord_fast(t, mb, nb, min(g, mb), ctypes.byref(m2), ctypes.byref(n2))
+            assert (m.value, n.value) == (m2.value, n2.value), (mb, nb, g, t)
