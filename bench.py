@@ -292,6 +292,38 @@ def cpu_baseline(M, N, K, dist):
             "sample": f"first {rows} of {M} rows of C (rows x {N} x {K}), {t:.2f} s wall; whole-matrix time scales linearly in M"}
 
 
+ALL_CPUS = set(os.sched_getaffinity(0))  # what this process may run on, before any binding
+
+
+def bind_to_gpu_cpus(torch, index):
+    """Run this process on the CPUs NVML names as local to GPU `index`, so that the pinned host buffers it
+    allocates afterwards lie in the memory next to that GPU's host link (with eight ranks on a two-socket host,
+    half of them would otherwise copy across the sockets). Returns the CPU count it bound to, or None."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(index).uuid)
+        handle = None
+        for i in range(pynvml.nvmlDeviceGetCount()):
+            h = pynvml.nvmlDeviceGetHandleByIndex(i)
+            u = pynvml.nvmlDeviceGetUUID(h)
+            if uuid in (u.decode() if isinstance(u, bytes) else u):
+                handle = h
+        if handle is None:
+            return None
+        n_cpus = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpus + 63) // 64)
+        local = {c for c in range(n_cpus) if (int(words[c // 64]) >> (c % 64)) & 1}
+        allowed = local & set(os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return len(allowed)
+    except Exception:
+        return None
+
+
 def dist_setup(torch, n_gpus):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -340,6 +372,7 @@ def run_ours(args):
 
     rank, world, local = dist_setup(torch, args.gpus)
     device = torch.device("cuda", local)
+    bound_cpus = bind_to_gpu_cpus(torch, local)
     M, N, K, dist_name, desc = WORKLOADS[args.workload]
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
@@ -498,7 +531,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": int((rows * K + (N // world if sharded_b else N) * K) * 2),
                 "d2h_bytes_per_step": int(rows * N * 2),
                 "nvlink_bytes_per_step": int((N - N // world) * K * 2) if sharded_b else 0,
-                "steps": e2e_steps, "matches_device_result": e2e_ok,
+                "steps": e2e_steps, "matches_device_result": e2e_ok, "host_cpus_bound_to_gpu": bound_cpus,
                 "api": ("multi_gpu.slab_hgemm_host (per rank: pinned host buffers -> H2D of A's rows and 1/N of B -> "
                         "NCCL all-gather of B -> b200_hgemm_host_a -> D2H)") if sharded_b else
                        "b200_hgemm_host (pinned host buffers -> H2D -> kernel -> D2H, per rank)"},
@@ -554,6 +587,7 @@ def run_ours(args):
         out["workloads"] = [measure_workload(torch, api, cmp_lib, name, device, peaks, warmup, steps)
                             for name in EXTRA_WORKLOADS if name != args.workload]
     if world == 1:
+        os.sched_setaffinity(0, ALL_CPUS)  # the host GEMM uses every core again
         out["cpu_baseline"] = cpu_baseline(M, N, K, dist_name)
     if gather_ms is not None:
         out["allgather_c"] = {"ms": round(gather_ms, 4), "bytes_received_per_rank": int((M - rows) * N * 2),
@@ -600,6 +634,7 @@ def run_reference(args):
 
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
+    bind_to_gpu_cpus(torch, 0)  # the same placement of the pinned host buffers as the other arm's
     lib = ctypes.CDLL(str(oracle_build.REF_SO))
     A, B = make_inputs(torch, M, N, K, dist_name, device, 0, M)
     C = torch.empty((M, N), dtype=torch.float16, device=device)
@@ -639,9 +674,10 @@ def run_reference(args):
                  "kernels": per_kernel, "gpu_launches": launches,
                  "e2e": {"value": round(flops / e2e_s / 1e12, 2), "unit": "TFLOP/s",
                          "h2d_bytes_per_step": int((M * K + N * K) * 2), "d2h_bytes_per_step": int(M * N * 2)},
-                 "cpu_baseline": cpu_baseline(M, N, K, dist_name),
                  "note": "reference = its own CUDA kernels built unmodified for sm_100a (it has no CPU path); "
                          "cpu_baseline is the checker's host GEMM"})
+    os.sched_setaffinity(0, ALL_CPUS)
+    base["cpu_baseline"] = cpu_baseline(M, N, K, dist_name)
     print(json.dumps(base), flush=True)
 
 
