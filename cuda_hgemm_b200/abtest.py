@@ -9,9 +9,11 @@ does instead (a short run after an idle pause, before the power cap bites).
     python -m cuda_hgemm_b200.abtest --shape 8192x8192x8192 \
         --plans auto,cta2:256,cta1:256:g16,cta1:128,streamk:128,mcast:256
 
-A plan is ``variant:bn[:gN][:pN][:sN][:nt]`` with variant one of cta1, cta2, streamk, hybrid, mcast, skinny, simt;
-``gN`` sets the rasterisation band height, ``pN`` the number of stream-k ranges, ``nt`` turns the
-TMA-store epilogue off. ``auto`` is the library's own choice.
+A plan is ``variant:bn[:gN][:pN][:sN][:cN][:nt]`` with variant one of cta1, cta2, streamk, hybrid, hybrid2, mcast,
+skinny, skinny2, simt; ``gN`` sets the rasterisation band height (short-A kernels: the column-tile width), ``pN``
+the number of k-ranges, ``sN`` the ring depth, ``cN`` the plan's ``grid`` field (CTAs launched; short-A kernels:
+1 = k-ranges summed inside clusters, 2 = through the workspace), ``nt`` turns the TMA-store epilogue off.
+``auto`` is the library's own choice.
 """
 from __future__ import annotations
 
@@ -40,6 +42,8 @@ def parse_plan(text: str) -> _native.Plan:
             plan.parts = int(extra[1:])
         elif extra.startswith("s"):
             plan.stages = int(extra[1:])
+        elif extra.startswith("c"):
+            plan.grid = int(extra[1:])
         elif extra == "nt":
             plan.tma_store = 0
         else:
@@ -59,6 +63,9 @@ def main(argv=None) -> int:
     ap.add_argument("--burst", action="store_true",
                     help="the reference driver's protocol: idle pause, 3 warm-up and --steps timed launches, no pre-heat")
     ap.add_argument("--dist", choices=("uniform", "normal"), default="uniform")
+    ap.add_argument("--b-copies", type=int, default=1,
+                    help="distinct copies of B cycled through from launch to launch, so that a B that fits L2 still comes "
+                         "from HBM (the decode shapes: 7 copies of 112 MiB); with --graph the graph holds 3 launches per copy")
     args = ap.parse_args(argv)
 
     M, N, K = (int(x) for x in args.shape.lower().split("x"))
@@ -72,6 +79,15 @@ def main(argv=None) -> int:
         A = torch.randn((M, K), generator=g, device=dev).half()
         B = (torch.randn((N, K), generator=g, device=dev) / K ** 0.5).half()
     C = torch.empty((M, N), dtype=torch.float16, device=dev)
+    Bs = [B] + [B.clone() for _ in range(max(0, args.b_copies - 1))]
+    turn = [0]
+
+    def next_of(items):
+        turn[0] += 1
+        return items[turn[0] % len(items)]
+
+    def next_b():
+        return next_of(Bs)
 
     if any(text.startswith("mcast") for text in args.plans.split(",")) and not api.enable_multicast(True):
         print("the multicast kernels are not available in this process", file=sys.stderr)
@@ -79,21 +95,22 @@ def main(argv=None) -> int:
     candidates = {}
     cmp_lib = load_compare()
     if cmp_lib is not None:
-        candidates["cublas_fp32_compute"] = cublas_callable(torch, cmp_lib, "hgemm_compare_cublas_fp32", A, B, C)
-        candidates["cublas_fp16_compute"] = cublas_callable(torch, cmp_lib, "hgemm_compare_cublas_fp16", A, B, C)
+        for name, entry in (("cublas_fp32_compute", "hgemm_compare_cublas_fp32"), ("cublas_fp16_compute", "hgemm_compare_cublas_fp16")):
+            calls = [cublas_callable(torch, cmp_lib, entry, A, b, C) for b in Bs]
+            candidates[name] = (lambda calls=calls: next_of(calls)())
     for text in args.plans.split(","):
         if text == "auto":
-            candidates["auto"] = lambda: api.b200Hgemm(A, B, C)
+            candidates["auto"] = lambda: api.b200Hgemm(A, next_b(), C)
         else:
             plan = parse_plan(text)
-            candidates[text] = (lambda plan=plan: api.hgemm_ex(A, B, C, plan))
+            candidates[text] = (lambda plan=plan: api.hgemm_ex(A, next_b(), C, plan))
 
     gflop = 2.0 * M * N * K / 1e9
     results = {name: [] for name in candidates}
     for _ in range(args.rounds):
         for name, fn in candidates.items():
             if args.graph:
-                ms = time_graph(torch, fn)
+                ms = time_graph(torch, fn, launches=3 * len(Bs), replays=3) if len(Bs) > 1 else time_graph(torch, fn)
             elif args.burst:
                 ms = time_burst(torch, fn, 3, args.steps)
             else:
@@ -102,8 +119,9 @@ def main(argv=None) -> int:
     if api.last_device_error() != 0:
         print("device-side wait expired", file=sys.stderr)
         return 1
-    print(json.dumps({"shape": [M, N, K], "tflops_median_min_max": {
-        name: [round(statistics.median(v), 1), round(min(v), 1), round(max(v), 1)] for name, v in results.items()}}))
+    print(json.dumps({"shape": [M, N, K], "b_copies": len(Bs), "tflops_median_min_max": {
+        name: [round(statistics.median(v), 1), round(min(v), 1), round(max(v), 1)] for name, v in results.items()},
+        "us_median": {name: round(gflop / statistics.median(v) * 1e3, 2) for name, v in results.items()}}))
     return 0
 
 

@@ -80,9 +80,20 @@ struct SkinnyTraits {
 
 // EPI: whole results get alpha * acc + beta * c_in + bias before their one rounding and leave in epi.c_type
 // (FP32 partials of cut k-ranges are left as they are: skinny_reduce_kernel applies the same to their sum).
-template <int MT, int STAGES, int KPS, int CG = 1, bool EPI = false>
+//
+// CK: the k-ranges of one column tile (p.slices of them, at least two) run as one thread-block cluster and sum
+// their partial results on chip. CTA `s` of the cluster owns rows [s * rows_per, (s + 1) * rows_per) of the
+// tile. Every CTA first turns its accumulator into rows of C (FP32) in its own ring; when all CTAs of the cluster
+// have done so (cluster barrier: every MMA has retired, every ring is free) it sends each owner that owner's
+// rows with one bulk copy from shared memory to shared memory, counted on a barrier of the owner; the owner
+// then adds the k-ranges in order -- the order and the arithmetic of skinny_reduce_kernel, so both forms give
+// the same bits -- and stores its rows of C. No workspace, no second kernel. With CG = 2 the cluster holds
+// p.slices pairs: rank = 2 * k-range + position in the pair.
+template <int MT, int STAGES, int KPS, int CG = 1, bool EPI = false, bool CK = false>
 __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_constant__ SkinnyParams p) {
     using T = SkinnyTraits<MT, STAGES, KPS, CG>;
+    static_assert(!CK || STAGES * T::kStageBytes >= (2 * MT + 8) * 128 * 4, "the ring must hold the accumulator and the other k-ranges' rows");
+    static_assert(16 * STAGES + 24 <= 256 && STAGES + 3 <= 32, "barrier area too small");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -95,13 +106,18 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
     const uint32_t tfull_bar = bars + 16u * STAGES;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_ptr + 16u * STAGES + 8u);
     volatile uint32_t *abort_flag = tmem_slot + 1;
+    const uint32_t inbox_bar = bars + 16u * STAGES + 16u;  // CK: counts the bytes the other k-ranges send to this CTA
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t cta_rank = (CG == 2) ? cluster_cta_rank() : 0u;
-    // consecutive CTAs take consecutive column tiles (the two CTAs of a pair: tiles 2i and 2i + 1 of one k-range)
-    const uint32_t tile = blockIdx.x % p.n_tiles;
-    const uint32_t slice = blockIdx.x / p.n_tiles;
+    // position in the cluster, position in the pair, and the pair's leader (the even rank)
+    const uint32_t cluster_rank = (CG == 2 || CK) ? cluster_cta_rank() : 0u;
+    const uint32_t cta_rank = (CG == 2) ? (cluster_rank & 1u) : 0u;
+    const uint32_t leader_rank = cluster_rank & ~1u;
+    // consecutive CTAs take consecutive column tiles (the two CTAs of a pair: tiles 2i and 2i + 1 of one k-range);
+    // with CK consecutive clusters do, and the CTAs (pairs) of a cluster take the k-ranges of one tile (pair of tiles)
+    const uint32_t tile = CK ? (blockIdx.x / (p.slices * CG)) * CG + cta_rank : blockIdx.x % p.n_tiles;
+    const uint32_t slice = CK ? cluster_rank / CG : blockIdx.x / p.n_tiles;
     const uint32_t kb0 = slice * p.kb_per_slice;
     const uint32_t kb1 = min(p.k_blocks, kb0 + p.kb_per_slice);
     const uint32_t n0 = tile * p.tile_w;
@@ -115,6 +131,8 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
             mbar_init(tfull_bar, 1);
         } else if (lane == static_cast<uint32_t>(STAGES) + 1u) {
             *abort_flag = 0;
+        } else if (CK && lane == static_cast<uint32_t>(STAGES) + 2u) {
+            mbar_init(inbox_bar, 1);
         }
         fence_mbar_init();
         __syncwarp();
@@ -147,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
     const uint32_t tmem_base = (CG == 1 && warp == 0) ? 0u : *tmem_slot;
     pdl_launch_dependents();
     if (threadIdx.x == 0) B200_STAMP(1);
+    uint32_t ready = 1;  // epilogue warps: the accumulator is complete
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -178,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
                 } else {
                     // both CTAs' copies complete on the leader's barrier; the leader posts the byte count of the pair
                     if (cta_rank == 0) mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * blocks * block_tx);
-                    const uint32_t leader_bar = map_to_cta(full_bar + 8u * stage, 0);
+                    const uint32_t leader_bar = map_to_cta(full_bar + 8u * stage, leader_rank);
                     for (uint32_t j = 0; j < blocks; ++j) {
                         const uint32_t sw = slot + j * T::kBlockBytes;
                         const int32_t kx = static_cast<int32_t>((kb + j) * kBK);
@@ -222,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
                 if (CG == 1) {
                     umma_commit(empty_bar + 8u * stage);
                 } else {
-                    umma_commit_pair(empty_bar + 8u * stage, 0x3);
+                    umma_commit_pair(empty_bar + 8u * stage, static_cast<uint16_t>(0x3u << leader_rank));
                 }
                 if (++stage == STAGES) {
                     stage = 0;
@@ -233,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
                 if (CG == 1) {
                     umma_commit(tfull_bar);
                 } else {
-                    umma_commit_pair(tfull_bar, 0x3);
+                    umma_commit_pair(tfull_bar, static_cast<uint16_t>(0x3u << leader_rank));
                 }
             }
             B200_STAMP(5);
@@ -248,10 +267,9 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
         const bool col_live = n < p.n && col_in_tile < p.tile_w;
         const bool staged = p.slices == 1 && p.tma_store != 0;  // whole results, through shared memory and one TMA store
         pdl_wait_prior_grids();  // C (or the workspace) may still be read by the previous kernel
-        uint32_t ready = 1;
         if (lane == 0) ready = mbar_wait(tfull_bar, 0, abort_flag) ? 1u : 0u;
         ready = __shfl_sync(0xffffffffu, ready, 0);
-        if (ready) {
+        if (ready && !CK) {
             tcgen05_fence_after_sync();
             if (threadIdx.x == 64) B200_STAMP(6);
             const uint32_t taddr = tmem_base + ((q * 32u) << 16);
@@ -316,6 +334,139 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_skinny_kernel(const __grid_
             }
         }
         if (threadIdx.x == 64) B200_STAMP(8);
+    }
+
+    if (CK) {
+        // ------------------------------------------------------------------ sum of the k-ranges inside the cluster
+        // Every thread of the cluster passes both cluster barriers, whatever its warp did before (a CTA whose
+        // wait expired still arrives; its error word is set below and the result is not to be used).
+        const uint32_t rows_per = (p.m + p.slices - 1u) / p.slices;  // rows of C per owner
+        const uint32_t m0 = slice * rows_per;                        // this CTA owns rows [m0, m0 + my_rows)
+        const uint32_t my_rows = m0 < p.m ? min(rows_per, p.m - m0) : 0u;
+        const uint32_t col_in_tile = ((warp & 3u) << 5) + lane;
+        // The ring is free once this CTA's MMAs have retired. Its first MT x 128 floats take this CTA's accumulator
+        // as rows of C ([row][128 columns]: an owner's rows are one contiguous block); behind them the rows this
+        // CTA owns arrive from the other k-ranges ([k-range][rows_per][128]).
+        const uint32_t staging = base;
+        const uint32_t inbox = base + MT * 512u;
+        const float *staging_f = reinterpret_cast<const float *>(base_ptr);
+        if (warp >= 2) {
+            if (ready) {
+                tcgen05_fence_after_sync();
+                if (threadIdx.x == 64) B200_STAMP(6);
+                const uint32_t taddr = tmem_base + (((warp & 3u) * 32u) << 16);
+#pragma unroll
+                for (uint32_t c = 0; c < MT / 16; ++c) {
+                    if (c * 16u < p.m) {  // uniform over the CTA
+                        uint32_t r[16];
+                        tmem_ld_32x32b_x16(taddr + c * 16u, r);
+                        tmem_ld_wait();
+                        float *row = reinterpret_cast<float *>(base_ptr) + c * 16u * 128u + col_in_tile;
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; ++j) row[j * 128u] = __uint_as_float(r[j]);  // 32 lanes: 128 consecutive bytes
+                    }
+                }
+                fence_proxy_async_smem();  // the bulk copies below read what the threads wrote
+            }
+            if (threadIdx.x == 64 && my_rows > 0) mbar_arrive_expect_tx(inbox_bar, (p.slices - 1u) * my_rows * 512u);
+        }
+        cluster_sync_all();  // every CTA of the cluster has staged its accumulator: every ring is free to receive
+        if (warp == 2 && ready) {
+            // lane 4 * o + q sends the q-th quarter of owner o's rows: more copies in flight than one per owner
+            const uint32_t o = lane >> 2, quarter = lane & 3u;
+            const uint32_t first = o * rows_per;
+            if (o < p.slices && o != slice && first < p.m) {
+                const uint32_t bytes = min(rows_per, p.m - first) * 128u;  // a quarter of the rows' 512 bytes each
+                const uint32_t to = o * CG + cta_rank;
+                bulk_copy_to_cluster(map_to_cta(inbox + slice * rows_per * 512u + quarter * bytes, to),
+                                     staging + first * 512u + quarter * bytes, bytes, map_to_cta(inbox_bar, to));
+            }
+        }
+        uint32_t arrived = 1;
+        if (my_rows > 0) {
+            if (lane == 0) arrived = mbar_wait(inbox_bar, 0, abort_flag) ? 1u : 0u;  // false soon when the CTA has given up
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        }
+        // No CTA may leave (and hand its shared memory on) while a copy out of it may still be running. A CTA
+        // arrives here when everything sent to it has come in, so when all have arrived every copy inside the
+        // cluster is complete; the wait comes after this CTA's own additions, which the others need not see.
+        cluster_arrive_relaxed();  // (nothing this CTA wrote is read by the others after this point)
+        if (my_rows > 0) {
+            // All six warps add (the producer and the MMA issuer have nothing else left to do). A warp takes whole
+            // rows: lane l adds columns 4l ... 4l + 3 of every k-range's copy of the row -- one 16-byte load each,
+            // four k-ranges' loads issued before the first addition -- and stores four results at once.
+            constexpr uint32_t kSumWarps = kThreads / 32;
+            const uint32_t c4 = lane * 4u;
+            const uint32_t n = n0 + c4;
+            const bool vec_ok = (p.n & 3u) == 0 && !EPI;  // 8-byte stores of four halves
+            // where k-range u's copy of this CTA's first row starts (in floats from the start of the ring)
+            uint32_t from[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8; ++u) from[u] = (u == slice ? m0 * 128u : (MT + u * rows_per) * 128u) + c4;
+            if (arrived && n < p.n && c4 < p.tile_w) {
+                for (uint32_t i = warp; i < my_rows; i += 2u * kSumWarps) {
+                    // two rows per trip: i and i + kSumWarps
+                    const float *row = staging_f + i * 128u;
+                    const bool second = i + kSumWarps < my_rows;
+                    float4 acc[2];
+                    acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (uint32_t s0 = 0; s0 < 8; s0 += 4u) {  // k-range order: the order of skinny_reduce_kernel
+                        if (s0 < p.slices) {
+                            float4 v[4][2];
+#pragma unroll
+                            for (uint32_t u = 0; u < 4; ++u) {
+                                if (s0 + u < p.slices) {
+                                    v[u][0] = *reinterpret_cast<const float4 *>(row + from[s0 + u]);
+                                    if (second) v[u][1] = *reinterpret_cast<const float4 *>(row + from[s0 + u] + kSumWarps * 128u);
+                                }
+                            }
+#pragma unroll
+                            for (uint32_t u = 0; u < 4; ++u) {
+                                if (s0 + u < p.slices) {
+#pragma unroll
+                                    for (uint32_t r = 0; r < 2; ++r) {
+                                        if (r == 0 || second) {
+                                            acc[r].x += v[u][r].x;
+                                            acc[r].y += v[u][r].y;
+                                            acc[r].z += v[u][r].z;
+                                            acc[r].w += v[u][r].w;
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t r = 0; r < 2; ++r) {
+                        if (r == 0 || second) {
+                            const uint32_t m = m0 + i + kSumWarps * r;
+                            const size_t at = static_cast<size_t>(m) * p.n + n;
+                            const float out[4] = {acc[r].x, acc[r].y, acc[r].z, acc[r].w};
+                            if (vec_ok) {
+                                uint2 packed;
+                                packed.x = pack_half2_rn(__float_as_uint(out[0]), __float_as_uint(out[1]));
+                                packed.y = pack_half2_rn(__float_as_uint(out[2]), __float_as_uint(out[3]));
+                                *reinterpret_cast<uint2 *>(p.c + at) = packed;
+                            } else {
+#pragma unroll
+                                for (uint32_t e = 0; e < 4; ++e) {
+                                    if (n + e < p.n) {
+                                        if (EPI) {
+                                            store_c_elem(p.c, at + e, fused_value(p.epi, out[e], m, n + e, p.n), p.epi.c_type);
+                                        } else {
+                                            p.c[at + e] = __float2half_rn(out[e]);
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (threadIdx.x == 64) B200_STAMP(8);
+        }
+        cluster_wait_acquire();
     }
 
     // ---------------------------------------------------------------------- teardown

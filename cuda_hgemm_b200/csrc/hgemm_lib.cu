@@ -79,8 +79,8 @@ struct DeviceState {
     size_t host_a_bytes = 0, host_b_bytes = 0, host_c_bytes = 0;
     cudaStream_t host_stream[3] = {nullptr, nullptr, nullptr};  // upload, GEMMs, download
     cudaEvent_t host_event[2] = {nullptr, nullptr};
-    bool attr_set[64] = {};
-    int max_clusters[64] = {};  // CTA pairs the device can keep resident at once, per pair kernel
+    bool attr_set[96] = {};
+    int max_clusters[96] = {};  // CTA pairs the device can keep resident at once, per pair kernel
     TensorMapSlot tm_cache[64 * kTensorMapWays];
     uint64_t tm_clock = 0;
 };
@@ -325,6 +325,8 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
         if (pl.bn != 16 && pl.bn != 32 && pl.bn != 64 && pl.bn != 128) return B200_HGEMM_ERR_UNSUPPORTED;
         // group_m is the width of a column tile here: a multiple of 8 from 8 to 128, or 0 for the library's choice
         if (pl.group_m != 0 && (pl.group_m < 8 || pl.group_m > 128 || pl.group_m % 8 != 0)) return B200_HGEMM_ERR_UNSUPPORTED;
+        // grid names how several k-ranges are summed: 0 the library's choice, 1 inside clusters, 2 through the workspace
+        if (pl.grid > 2) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.variant == B200_VARIANT_CTA2_MCAST) {
         // bn names the CTA arrangement here: 256 = 128 x 256 per CTA, 512 = 256 x 256 per CTA
         if ((pl.bn != 256 && pl.bn != 512) || N % 8 != 0 || !mc_launch_fn(pl.bn)) return B200_HGEMM_ERR_UNSUPPORTED;
@@ -497,7 +499,12 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         // 65 ... 128 rows against a large weight matrix: the short-A kernel on CTA pairs, which fetch the rows
         // of A once per pair (measured at N = 14336, K = 4096, M = 128: 26.3 us against 28.0 for 128-row tiles
         // of single CTAs; at N = 4096, K = 14336 with four k-ranges: 30.6 against 33.7 for stream-k)
-        pl->variant = B200_VARIANT_SKINNY_PAIR;
+        // Where the column tiles are so few that k would be cut into three or more ranges, single CTAs instead:
+        // (at most) four k-ranges of a tile are one cluster that sums on chip (pairs would need clusters of six
+        // or eight, which the GPU cannot hold all at once). Measured at N = 4096, K = 14336, M = 128: 28.4 us against 30.7 for pairs with the workspace.
+        const uint32_t col_tiles = ceil_div_u32(N, 128);
+        const uint32_t k_ranges = static_cast<uint64_t>(col_tiles) * 5 < 3ull * sms ? sms / col_tiles : 1u;
+        pl->variant = k_ranges >= 3 ? B200_VARIANT_SKINNY : B200_VARIANT_SKINNY_PAIR;
         pl->bn = 128;
         return;
     }
@@ -911,6 +918,13 @@ static uint32_t skinny_tile_w(const b200_hgemm_plan &pl, const DeviceState &st, 
     return best_w;
 }
 
+// B200_HGEMM_SKINNY_WORKSPACE_SUM (any value): the library never chooses the sum inside clusters by itself (for
+// measurements; a plan that asks for it with grid = 1 still gets it).
+static bool skinny_workspace_sum_forced() {
+    static const bool on = (getenv("B200_HGEMM_SKINNY_WORKSPACE_SUM") != nullptr);
+    return on;
+}
+
 static uint32_t skinny_slices(const b200_hgemm_plan &pl, const DeviceState &st, size_t N, size_t K) {
     const uint32_t tiles = ceil_div_u32(N, skinny_tile_w(pl, st, N));
     const uint32_t k_blocks = ceil_div_u32(K, 64);
@@ -921,6 +935,13 @@ static uint32_t skinny_slices(const b200_hgemm_plan &pl, const DeviceState &st, 
         slices = (tiles * 5 >= sms * 3) ? 1u : sms / tiles;
         const uint32_t most = k_blocks / 8 > 0 ? k_blocks / 8 : 1u;
         if (slices > most) slices = most;
+        // Four k-ranges summed inside a cluster beat more of them summed through the workspace as long as they
+        // still occupy two fifths of the SMs (measured at N = 2048 and 3072, K = 8192: 16 and 24 tiles, 11.0
+        // against 13.0 us and 12.8 against 13.6); single CTAs only -- pairs would be left with two k-ranges.
+        if (slices > 4 && pl.variant == B200_VARIANT_SKINNY && pl.grid != 2 && !skinny_workspace_sum_forced() &&
+            tiles * 4u * 5u >= sms * 2u) {
+            slices = 4;
+        }
     }
     if (slices > k_blocks) slices = k_blocks;
     if (slices < 1) slices = 1;
@@ -928,9 +949,24 @@ static uint32_t skinny_slices(const b200_hgemm_plan &pl, const DeviceState &st, 
     return ceil_div_u32(k_blocks, per);  // no empty slice
 }
 
+// How the k-ranges of a column tile are summed. plan.grid says: 1 = inside a thread-block cluster (the k-ranges of a
+// tile, times two CTAs for pairs, are one cluster of at most 8 CTAs: no workspace, no second kernel), 2 = through the
+// FP32 workspace and skinny_reduce_kernel, 0 = the library's choice: the cluster when it is at most four CTAs.
+// Returns 1 / 0, or -1 when the plan asks for a cluster that would be larger than 8 CTAs.
+static int skinny_sums_on_chip(const b200_hgemm_plan &pl, uint32_t slices) {
+    const uint32_t cg = pl.variant == B200_VARIANT_SKINNY_PAIR ? 2u : 1u;
+    if (slices < 2) return 0;
+    const bool fits = slices * cg <= 8u;
+    if (pl.grid == 1) return fits ? 1 : -1;
+    if (pl.grid == 2) return 0;
+    // left to the library: clusters of up to four CTAs (148 SMs hold far fewer clusters of eight than 148 / 8:
+    // measured, 16 of them ran as two waves)
+    return (slices * cg <= 4u && !skinny_workspace_sum_forced()) ? 1 : 0;
+}
+
 static size_t skinny_workspace_bytes(const b200_hgemm_plan &pl, const DeviceState &st, size_t N, size_t K) {
     const uint32_t slices = skinny_slices(pl, st, N, K);
-    if (slices <= 1) return 0;
+    if (slices <= 1 || skinny_sums_on_chip(pl, slices) == 1) return 0;
     const size_t n_pad = (N + 31) / 32 * 32;
     return static_cast<size_t>(slices) * pl.bn * n_pad * sizeof(float);
 }
@@ -947,20 +983,26 @@ static uint32_t skinny_prefetch_kb() {
     return kb;
 }
 
-template <int MT, int STAGES, int KPS, int CG, bool EPI>
+template <int MT, int STAGES, int KPS, int CG, bool EPI, bool CK>
 static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream);
 
-// The kernel for this tile height and CTA grouping, plain or with the fused epilogue (attribute slots 32 up).
+// The kernel for this tile height and CTA grouping, plain or with the fused epilogue (attribute slots 32 up), its
+// k-ranges summed through the workspace or (on_chip) inside clusters (attribute slots 64 up: eight plain, eight fused).
 template <int MT, int STAGES, int KPS, int CG = 1>
-static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool fused) {
-    if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true>(st, attr_slot + 21, p, stream);
-    return launch_skinny_kernel<MT, STAGES, KPS, CG, false>(st, attr_slot, p, stream);
+static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool fused, bool on_chip) {
+    if (on_chip) {
+        const int ck_slot = 64 + (CG == 2 ? 4 + attr_slot - 25 : attr_slot - 11);
+        if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true, true>(st, ck_slot + 8, p, stream);
+        return launch_skinny_kernel<MT, STAGES, KPS, CG, false, true>(st, ck_slot, p, stream);
+    }
+    if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true, false>(st, attr_slot + 21, p, stream);
+    return launch_skinny_kernel<MT, STAGES, KPS, CG, false, false>(st, attr_slot, p, stream);
 }
 
-template <int MT, int STAGES, int KPS, int CG, bool EPI>
+template <int MT, int STAGES, int KPS, int CG, bool EPI, bool CK>
 static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream) {
     using T = SkinnyTraits<MT, STAGES, KPS, CG>;
-    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS, CG, EPI>;
+    auto kern = hgemm_skinny_kernel<MT, STAGES, KPS, CG, EPI, CK>;
     if (!st.attr_set[attr_slot]) {
         std::lock_guard<std::mutex> lock(st.mu);
         if (!st.attr_set[attr_slot]) {
@@ -983,9 +1025,9 @@ static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyPara
         attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
         ++n_attrs;
     }
-    if (CG == 2) {  // the grid is a whole number of pairs (n_tiles is even)
+    if (CG == 2 || CK) {  // the grid is a whole number of pairs (n_tiles is even), or of clusters of one tile's k-ranges
         attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
-        attrs[n_attrs].val.clusterDim.x = 2;
+        attrs[n_attrs].val.clusterDim.x = CK ? p.slices * CG : 2;
         attrs[n_attrs].val.clusterDim.y = 1;
         attrs[n_attrs].val.clusterDim.z = 1;
         ++n_attrs;
@@ -1036,11 +1078,14 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     // whole results leave through one TMA store per tile (a plain row-major box of tile_w x bn) when C can
     // have a tensor map: rows of N halves must be a multiple of 16 bytes
     p.tma_store = (pl.tma_store && N % 8 == 0 && p.slices == 1 && p.epi.c_type != kOutF32) ? 1u : 0u;  // FP32 leaves by element
+    const int sum_on_chip = skinny_sums_on_chip(pl, p.slices);
+    if (sum_on_chip < 0) return B200_HGEMM_ERR_UNSUPPORTED;
+    const bool on_chip = sum_on_chip == 1;
     if (p.tma_store) {
         rc = get_tensor_map(st, C, M, N, static_cast<uint32_t>(pl.bn), p.tile_w, &p.tm_c, false);
         if (rc != B200_HGEMM_OK) return rc;
     }
-    if (p.slices > 1) {
+    if (p.slices > 1 && !on_chip) {
         const size_t need = skinny_workspace_bytes(pl, st, N, K);
         uint8_t *ws = nullptr;
         if (ws_override) {
@@ -1054,24 +1099,24 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     }
     if (pairs) {
         if (pl.bn == 16) {
-            rc = launch_skinny<16, 6, 2, 2>(st, 25, p, stream, fused);
+            rc = launch_skinny<16, 6, 2, 2>(st, 25, p, stream, fused, on_chip);
         } else if (pl.bn == 32) {
-            rc = launch_skinny<32, 6, 2, 2>(st, 26, p, stream, fused);
+            rc = launch_skinny<32, 6, 2, 2>(st, 26, p, stream, fused, on_chip);
         } else if (pl.bn == 64) {
-            rc = launch_skinny<64, 5, 2, 2>(st, 27, p, stream, fused);
+            rc = launch_skinny<64, 5, 2, 2>(st, 27, p, stream, fused, on_chip);
         } else {
-            rc = launch_skinny<128, 4, 2, 2>(st, 28, p, stream, fused);
+            rc = launch_skinny<128, 4, 2, 2>(st, 28, p, stream, fused, on_chip);
         }
     } else if (pl.bn == 16) {
-        rc = launch_skinny<16, 6, 2>(st, 11, p, stream, fused);
+        rc = launch_skinny<16, 6, 2>(st, 11, p, stream, fused, on_chip);
     } else if (pl.bn == 32) {
-        rc = launch_skinny<32, 5, 2>(st, 12, p, stream, fused);
+        rc = launch_skinny<32, 5, 2>(st, 12, p, stream, fused, on_chip);
     } else if (pl.bn == 64) {
-        rc = launch_skinny<64, 4, 2>(st, 13, p, stream, fused);
+        rc = launch_skinny<64, 4, 2>(st, 13, p, stream, fused, on_chip);
     } else {
-        rc = launch_skinny<128, 3, 2>(st, 14, p, stream, fused);
+        rc = launch_skinny<128, 3, 2>(st, 14, p, stream, fused, on_chip);
     }
-    if (rc != B200_HGEMM_OK || p.slices == 1) return rc;
+    if (rc != B200_HGEMM_OK || p.slices == 1 || on_chip) return rc;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(ceil_div_u32(N, kSkinnyReduceThreads), static_cast<unsigned>(M), 1);

@@ -52,8 +52,28 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     return r;
 }
 
+// One float into the shared memory of another CTA of the cluster (an address from map_to_cta).
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
+// Bulk copy from this CTA's shared memory into another CTA's of the cluster; the bytes are counted on a barrier
+// in the destination CTA. Both cluster addresses come from map_to_cta with the same rank; addresses and size
+// are multiples of 16 bytes. The source must stay allocated and unchanged until the destination's barrier has
+// seen the bytes.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t cluster_dst, uint32_t local_src, uint32_t bytes,
+                                                     uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(cluster_dst),
+                 "r"(local_src), "r"(bytes), "r"(cluster_bar)
+                 : "memory");
+}
+
 __device__ __forceinline__ void cluster_arrive_release() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+// Arrival that publishes nothing: for a barrier that only says "what was sent to me has come in".
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void cluster_wait_acquire() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -59,9 +59,14 @@ enum {
                                    allocations of the GPU the call runs on */
     B200_VARIANT_SKINNY = 5,     /* M <= 128 (decode batches): B streams through the MMA's row operand and C is
                                    accumulated transposed; plan.bn = rows of A per tile (16, 32, 64 or 128, >= M),
-                                   plan.parts = equal k-ranges per column tile (0 = library's choice), summed
-                                   from an FP32 workspace when there is more than one; plan.group_m = columns of
-                                   C per tile (a multiple of 8 up to 128; 0 = library's choice) */
+                                   plan.parts = equal k-ranges per column tile (0 = library's choice); plan.group_m =
+                                   columns of C per tile (a multiple of 8 up to 128; 0 = library's choice). More than
+                                   one k-range is summed either on chip -- the k-ranges of a tile run as one
+                                   thread-block cluster (at most 8 CTAs) and add their results through distributed
+                                   shared memory: no workspace, no second kernel -- or from an FP32 workspace by a
+                                   second kernel; both give the same bits. plan.grid = 1 asks for the cluster
+                                   (B200_HGEMM_ERR_UNSUPPORTED when it would be larger than 8 CTAs), 2 for the
+                                   workspace, 0 leaves it to the library (the cluster whenever it fits) */
     B200_VARIANT_HYBRID = 6,     /* as STREAMK, but every full wave of tiles (parts tiles each) is computed whole
                                    and only the tiles of the ragged last wave are cut into k-ranges */
     B200_VARIANT_SKINNY_PAIR = 7, /* as SKINNY on CTA pairs (cta_group::2): two neighbouring column tiles share
@@ -82,7 +87,8 @@ typedef struct b200_hgemm_plan {
     int32_t parts;     /* STREAMK: number of equal k-ranges = CTAs launched; 0 = one per SM */
     int32_t group_m;   /* rasterisation band height in row blocks; 0 = library default */
     int32_t tma_store; /* 1: epilogue writes C with TMA stores (needs N % 8 == 0); 0: plain stores */
-    int32_t grid;      /* CTA1/CTA2: CTAs launched (0 = min(tiles, SMs)); informational for STREAMK */
+    int32_t grid;      /* CTA1/CTA2: CTAs launched (0 = min(tiles, SMs)); informational for STREAMK;
+                        * SKINNY/SKINNY_PAIR: how several k-ranges are summed (see B200_VARIANT_SKINNY) */
     int32_t stages;    /* CTA1/CTA2: depth of the operand ring; 0 = the kernel's default (its deepest). Shallower
                         * rings exist for measurements and the autotuner: CTA1 bn 256: 3, bn 128: 2, bn 64: 3;
                         * CTA2 bn 256: 4 or 5, bn 128: 3; anything else is B200_HGEMM_ERR_UNSUPPORTED */

@@ -101,13 +101,20 @@ def test_plan_selection_covers_the_benchmark_shapes(native_lib):
     assert api.workspace_bytes(16, 14336, 4096, wide) == 0
     skinny = api.select_plan_untuned(48, 4096, 14336)
     assert skinny.variant == _native.VARIANT_SKINNY and skinny.bn == 64
-    assert api.workspace_bytes(48, 4096, 14336, skinny) > 0
-    # 65 ... 128 rows against a large B: the same kernel on CTA pairs, k cut where the column tiles are few
+    assert api.workspace_bytes(48, 4096, 14336, skinny) == 0  # four k-ranges per tile: one cluster, summed on chip
+    through_workspace = api.select_plan_untuned(48, 4096, 14336)
+    through_workspace.grid = 2
+    assert api.workspace_bytes(48, 4096, 14336, through_workspace) > 0
+    # 16 column tiles would make nine k-ranges: four of them in one cluster instead (64 of 148 SMs)
+    assert api.workspace_bytes(16, 2048, 8192, api.select_plan_untuned(16, 2048, 8192)) == 0
+    # four column tiles: 16 CTAs would be too few, 37 k-ranges go through the workspace
+    assert api.workspace_bytes(16, 512, 8192, api.select_plan_untuned(16, 512, 8192)) > 0
+    # 65 ... 128 rows against a large B: the same kernel on CTA pairs; single CTAs with k cut where the column tiles are few
     wide128 = api.select_plan_untuned(128, 14336, 4096)
     assert (wide128.variant, wide128.bn) == (_native.VARIANT_SKINNY_PAIR, 128)
     assert api.workspace_bytes(128, 14336, 4096, wide128) == 0
-    mid = api.select_plan_untuned(96, 4096, 14336)
-    assert mid.variant == _native.VARIANT_SKINNY_PAIR and api.workspace_bytes(96, 4096, 14336, mid) > 0
+    mid = api.select_plan_untuned(96, 4096, 14336)  # single CTAs, so that the four k-ranges fit a cluster of four
+    assert (mid.variant, mid.bn) == (_native.VARIANT_SKINNY, 128) and api.workspace_bytes(96, 4096, 14336, mid) == 0
     # small problems of that height keep the 128-row tiles or k-ranges over them
     assert api.select_plan_untuned(100, 512, 4096).variant in (_native.VARIANT_CTA1, _native.VARIANT_STREAMK)
     assert api.workspace_bytes(8192, 8192, 8192, big) == 0
@@ -169,6 +176,10 @@ def test_every_plan_the_rules_pick_is_one_the_kernels_can_serve(native_lib):
         assert p.variant in (V.VARIANT_CTA1, V.VARIANT_CTA2, V.VARIANT_STREAMK, V.VARIANT_CTA2_MCAST, V.VARIANT_SKINNY,
                              V.VARIANT_SKINNY_PAIR), what
         assert p.parts == 0 and p.grid == 0 and p.group_m == 0, what
+        if p.variant == V.VARIANT_SKINNY and p.bn == 128:
+            # 65 ... 128 rows on single CTAs only where k would be cut into three or more ranges (four, one cluster per tile)
+            assert 64 < M <= 128 and N >= 2048 and K >= 1024 and 148 // -(-N // 128) >= 3, what
+            continue
         if p.variant == V.VARIANT_SKINNY:
             assert M <= 64 and p.bn in (16, 32, 64) and M <= p.bn and (p.bn == 16 or M > p.bn // 2), what
             continue
@@ -193,9 +204,9 @@ def test_workspace_sizes_callers_can_rely_on(native_lib):
     """b200_hgemm_workspace_bytes for the kernels that cut k (a caller sizing its own workspace uses these)."""
     from cuda_hgemm_b200 import api
 
-    def plan(variant, bn, parts=0):
+    def plan(variant, bn, parts=0, grid=0):
         p = _native.Plan()
-        p.variant, p.bn, p.parts, p.tma_store = variant, bn, parts, 1
+        p.variant, p.bn, p.parts, p.tma_store, p.grid = variant, bn, parts, 1, grid
         return p
 
     header = 64 * 1024
@@ -205,9 +216,16 @@ def test_workspace_sizes_callers_can_rely_on(native_lib):
     # never more k-ranges than (tile, stage) units: 2 tiles x 2 stages of two k-blocks each
     assert api.workspace_bytes(128, 256, 256, plan(_native.VARIANT_STREAMK, 128)) == header + 4 * 2 * 128 * 128 * 4
     assert api.workspace_bytes(128, 256, 256, plan(_native.VARIANT_HYBRID, 128)) == header + 4 * 2 * 128 * 128 * 4
-    # short A: slices x tile height x padded N floats when k is cut (32 column tiles -> 4 slices), nothing otherwise
-    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY, 64)) == 4 * 64 * 4096 * 4
-    assert api.workspace_bytes(48, 4100, 14336, plan(_native.VARIANT_SKINNY, 64, parts=3)) == 3 * 64 * 4128 * 4
+    # short A, k cut (32 column tiles -> 4 k-ranges) and summed through the workspace (plan.grid = 2): k-ranges x tile
+    # height x padded N floats; nothing when the k-ranges are summed inside clusters (the library's choice up to four
+    # CTAs per cluster, or plan.grid = 1 up to eight) or when k is whole
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY, 64, grid=2)) == 4 * 64 * 4096 * 4
+    assert api.workspace_bytes(48, 4100, 14336, plan(_native.VARIANT_SKINNY, 64, parts=3, grid=2)) == 3 * 64 * 4128 * 4
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY, 64)) == 0
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY, 64, parts=8, grid=1)) == 0
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY, 64, parts=8)) == 8 * 64 * 4096 * 4
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY_PAIR, 64)) == 4 * 64 * 4096 * 4  # clusters of eight
+    assert api.workspace_bytes(48, 4096, 14336, plan(_native.VARIANT_SKINNY_PAIR, 64, parts=2)) == 0
     assert api.workspace_bytes(16, 14336, 4096, plan(_native.VARIANT_SKINNY, 16)) == 0
     # whole-tile kernels need none
     for variant, bn in ((_native.VARIANT_CTA1, 256), (_native.VARIANT_CTA2, 512), (_native.VARIANT_CTA2_MCAST, 512)):

@@ -340,6 +340,51 @@ def test_short_a_kernel_tile_widths_and_128_rows(cuda_device, case, variant):
     assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
 
 
+CLUSTER_SUM_CASES = [
+    # M, N, K, rows of A per tile, columns of C per tile (0 = the library's choice), k-ranges
+    (16, 256, 256, 16, 0, 2),        # two k-ranges of two k-blocks; each owner sums 8 rows
+    (1, 128, 192, 16, 0, 3),         # one row: owners 1 and 2 have nothing to sum
+    (9, 520, 200, 16, 0, 4),         # tails in M, N (not a multiple of 8) and K; rows 3 + 3 + 3 + 0
+    (16, 4096, 3584, 16, 0, 4),
+    (17, 264, 136, 32, 0, 2),
+    (32, 1000, 1096, 32, 72, 8),     # the largest cluster of single CTAs, narrow tiles
+    (64, 4096, 3584, 64, 0, 0),      # the library's choice: 32 tiles, four k-ranges
+    (100, 1032, 1096, 128, 0, 3),    # 34 + 34 + 32 rows
+    (128, 4096, 3584, 128, 0, 4),    # the transposed decode shape with a shorter K
+    (128, 777, 320, 128, 88, 5),     # five k-ranges of one k-block: pairs would need a cluster of ten
+]
+
+
+@pytest.mark.parametrize("variant", [_native.VARIANT_SKINNY, _native.VARIANT_SKINNY_PAIR], ids=["single", "pairs"])
+@pytest.mark.parametrize("case", CLUSTER_SUM_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-mt{c[3]}-w{c[4]}-p{c[5]}")
+def test_short_a_kernel_sums_k_ranges_inside_clusters(cuda_device, case, variant):
+    """plan.grid = 1: the k-ranges of a column tile are one thread-block cluster and add their partial results through
+    distributed shared memory; plan.grid = 2: through the FP32 workspace and the summing kernel. Same products, same
+    order of addition: the same bits. A cluster larger than eight CTAs is refused."""
+    M, N, K, mt, width, parts = case
+    A, B = make_inputs(M, N, K, seed=35, dist="normal")
+    cg = 2 if variant == _native.VARIANT_SKINNY_PAIR else 1
+    on_chip = plan_of(variant, mt, parts=parts, group_m=width, grid=1)
+    if parts * cg > 8:
+        import torch
+
+        dA, dB = (torch.from_numpy(x).to(cuda_device) for x in (A, B))
+        C = torch.empty((M, N), dtype=torch.float16, device=cuda_device)
+        with pytest.raises(_native.HgemmError) as e:
+            api.hgemm_ex(dA, dB, C, on_chip)
+        assert e.value.status == _native.ERR_UNSUPPORTED
+        return
+    assert api.workspace_bytes(M, N, K, on_chip) == 0
+    C = run(None, A, B, cuda_device, on_chip)
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"short-A cluster sum mt={mt} width={width} parts={parts} {(M, N, K)}")
+    through_workspace = plan_of(variant, mt, parts=parts, group_m=width, grid=2)
+    assert api.workspace_bytes(M, N, K, through_workspace) > 0
+    C2 = run(None, A, B, cuda_device, through_workspace)
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+    C3 = run(None, A, B, cuda_device, on_chip)
+    assert np.array_equal(C.view(np.uint16), C3.view(np.uint16))
+
+
 def test_short_a_kernel_refuses_more_rows_than_its_tile(cuda_device):
     import torch
 
@@ -701,16 +746,19 @@ FUSED_PLAN_CASES = [
     (40, 1000, 520, _native.VARIANT_SKINNY, 64, 0, 1),        # N % 8 != 0: by element
     (128, 2048, 1024, _native.VARIANT_SKINNY_PAIR, 128, 0, 1),
     (65, 1032, 1096, _native.VARIANT_SKINNY_PAIR, 128, 2, 1),
+    # the same two with the k-ranges summed through the workspace (an eighth field: plan.grid = 2) instead of on chip
+    (16, 4096, 3584, _native.VARIANT_SKINNY, 16, 3, 1, 2),
+    (65, 1032, 1096, _native.VARIANT_SKINNY_PAIR, 128, 2, 1, 2),
 ]
 
 
 @pytest.mark.parametrize("c_dtype", ["float16", "bfloat16", "float32"])
-@pytest.mark.parametrize("case", FUSED_PLAN_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-v{c[3]}-bn{c[4]}-p{c[5]}")
+@pytest.mark.parametrize("case", FUSED_PLAN_CASES, ids=lambda c: "x".join(map(str, c[:3])) + f"-v{c[3]}-bn{c[4]}-p{c[5]}" + ("-ws" if len(c) > 7 else ""))
 def test_fused_epilogue_on_every_kernel_family_and_output_type(cuda_device, case, c_dtype):
     """alpha, beta * c_in and bias on an explicit plan, C (and c_in) as FP16, BF16 or FP32."""
     import torch
 
-    M, N, K, variant, bn, parts, tma_store = case
+    M, N, K, variant, bn, parts, tma_store = case[:7]
     dtype = getattr(torch, c_dtype)
     A, B = make_inputs(M, N, K, seed=66)
     rng = np.random.default_rng(67)
@@ -720,7 +768,7 @@ def test_fused_epilogue_on_every_kernel_family_and_output_type(cuda_device, case
     ref = (alpha * oracle.gemm_f32(A, B) + np.float32(beta) * c_in.float().numpy() + bias.astype(np.float32)[None, :])
     dA, dB = to_dev(A, cuda_device), to_dev(B, cuda_device)
     C = torch.full((M, N), float("nan"), dtype=dtype, device=cuda_device)
-    plan = plan_of(variant, bn, parts=parts, tma_store=tma_store if N % 8 == 0 else 0)
+    plan = plan_of(variant, bn, parts=parts, tma_store=tma_store if N % 8 == 0 else 0, grid=case[7] if len(case) > 7 else 0)
     if variant == _native.VARIANT_CTA2 and bn == 512 and c_dtype == "float32":
         with pytest.raises(_native.HgemmError) as e:
             api.hgemm_fused(dA, dB, C, alpha, beta, to_dev(bias, cuda_device), c_in.to(cuda_device), plan=plan)
