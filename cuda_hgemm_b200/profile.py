@@ -59,9 +59,15 @@ CAPTURES = OrderedDict([
         TARGET + ["--shape", "128x14336x4096", "--dist", "normal", "--b-copies", "7", "--launches", "10"],
         "hgemm_skinny", 6, 3, (128, 14336, 4096))),
     ("hgemm_skinny_skinny16t", (
-        "the short-A kernel with four k-ranges at M=16, N=4096, K=14336 (B cycled through 7 copies); the summing kernel runs beside it",
+        "the short-A kernel with four k-ranges per column tile, summed inside clusters of four, at M=16, N=4096, K=14336 "
+        "(B cycled through 7 copies)",
         TARGET + ["--shape", "16x4096x14336", "--dist", "normal", "--b-copies", "7", "--launches", "10"],
         "hgemm_skinny", 6, 3, (16, 4096, 14336))),
+    ("hgemm_skinny_skinny128t", (
+        "the short-A kernel with four k-ranges per column tile, summed inside clusters of four, at M=128, N=4096, K=14336 "
+        "(B cycled through 7 copies)",
+        TARGET + ["--shape", "128x4096x14336", "--dist", "normal", "--b-copies", "7", "--launches", "10"],
+        "hgemm_skinny", 6, 3, (128, 4096, 14336))),
     ("launch_list_bench_square16384", (
         "every launch of `bench.py` at the default workload",
         [sys.executable, "bench.py", "--steps", "2", "--warmup", "3", "--no-sweep", "--no-workloads"],
