@@ -58,7 +58,7 @@ def candidate_plans(M: int, N: int, K: int):
     tiles256 = -(-M // 128) * -(-N // 256)
     for bn in (256, 128) + ((64,) if tiles256 <= 64 else ()):
         add(V.VARIANT_CTA1, bn)
-    for bn in (256, 224, 192, 160, 128):
+    for bn in (320, 288, 256, 224, 192, 160, 128):
         add(V.VARIANT_CTA2, bn)
     if N % 8 == 0 and K >= 1024 and M * N >= 2048 * 2048:
         add(V.VARIANT_CTA2, 512)

@@ -114,9 +114,17 @@ struct alignas(64) GemmParams {
 template <int BN, int STAGES, int CG, int KPS = 1>
 struct KernelTraits {
     static_assert(KPS == 1 || KPS == 2, "a stage holds one or two 64-wide k-blocks");
-    static_assert(BN == 64 || BN == 128 || BN == 160 || BN == 192 || BN == 224 || BN == 256, "tile widths the kernels are built for");
+    static_assert(BN == 64 || BN == 128 || BN == 160 || BN == 192 || BN == 224 || BN == 256 || BN == 288 || BN == 320,
+                  "tile widths the kernels are built for");
     static_assert((BN / CG) % 8 == 0 && BN % 32 == 0, "whole swizzle atoms per CTA, whole 32-column epilogue chunks");
     static_assert(CG == 1 || CG == 2, "CG is the CTA-pair size");
+    // Tiles wider than one MMA (N <= 256) are two MMAs of BN / 2 columns side by side in one accumulator; pairs
+    // only. Each CTA then stages two slabs of BN / 4 rows of B, one per MMA: an MMA of a pair takes its first
+    // N / 2 columns from the leader's slab and the other half from the peer's, so the slabs are cut to keep the
+    // accumulator's columns in the order of C's.
+    static constexpr bool kWide = BN > 256;
+    static_assert(!kWide || (CG == 2 && KPS == 1 && (BN / 4) % 8 == 0 && (BN / 2) % 16 == 0), "wide tiles: CTA pairs, one k-block per stage");
+    static constexpr uint32_t kAccStages = 2 * BN <= 512 ? 2 : 1;  // a wide tile's accumulator leaves no room for a second
     static constexpr uint32_t kARows = kBM;
     static constexpr uint32_t kBRows = BN / CG;
     static constexpr uint32_t kABytes = kARows * kBK * 2;
@@ -124,7 +132,7 @@ struct KernelTraits {
     static constexpr uint32_t kBlockBytes = kABytes + kBBytes;   // one k-block of A and B
     static constexpr uint32_t kStageBytes = KPS * kBlockBytes;  // [A0][B0] or [A0][B0][A1][B1]
     static constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;  // two accumulators; power of two
-    static constexpr uint32_t kAccStride = kTmemCols / 2;  // the second accumulator starts half way (BN columns for the widths that are powers of two times 64)
+    static constexpr uint32_t kAccStride = kTmemCols / 2;  // the second accumulator (if any) starts half way (BN columns for the widths that are powers of two times 64)
     static constexpr uint32_t kBarrierBytes = 256;
     static constexpr uint32_t kSmemBytes = 1024 + STAGES * kStageBytes + kStagingBytes + kBarrierBytes;
     static_assert((kBlockBytes % 1024) == 0, "operand slabs must keep 1024-byte alignment");
@@ -521,6 +529,12 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                             } else if (BATCHED) {
                                 tma_load_3d_pair(sa, &p.tm_a, kx, row_a, z, leader_bar);
                                 tma_load_3d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, z, leader_bar);
+                            } else if (T::kWide) {
+                                // two slabs of BN / 4 rows: columns [r * BN / 4, (r + 1) * BN / 4) of each half of the tile
+                                tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
+                                const int32_t half0 = static_cast<int32_t>(tc.n_blk * BN + cta_rank * (BN / 4));
+                                tma_load_2d_pair(sa + T::kABytes, &p.tm_b, kx, half0, leader_bar);
+                                tma_load_2d_pair(sa + T::kABytes + (BN / 4) * 128u, &p.tm_b, kx, half0 + BN / 2, leader_bar);
                             } else {
                                 tma_load_2d_pair(sa, &p.tm_a, kx, row_a, leader_bar);
                                 tma_load_2d_pair(sa + T::kABytes, &p.tm_b, kx, row_b, leader_bar);
@@ -545,14 +559,15 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc = BKN ? umma_idesc_f16_f32_b_mn(kBM * CG, BN) : umma_idesc_f16_f32(kBM * CG, BN);
+            constexpr uint32_t kMmaN = T::kWide ? BN / 2 : BN;  // columns one MMA writes
+            constexpr uint32_t idesc = BKN ? umma_idesc_f16_f32_b_mn(kBM * CG, kMmaN) : umma_idesc_f16_f32(kBM * CG, kMmaN);
             WorkWalker<MODE> work(p, worker, workers);
             Segment seg;
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
             while (ok && work.next(seg)) {
-                const uint32_t acc = it & 1u;
-                const uint32_t acc_phase = (it >> 1) & 1u;
+                const uint32_t acc = T::kAccStages == 2 ? (it & 1u) : 0u;
+                const uint32_t acc_phase = T::kAccStages == 2 ? ((it >> 1) & 1u) : (it & 1u);
                 if (!mbar_wait(tempty_bar + 8u * acc, acc_phase ^ 1u, abort_flag)) break;
                 tcgen05_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * T::kAccStride;
@@ -577,6 +592,12 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
                             // the MN-major B, 16 rows of k = two atoms of 1024 bytes -> +128
                             umma_f16<CG>(d_tmem, da + 2u * k, db + (BKN ? 128u : 2u) * k, idesc,
                                          (kb > seg.kb0 || j > 0 || k > 0) ? 1u : 0u);
+                            if (T::kWide) {
+                                // the tile's second half: the other slab of B (BN / 4 rows of 128 bytes further, in
+                                // the descriptor's 16-byte units), the accumulator's columns BN / 2 onward
+                                umma_f16<CG>(d_tmem + BN / 2, da + 2u * k, db + (BN / 4) * 8u + 2u * k, idesc,
+                                             (kb > seg.kb0 || j > 0 || k > 0) ? 1u : 0u);
+                            }
                         }
                     }
                     if (CG == 1) {
@@ -611,8 +632,8 @@ __global__ void __launch_bounds__(kThreads, 1) hgemm_tcgen05_kernel(const __grid
         uint32_t it = 0, store_buf = 0;
         pdl_wait_prior_grids();  // C and the workspace may still be in use by the previous kernel
         while (work.next(seg)) {
-            const uint32_t acc = it & 1u;
-            const uint32_t acc_phase = (it >> 1) & 1u;
+            const uint32_t acc = T::kAccStages == 2 ? (it & 1u) : 0u;
+            const uint32_t acc_phase = T::kAccStages == 2 ? ((it >> 1) & 1u) : (it & 1u);
             uint32_t zt = seg.tile;
             int32_t z = 0;
             if (BATCHED) {

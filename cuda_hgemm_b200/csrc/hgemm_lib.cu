@@ -339,6 +339,10 @@ static int validate_plan(const b200_hgemm_plan &pl, size_t N, size_t K) {
     } else if (pl.bn == 160 || pl.bn == 224) {
         // two more widths for the same purpose, on CTA pairs only
         if (pl.variant != B200_VARIANT_CTA2) return B200_HGEMM_ERR_UNSUPPORTED;
+    } else if (pl.bn == 288 || pl.bn == 320) {
+        // wider than one MMA: two MMAs side by side in one accumulator that fills tensor memory alone; CTA pairs,
+        // the default ring only
+        if (pl.variant != B200_VARIANT_CTA2 || pl.stages != 0) return B200_HGEMM_ERR_UNSUPPORTED;
     } else if (pl.bn != 64 && pl.bn != 128 && pl.bn != 256) {
         return B200_HGEMM_ERR_UNSUPPORTED;
     }
@@ -585,7 +589,9 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
     // (about 4 TB/s for this pattern): with full-height tiles that costs more than a ragged last
     // wave does, so stream-k only wins here when the tiles are few and k is long
     auto partial_us = [&](int bn) { return 2.0 * sms * 2.0 * (128.0 * bn * 4.0) / 4.0e6; };
-    constexpr int kCands = 8;
+    constexpr int kCands = 10;
+    const uint64_t pairs288 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 288);
+    const uint64_t pairs320 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 320);
     const uint64_t pairs192 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 192);
     const uint64_t pairs224 = static_cast<uint64_t>(ceil_div_u32(M, 256)) * ceil_div_u32(N, 224);
     // Waves of pair tiles, the last one counted by how full it is: behind at least one full wave a nearly empty
@@ -613,7 +619,18 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         // TFLOP/s, 2560^3 1160 against 990; no gain where 256-wide tiles fit one wave, as at 1792^3)
         {B200_VARIANT_CTA2, 192, pairs256 > pair_slots ? pair_waves(pairs192) * kb * 0.27 + 2.5 : 1e30},
         {B200_VARIANT_CTA2, 224, pairs256 > pair_slots ? pair_waves(pairs224) * kb * 0.308 + 2.5 : 1e30},
+        // pairs on tiles wider than one MMA (two MMAs of 144 or 160 columns side by side, which read the rows of A
+        // from shared memory twice: about 0.49 us per k-block against 0.335 for 256 columns): only where they turn
+        // two ragged waves into one. Measured at 2304 x 2304 x K (72 tiles of 256 x 288 on 74 pairs), burst
+        // protocol, against the best of the narrower pair tiles (two waves of 256 x 160): K = 1536 18.6 / 19.3 us,
+        // 2304 23.9 / 24.6, 4096 36.1 / 37.8, 8192 65.3 / 73.3; 2304 x 2560 x 2304 on 256 x 320: 24.5 / 25.0;
+        // 4608 x 1152 x 2048: 22.0 / 23.3. With several tiles per pair they lose (one accumulator: no overlap of
+        // epilogue and MMAs). The factors below are set under the narrower tiles' so that one wave wins.
+        {B200_VARIANT_CTA2, 288, (pairs256 > pair_slots && pairs288 <= pair_slots && N % 8 == 0) ? kb * 0.44 + 2.5 : 1e30},
+        {B200_VARIANT_CTA2, 320, (pairs256 > pair_slots && pairs320 <= pair_slots && N % 8 == 0) ? kb * 0.455 + 2.5 : 1e30},
     };
+    if (M % 256 != 0) cands[8].us *= 1.0 + 128.0 / static_cast<double>(M);
+    if (M % 256 != 0) cands[9].us *= 1.0 + 128.0 / static_cast<double>(M);
     if (M % 256 != 0) cands[7].us *= 1.0 + 128.0 / static_cast<double>(M);
     if (M % 256 != 0) cands[6].us *= 1.0 + 128.0 / static_cast<double>(M);
     if (M % 256 != 0) cands[3].us *= 1.0 + 128.0 / static_cast<double>(M);  // the pair's second CTA idles on the last rows
@@ -1266,7 +1283,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
 
     rc = get_tensor_map(st, A, M, K, 128, 64, &p.tm_a);
     if (rc != B200_HGEMM_OK) return rc;
-    rc = get_tensor_map(st, B, N, K, static_cast<uint32_t>(bn / cg), 64, &p.tm_b);
+    // (tiles wider than 256 columns stage two slabs of bn / 4 rows per CTA, one per MMA)
+    rc = get_tensor_map(st, B, N, K, static_cast<uint32_t>(bn > 256 ? bn / 4 : bn / cg), 64, &p.tm_b);
     if (rc != B200_HGEMM_OK) return rc;
     if (p.tma_store) {
         rc = get_tensor_map(st, C, M, N, 32, 64, &p.tm_c);
@@ -1312,6 +1330,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2, true>(st, 22, p, grid, stream);
         if (bn == 160) return launch_kernel<160, 3, 2, kModeTiles, 2, true>(st, 39, p, grid, stream);
         if (bn == 224) return launch_kernel<224, 3, 2, kModeTiles, 2, true>(st, 40, p, grid, stream);
+        if (bn == 288) return launch_kernel<288, 5, 2, kModeTiles, 1, true>(st, 82, p, grid, stream);
+        if (bn == 320) return launch_kernel<320, 5, 2, kModeTiles, 1, true>(st, 83, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2, true>(st, 20, p, grid, stream);
     }
     if (pl.variant == B200_VARIANT_CTA1) {
@@ -1333,6 +1353,8 @@ static int run_plan(DeviceState &st, const void *A, const void *B, void *C, size
         if (bn == 192) return launch_kernel<192, 3, 2, kModeTiles, 2>(st, 10, p, grid, stream);
         if (bn == 160) return launch_kernel<160, 3, 2, kModeTiles, 2>(st, 37, p, grid, stream);
         if (bn == 224) return launch_kernel<224, 3, 2, kModeTiles, 2>(st, 38, p, grid, stream);
+        if (bn == 288) return launch_kernel<288, 5, 2, kModeTiles>(st, 80, p, grid, stream);
+        if (bn == 320) return launch_kernel<320, 5, 2, kModeTiles>(st, 81, p, grid, stream);
         return launch_kernel<128, 4, 2, kModeTiles, 2>(st, 4, p, grid, stream);
     }
     if (pl.variant == B200_VARIANT_HYBRID_PAIR) {

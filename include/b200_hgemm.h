@@ -80,7 +80,8 @@ enum {
  * caller may edit them and pass the plan to b200_hgemm_ex(). */
 typedef struct b200_hgemm_plan {
     int32_t variant;   /* B200_VARIANT_* */
-    int32_t bn;        /* tile width in N: 64, 128, 192 or 256 (tile height is 128, or 256 per CTA pair); CTA2 also 160, 224.
+    int32_t bn;        /* tile width in N: 64, 128, 192 or 256 (tile height is 128, or 256 per CTA pair); CTA2 also 160, 224,
+                        * and 288, 320 (two MMAs side by side and a single accumulator: for shapes whose tiles then fit one wave).
                         * 512 with CTA2 or CTA2_MCAST selects the arrangement with 256 x 256 outputs per CTA
                         * instead: 512 x 256 tiles per pair (CTA2), 512 x 512 per group of four CTAs
                         * (CTA2_MCAST, which otherwise takes 256 only); both need N % 8 == 0 and tma_store = 1 */

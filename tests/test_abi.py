@@ -193,7 +193,7 @@ def test_every_plan_the_rules_pick_is_one_the_kernels_can_serve(native_lib):
         elif p.variant == V.VARIANT_STREAMK:
             assert p.bn in (64, 128, 256) and -(-K // 64) >= 8, what
         elif p.variant == V.VARIANT_CTA2:
-            assert p.bn in (192, 224, 256, 512) and M > 128, what
+            assert p.bn in (192, 224, 256, 288, 320, 512) and M > 128, what
         if p.bn == 512:  # 256 x 256 outputs per CTA: TMA stores only, long k, long runs
             assert N % 8 == 0 and -(-K // 64) >= 24 and 2.0 * M * N * K >= 2.0 * 4096 ** 3, what
     # the draw reaches every family

@@ -117,7 +117,7 @@ def test_single_cta_tiles(cuda_device, shape, bn, tma_store):
     assert_close_to_oracle(C, oracle.gemm_f32(A, B), f"cta1 bn={bn} tma_store={tma_store} {shape}")
 
 
-@pytest.mark.parametrize("bn", [128, 160, 192, 224, 256])
+@pytest.mark.parametrize("bn", [128, 160, 192, 224, 256, 288, 320])  # 288 and 320: two MMAs side by side per tile
 @pytest.mark.parametrize("shape", [(256, 256, 64), (256, 512, 320), (512, 2048, 1024), (328, 264, 136), (2048, 2048, 512),
                                    (3840, 3840, 192),   # 225 tiles of 256 x 256 on 74 pairs: several tiles per pair
                                    (1300, 3320, 136)],  # 78 such tiles, ragged in M, N and K
@@ -739,6 +739,8 @@ FUSED_PLAN_CASES = [
     (600, 776, 520, _native.VARIANT_CTA2, 192, 0, 1),
     (600, 776, 520, _native.VARIANT_CTA2, 160, 0, 1),         # the tile's last 32 columns leave by plain stores
     (1300, 3320, 136, _native.VARIANT_CTA2, 224, 0, 1),
+    (1300, 3320, 136, _native.VARIANT_CTA2, 288, 0, 1),       # wider than one MMA; one accumulator, several tiles per pair
+    (600, 776, 520, _native.VARIANT_CTA2, 320, 0, 0),
     (200, 1032, 1096, _native.VARIANT_STREAMK, 128, 33, 1),   # whole and cut tiles in one launch
     (200, 1032, 1096, _native.VARIANT_STREAMK, 64, 7, 0),
     (1000, 1032, 1096, _native.VARIANT_HYBRID, 256, 7, 1),
