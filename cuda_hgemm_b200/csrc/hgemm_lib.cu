@@ -619,8 +619,8 @@ static void select_plan(const DeviceState &st, size_t M, size_t N, size_t K, b20
         // TFLOP/s, 2560^3 1160 against 990; no gain where 256-wide tiles fit one wave, as at 1792^3)
         {B200_VARIANT_CTA2, 192, pairs256 > pair_slots ? pair_waves(pairs192) * kb * 0.27 + 2.5 : 1e30},
         {B200_VARIANT_CTA2, 224, pairs256 > pair_slots ? pair_waves(pairs224) * kb * 0.308 + 2.5 : 1e30},
-        // pairs on tiles wider than one MMA (two MMAs of 144 or 160 columns side by side, which read the rows of A
-        // from shared memory twice: about 0.49 us per k-block against 0.335 for 256 columns): only where they turn
+        // pairs on tiles wider than one MMA (two MMAs of 144 or 160 columns side by side, each with the fixed part
+        // of an MMA's time: about 0.49 us per k-block against 0.335 for 256 columns): only where they turn
         // two ragged waves into one. Measured at 2304 x 2304 x K (72 tiles of 256 x 288 on 74 pairs), burst
         // protocol, against the best of the narrower pair tiles (two waves of 256 x 160): K = 1536 18.6 / 19.3 us,
         // 2304 23.9 / 24.6, 4096 36.1 / 37.8, 8192 65.3 / 73.3; 2304 x 2560 x 2304 on 256 x 320: 24.5 / 25.0;
