@@ -56,3 +56,18 @@ def test_refinements_vary_one_knob_at_a_time():
     for p in around + sk + short:
         assert lib.b200_hgemm_plan_supported(8192, 8192, 8192, ctypes.byref(p)) == _native.OK or p.variant in (
             _native.VARIANT_SKINNY, _native.VARIANT_SKINNY_PAIR)
+
+
+def test_plan_spelling_of_the_timing_tools():
+    """abtest / timeline / profile_target spell a plan `variant:bn[:gN][:pN][:sN][:cN][:nt]`."""
+    from cuda_hgemm_b200.abtest import parse_plan
+
+    p = parse_plan("skinny:128:p4:c1")
+    assert (p.variant, p.bn, p.parts, p.grid, p.group_m, p.tma_store) == (_native.VARIANT_SKINNY, 128, 4, 1, 0, 1)
+    p = parse_plan("skinny2:64:g104:c2:nt")
+    assert (p.variant, p.bn, p.group_m, p.grid, p.tma_store) == (_native.VARIANT_SKINNY_PAIR, 64, 104, 2, 0)
+    p = parse_plan("cta2:288")
+    assert (p.variant, p.bn, p.stages) == (_native.VARIANT_CTA2, 288, 0)
+    assert parse_plan("cta2:256:s5").stages == 5
+    # the wide pair tiles are among the candidates of a square
+    assert {(_native.VARIANT_CTA2, 288), (_native.VARIANT_CTA2, 320)} <= keys(2304, 2304, 2304)
