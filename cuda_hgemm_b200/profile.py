@@ -68,6 +68,11 @@ CAPTURES = OrderedDict([
         "(B cycled through 7 copies)",
         TARGET + ["--shape", "128x4096x14336", "--dist", "normal", "--b-copies", "7", "--launches", "10"],
         "hgemm_skinny", 6, 3, (128, 4096, 14336))),
+    ("hgemm_tcgen05_wide288_square2304", (
+        "pairs on 256 x 288 tiles (two MMAs side by side per k-step) at M=N=K=2304: 72 tiles, one wave on 74 pairs "
+        "(operands and C together are 32 MB: they stay in L2, so the DRAM figures are small)",
+        TARGET + ["--shape", "2304x2304x2304", "--plan", "cta2:288", "--launches", "6"],
+        "hgemm_tcgen05_kernel", 3, 3, (2304, 2304, 2304))),
     ("launch_list_bench_square16384", (
         "every launch of `bench.py` at the default workload",
         [sys.executable, "bench.py", "--steps", "2", "--warmup", "3", "--no-sweep", "--no-workloads"],
