@@ -14,6 +14,7 @@ traffic compares with it. Text after a line ``## Reading`` in an existing summar
 from __future__ import annotations
 
 import argparse
+import os
 import csv
 import shlex
 import statistics
@@ -197,7 +198,8 @@ def main(argv=None) -> int:
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--only", default="", help="comma-separated capture names (default: all)")
     ap.add_argument("--out", default=str(ROOT / "profiles"))
-    ap.add_argument("--raw", default=str(ROOT / "gpurun_out" / "ncu_raw"), help="where the CSV files and logs go (scratch)")
+    ap.add_argument("--raw", default=os.environ.get("B200_PROFILE_RAW", str(ROOT / "ncu_raw")),
+                    help="where the CSV files and logs go (scratch; default: $B200_PROFILE_RAW or ncu_raw/ in the repository)")
     ap.add_argument("--summarise-only", action="store_true",
                     help="rewrite the summaries from the CSV files an earlier run left under --raw (e.g. captured on another machine)")
     args = ap.parse_args(argv)
