@@ -1861,8 +1861,15 @@ int b200_hgemm_plan_supported(size_t M, size_t N, size_t K, const b200_hgemm_pla
     if (!plan || M == 0 || N == 0 || K == 0) return B200_HGEMM_ERR_INVALID_ARG;
     const int rc = validate_plan(*plan, N, K);
     if (rc != B200_HGEMM_OK) return rc;
-    if ((plan->variant == B200_VARIANT_SKINNY || plan->variant == B200_VARIANT_SKINNY_PAIR) && M > static_cast<size_t>(plan->bn)) {
-        return B200_HGEMM_ERR_UNSUPPORTED;
+    if (plan->variant == B200_VARIANT_SKINNY || plan->variant == B200_VARIANT_SKINNY_PAIR) {
+        if (M > static_cast<size_t>(plan->bn)) return B200_HGEMM_ERR_UNSUPPORTED;
+        if (plan->grid == 1) {
+            // the k-ranges of a tile must fit one cluster of at most eight CTAs (no device is asked: where the
+            // plan leaves the number of k-ranges to the library, a B200's 148 SMs are assumed)
+            DeviceState nominal;
+            nominal.sm_count = 148;
+            if (skinny_sums_on_chip(*plan, skinny_slices(*plan, nominal, N, K)) < 0) return B200_HGEMM_ERR_UNSUPPORTED;
+        }
     }
     return B200_HGEMM_OK;
 }

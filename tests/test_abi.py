@@ -274,3 +274,23 @@ def test_public_header_is_plain_c(tmp_path):
                    "return b200_hgemm_status_string(0) != 0; }\n")
     for args in (["-std=c99", "-pedantic"], ["-x", "c++", "-std=c++11"]):
         subprocess.run([gcc, *args, "-Wall", "-Wextra", "-Werror", "-fsyntax-only", f"-I{root / 'include'}", str(src)], check=True)
+
+
+def test_plan_supported_knows_the_cluster_limit_of_the_short_a_kernels(native_lib):
+    """plan.grid = 1 asks for the k-ranges of a tile in one cluster: at most eight CTAs (four k-ranges for pairs)."""
+    import ctypes
+
+    def plan(variant, bn, parts, grid):
+        p = _native.Plan()
+        p.variant, p.bn, p.parts, p.tma_store, p.grid = variant, bn, parts, 1, grid
+        return p
+
+    lib = native_lib
+    ok = lambda p: lib.b200_hgemm_plan_supported(16, 4096, 14336, ctypes.byref(p))  # noqa: E731
+    assert ok(plan(_native.VARIANT_SKINNY, 16, 8, 1)) == _native.OK
+    assert ok(plan(_native.VARIANT_SKINNY, 16, 9, 1)) == _native.ERR_UNSUPPORTED
+    assert ok(plan(_native.VARIANT_SKINNY, 16, 9, 2)) == _native.OK
+    assert ok(plan(_native.VARIANT_SKINNY, 16, 9, 0)) == _native.OK       # the library's choice: through the workspace
+    assert ok(plan(_native.VARIANT_SKINNY_PAIR, 16, 4, 1)) == _native.OK
+    assert ok(plan(_native.VARIANT_SKINNY_PAIR, 16, 5, 1)) == _native.ERR_UNSUPPORTED
+    assert ok(plan(_native.VARIANT_SKINNY, 16, 4, 3)) == _native.ERR_UNSUPPORTED  # grid names nothing beyond 2 here
