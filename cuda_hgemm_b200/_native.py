@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = (
     "b200_mg_slab", "b200_mg_hgemm", "b200_mg_gather_c", "b200_mg_synchronize", "b200_mg_elapsed_ms_max",
     "b200_hgemm_enable_multicast", "b200_hgemm_multicast_state", "b200_hgemm_plan_supported",
     "b200_hgemm_release_workspaces", "b200_hgemm_synchronize", "b200_hgemm_streamk_static_last_error",
-    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched", "b200_hgemm_bkn", "b200_hgemm_host_a_after", "b200_sched_tile_coord_fast", "b200_debug_fast_div",
+    "b200_debug_wait_expiry_static", "b200_hgemm_fused_ex", "b200_hgemm_batched", "b200_hgemm_bkn", "b200_hgemm_host_a_after", "b200_sched_tile_coord_fast", "b200_debug_fast_div", "b200_debug_cluster_capacity",
 )
 
 OK = 0
@@ -140,6 +140,8 @@ def load() -> ctypes.CDLL:
     lib.b200_sched_tile_coord.restype = None
     lib.b200_sched_tile_coord_fast.argtypes = [c_uint32, c_uint32, c_uint32, c_uint32, POINTER(c_uint32), POINTER(c_uint32)]
     lib.b200_sched_tile_coord_fast.restype = None
+    lib.b200_debug_cluster_capacity.argtypes = [c_int]
+    lib.b200_debug_cluster_capacity.restype = None
     lib.b200_debug_fast_div.argtypes = [c_uint32, c_uint32]
     lib.b200_debug_fast_div.restype = c_uint32
     lib.b200_sched_segments.argtypes = [c_uint32, c_uint32, c_uint32, c_uint32, POINTER(c_uint32), c_uint32]

@@ -80,7 +80,8 @@ struct DeviceState {
     cudaStream_t host_stream[3] = {nullptr, nullptr, nullptr};  // upload, GEMMs, download
     cudaEvent_t host_event[2] = {nullptr, nullptr};
     bool attr_set[96] = {};
-    int max_clusters[96] = {};  // CTA pairs the device can keep resident at once, per pair kernel
+    int max_clusters[96] = {};
+    int ck_clusters[16][9] = {};  // short-A kernels that sum inside clusters: clusters of each size the device holds at once (-1: none)  // CTA pairs the device can keep resident at once, per pair kernel
     TensorMapSlot tm_cache[64 * kTensorMapWays];
     uint64_t tm_clock = 0;
 };
@@ -1000,24 +1001,29 @@ static uint32_t skinny_prefetch_kb() {
     return kb;
 }
 
+static std::atomic<int> g_debug_cluster_capacity{0};  // b200_debug_cluster_capacity(): > 0 overrides what the device reports
+
 template <int MT, int STAGES, int KPS, int CG, bool EPI, bool CK>
-static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream);
+static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool whole_wave_only);
 
 // The kernel for this tile height and CTA grouping, plain or with the fused epilogue (attribute slots 32 up), its
 // k-ranges summed through the workspace or (on_chip) inside clusters (attribute slots 64 up: eight plain, eight fused).
 template <int MT, int STAGES, int KPS, int CG = 1>
-static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool fused, bool on_chip) {
+// whole_wave_only (with on_chip): B200_HGEMM_ERR_UNSUPPORTED, and nothing launched, unless the device can hold all the
+// clusters at once (the caller then takes the workspace form).
+static int launch_skinny(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool fused, bool on_chip,
+                         bool whole_wave_only) {
     if (on_chip) {
         const int ck_slot = 64 + (CG == 2 ? 4 + attr_slot - 25 : attr_slot - 11);
-        if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true, true>(st, ck_slot + 8, p, stream);
-        return launch_skinny_kernel<MT, STAGES, KPS, CG, false, true>(st, ck_slot, p, stream);
+        if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true, true>(st, ck_slot + 8, p, stream, whole_wave_only);
+        return launch_skinny_kernel<MT, STAGES, KPS, CG, false, true>(st, ck_slot, p, stream, whole_wave_only);
     }
-    if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true, false>(st, attr_slot + 21, p, stream);
-    return launch_skinny_kernel<MT, STAGES, KPS, CG, false, false>(st, attr_slot, p, stream);
+    if (fused) return launch_skinny_kernel<MT, STAGES, KPS, CG, true, false>(st, attr_slot + 21, p, stream, false);
+    return launch_skinny_kernel<MT, STAGES, KPS, CG, false, false>(st, attr_slot, p, stream, false);
 }
 
 template <int MT, int STAGES, int KPS, int CG, bool EPI, bool CK>
-static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream) {
+static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyParams &p, cudaStream_t stream, bool whole_wave_only) {
     using T = SkinnyTraits<MT, STAGES, KPS, CG>;
     auto kern = hgemm_skinny_kernel<MT, STAGES, KPS, CG, EPI, CK>;
     if (!st.attr_set[attr_slot]) {
@@ -1051,6 +1057,28 @@ static int launch_skinny_kernel(DeviceState &st, int attr_slot, const SkinnyPara
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n_attrs;
+    if (CK && whole_wave_only) {
+        // clusters that wait for a second wave would double the kernel's time: ask once per cluster size
+        const uint32_t size = p.slices * CG;
+        const int idx = attr_slot - 64;
+        if (idx < 0 || idx >= 16 || size > 8) return B200_HGEMM_ERR_UNSUPPORTED;
+        int known;
+        {
+            std::lock_guard<std::mutex> lock(st.mu);
+            if (st.ck_clusters[idx][size] == 0) {
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+                    cudaGetLastError();
+                    n = -1;
+                }
+                st.ck_clusters[idx][size] = n;
+            }
+            known = st.ck_clusters[idx][size];
+        }
+        const int pretend = g_debug_cluster_capacity.load(std::memory_order_relaxed);
+        if (pretend > 0) known = pretend;
+        if (known < 0 || static_cast<uint64_t>(known) * size < cfg.gridDim.x) return B200_HGEMM_ERR_UNSUPPORTED;
+    }
     if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, p), "cudaLaunchKernelEx")) {
         cudaGetLastError();
         return B200_HGEMM_ERR_CUDA;
@@ -1102,8 +1130,28 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
         rc = get_tensor_map(st, C, M, N, static_cast<uint32_t>(pl.bn), p.tile_w, &p.tm_c, false);
         if (rc != B200_HGEMM_OK) return rc;
     }
-    if (p.slices > 1 && !on_chip) {
-        const size_t need = skinny_workspace_bytes(pl, st, N, K);
+    // the kernel for this tile height and CTA grouping, summing inside clusters or not
+    auto launch = [&](bool in_clusters, bool whole_wave_only) -> int {
+        if (pairs) {
+            if (pl.bn == 16) return launch_skinny<16, 6, 2, 2>(st, 25, p, stream, fused, in_clusters, whole_wave_only);
+            if (pl.bn == 32) return launch_skinny<32, 6, 2, 2>(st, 26, p, stream, fused, in_clusters, whole_wave_only);
+            if (pl.bn == 64) return launch_skinny<64, 5, 2, 2>(st, 27, p, stream, fused, in_clusters, whole_wave_only);
+            return launch_skinny<128, 4, 2, 2>(st, 28, p, stream, fused, in_clusters, whole_wave_only);
+        }
+        if (pl.bn == 16) return launch_skinny<16, 6, 2>(st, 11, p, stream, fused, in_clusters, whole_wave_only);
+        if (pl.bn == 32) return launch_skinny<32, 5, 2>(st, 12, p, stream, fused, in_clusters, whole_wave_only);
+        if (pl.bn == 64) return launch_skinny<64, 4, 2>(st, 13, p, stream, fused, in_clusters, whole_wave_only);
+        return launch_skinny<128, 3, 2>(st, 14, p, stream, fused, in_clusters, whole_wave_only);
+    };
+    if (on_chip) {
+        // The library's own choice must fit the device in one wave of clusters; where it does not (a device with
+        // fewer SMs per GPC than a B200's), the same k-ranges go through the workspace instead. A plan that asks
+        // for the clusters gets them, or the launch's error.
+        rc = launch(true, pl.grid != 1);
+        if (rc != B200_HGEMM_ERR_UNSUPPORTED || pl.grid == 1) return rc;
+    }
+    if (p.slices > 1) {
+        const size_t need = static_cast<size_t>(p.slices) * pl.bn * p.n_pad * sizeof(float);
         uint8_t *ws = nullptr;
         if (ws_override) {
             if (ws_override_bytes < need) return B200_HGEMM_ERR_WORKSPACE;
@@ -1114,26 +1162,8 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
         }
         p.partials = reinterpret_cast<float *>(ws);
     }
-    if (pairs) {
-        if (pl.bn == 16) {
-            rc = launch_skinny<16, 6, 2, 2>(st, 25, p, stream, fused, on_chip);
-        } else if (pl.bn == 32) {
-            rc = launch_skinny<32, 6, 2, 2>(st, 26, p, stream, fused, on_chip);
-        } else if (pl.bn == 64) {
-            rc = launch_skinny<64, 5, 2, 2>(st, 27, p, stream, fused, on_chip);
-        } else {
-            rc = launch_skinny<128, 4, 2, 2>(st, 28, p, stream, fused, on_chip);
-        }
-    } else if (pl.bn == 16) {
-        rc = launch_skinny<16, 6, 2>(st, 11, p, stream, fused, on_chip);
-    } else if (pl.bn == 32) {
-        rc = launch_skinny<32, 5, 2>(st, 12, p, stream, fused, on_chip);
-    } else if (pl.bn == 64) {
-        rc = launch_skinny<64, 4, 2>(st, 13, p, stream, fused, on_chip);
-    } else {
-        rc = launch_skinny<128, 3, 2>(st, 14, p, stream, fused, on_chip);
-    }
-    if (rc != B200_HGEMM_OK || p.slices == 1 || on_chip) return rc;
+    rc = launch(false, false);
+    if (rc != B200_HGEMM_OK || p.slices == 1) return rc;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(ceil_div_u32(N, kSkinnyReduceThreads), static_cast<unsigned>(M), 1);
@@ -2356,6 +2386,10 @@ void b200_sched_tile_coord_fast(uint32_t tile, uint32_t m_blocks, uint32_t n_blo
     TileCoord c = tile_coord_fast(tile, r);
     *m_blk = c.m_blk;
     *n_blk = c.n_blk;
+}
+
+void b200_debug_cluster_capacity(int clusters) {
+    g_debug_cluster_capacity.store(clusters > 0 ? clusters : 0, std::memory_order_relaxed);
 }
 
 uint32_t b200_debug_fast_div(uint32_t n, uint32_t d) {

@@ -311,6 +311,10 @@ int b200_debug_wait_expiry(uint32_t limit_ms, b200_stream_t stream);
 /* The same, reported where b200_hgemm_streamk_static reports: in the first word of its static array
  * (b200_hgemm_streamk_static_last_error() then returns 1). Allocates nothing. */
 int b200_debug_wait_expiry_static(uint32_t limit_ms, b200_stream_t stream);
+/* For tests of the short-A kernels' fall-back: with clusters > 0 the library behaves as if the device could hold
+ * only that many thread-block clusters at once, whatever their size, so its own choice of summing k-ranges inside
+ * clusters gives way to the workspace form when there are more clusters than that; 0 restores what the device says. */
+void b200_debug_cluster_capacity(int clusters);
 /* tcgen05 descriptor encoders (instruction descriptor; shared-memory matrix descriptor). */
 uint32_t b200_debug_idesc(uint32_t m, uint32_t n);
 uint64_t b200_debug_smem_desc(uint32_t smem_addr);

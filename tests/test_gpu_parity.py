@@ -385,6 +385,32 @@ def test_short_a_kernel_sums_k_ranges_inside_clusters(cuda_device, case, variant
     assert np.array_equal(C.view(np.uint16), C3.view(np.uint16))
 
 
+def test_short_a_kernel_falls_back_to_the_workspace_when_the_clusters_do_not_fit(cuda_device):
+    """The library's own choice of summing inside clusters needs all clusters on the device at once; where the device
+    (here: a pretended one) holds fewer, the same k-ranges go through the workspace: two launches instead of one, the
+    same bits. A plan that asks for the clusters still gets them."""
+    M, N, K = 16, 4096, 3584
+    A, B = make_inputs(M, N, K, seed=37, dist="normal")
+    auto = plan_of(_native.VARIANT_SKINNY, 16)       # 32 tiles, four k-ranges: 32 clusters of four
+    lib = _native.load()
+    before = api.launch_count()
+    C = run(None, A, B, cuda_device, auto)
+    assert api.launch_count() - before == 1
+    assert_close_to_oracle(C, oracle.gemm_f32(A, B), "short-A, clusters")
+    lib.b200_debug_cluster_capacity(8)
+    try:
+        before = api.launch_count()
+        C2 = run(None, A, B, cuda_device, auto)
+        assert api.launch_count() - before == 2      # the GEMM and the summing kernel
+        before = api.launch_count()
+        C3 = run(None, A, B, cuda_device, plan_of(_native.VARIANT_SKINNY, 16, grid=1))
+        assert api.launch_count() - before == 1
+    finally:
+        lib.b200_debug_cluster_capacity(0)
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+    assert np.array_equal(C.view(np.uint16), C3.view(np.uint16))
+
+
 def test_short_a_kernel_refuses_more_rows_than_its_tile(cuda_device):
     import torch
 
