@@ -11,8 +11,10 @@
 // of C, tensor-memory column = row of C. A stage is two k-blocks (32 KB of B and 2 x MT x 128 B of A)
 // under one barrier round trip, six stages deep for MT = 16: twice the bytes of B in flight per SM and
 // 0.20 us of issue time per k-block. One CTA computes one (column tile, k-range) pair; when the tiles
-// are too few to fill the GPU (N = 4096: 32) the k-range is cut into equal slices whose FP32 partial
-// results go to a workspace and are summed by skinny_reduce_kernel, which follows in the stream.
+// are too few to fill the GPU (N = 4096: 32) the k-range is cut into equal slices. Their FP32 partial
+// results are summed either inside a thread-block cluster that holds the k-ranges of one tile (template
+// parameter CK below: no workspace, no second kernel) or, for more k-ranges than a cluster takes, through a
+// workspace by skinny_reduce_kernel, which follows in the stream; both give the same bits.
 //
 // A column tile is tile_w <= 128 columns of C wide (a multiple of 8): the TMA box of B has tile_w rows,
 // the MMA still multiplies 128 rows of the stage's slab, and whatever lies in the rows the box did not
