@@ -991,14 +991,18 @@ static size_t skinny_workspace_bytes(const b200_hgemm_plan &pl, const DeviceStat
 
 // k-blocks of B a short-A CTA asks into L2 before it waits for the previous kernel (B200_HGEMM_SKINNY_PREFETCH
 // overrides it for measurements; 0 switches the prefetch off). Without programmatic dependent launch there
-// is no previous kernel to overlap with.
-static uint32_t skinny_prefetch_kb() {
-    static const uint32_t kb = []() -> uint32_t {
-        if (!pdl_enabled()) return 0u;
+// is no previous kernel to overlap with. Measured inside CUDA graphs, B from HBM: tiles of 16 and 32 rows of A
+// are fastest with 6 ... 8 k-blocks (M = 16: -4 % against none; 32 and more lose), tiles of 64 and 128 rows
+// with 4 (against 8: 22.5 / 22.8 us at M = 64 and 24.7 / 25.2 at M = 128 for N = 14336, 23.0 / 23.8 and
+// 26.0 / 26.6 for N = 4096, K = 14336).
+static uint32_t skinny_prefetch_kb(int rows_per_tile) {
+    static const int forced = []() -> int {
         const char *v = getenv("B200_HGEMM_SKINNY_PREFETCH");
-        return v ? static_cast<uint32_t>(atoi(v)) : 8u;  // measured: 8 k-blocks -4 % at M = 16 ... 64; 32 and more lose
+        return v ? atoi(v) : -1;
     }();
-    return kb;
+    if (!pdl_enabled()) return 0u;
+    if (forced >= 0) return static_cast<uint32_t>(forced);
+    return rows_per_tile >= 64 ? 4u : 8u;
 }
 
 static std::atomic<int> g_debug_cluster_capacity{0};  // b200_debug_cluster_capacity(): > 0 overrides what the device reports
@@ -1111,7 +1115,7 @@ static int run_skinny(DeviceState &st, const void *A, const void *B, void *C, si
     p.slices = skinny_slices(pl, st, N, K);
     p.kb_per_slice = ceil_div_u32(p.k_blocks, p.slices);
     p.n_pad = static_cast<uint32_t>((N + 31) / 32 * 32);
-    p.prefetch_kb = skinny_prefetch_kb();
+    p.prefetch_kb = skinny_prefetch_kb(pl.bn);
 #ifdef B200_TIMELINE
     p.timeline = g_timeline;
 #endif
